@@ -1,0 +1,309 @@
+"""Python launchers of the CUDA kernels.
+
+Every function checks its tensors (device, dtype, layout, sizes) and raises a
+clear error for a size the kernel does not take; it never computes on the CPU
+and never falls back to a library.  Kernels run on torch's current stream, so
+they can be captured into a CUDA graph with the rest of a step.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p, c_ulonglong
+from typing import Optional
+
+import torch
+
+from .build import load_library
+
+_F32, _BF16 = 0, 1
+_STATUS = {1: "a size or option this kernel does not take", 2: "the kernel launch failed"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _dt(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return _F32
+    if dtype == torch.bfloat16:
+        return _BF16
+    raise KernelError(f"dtype {dtype} is not supported (float32 or bfloat16)")
+
+
+def _check(t: torch.Tensor, name: str, dtype=None, ndim=None) -> None:
+    if not isinstance(t, torch.Tensor):
+        raise KernelError(f"{name} must be a tensor")
+    if not t.is_cuda:
+        raise KernelError(f"{name} must live on a CUDA device (there is no CPU path)")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if ndim is not None and t.dim() != ndim:
+        raise KernelError(f"{name} must have {ndim} dimensions, got shape {tuple(t.shape)}")
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _p(t: Optional[torch.Tensor]) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _run(status: int, what: str) -> None:
+    if status != 0:
+        raise KernelError(f"{what}: {_STATUS.get(status, f'status {status}')}")
+
+
+_fn_cache = {}
+
+
+def _fn(lib: str, name: str, argtypes):
+    key = (lib, name)
+    f = _fn_cache.get(key)
+    if f is None:
+        f = getattr(load_library(lib), name)
+        f.argtypes = argtypes
+        f.restype = c_int
+        _fn_cache[key] = f
+    return f
+
+
+# ------------------------------------------------------------------ embedding
+def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    """float32 [T, H] rows of ``table`` ([V, H], float32 or bfloat16) at int32 ``ids``."""
+    _check(ids, "ids", torch.int32, 1)
+    _check(table, "table", None, 2)
+    T, (V, H) = ids.numel(), table.shape
+    out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    f = _fn("elementwise", "hb_embedding",
+            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _run(f(_p(out), _p(table), _p(ids), T, H, V, _dt(table.dtype), _stream()), "embedding")
+    return out
+
+
+# ------------------------------------------------------------------ norms
+def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,
+                eps: float, out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``residual += delta`` (float32, in place) and the RMS-normed rows in ``out_dtype``.
+
+    With ``rows`` (int32) only those rows are normed and the residual is left as it was.
+    """
+    _check(residual, "residual", torch.float32, 2)
+    _check(weight, "weight", torch.float32, 1)
+    n, H = residual.shape
+    if weight.numel() != H:
+        raise KernelError(f"norm weight has {weight.numel()} entries for width {H}")
+    if delta is not None:
+        _check(delta, "delta", out_dtype, 2)
+        if tuple(delta.shape) != (n, H):
+            raise KernelError(f"delta {tuple(delta.shape)} does not match residual {(n, H)}")
+    n_out = n
+    if rows is not None:
+        _check(rows, "rows", torch.int32, 1)
+        n_out = rows.numel()
+    out = torch.empty((n_out, H), dtype=out_dtype, device=residual.device)
+    f = _fn("elementwise", "hb_add_rmsnorm",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p])
+    _run(f(_p(out), _p(residual), _p(delta), _p(weight), _p(rows), n_out, H, float(eps),
+           _dt(out_dtype), _stream()), "add_rmsnorm")
+    return out
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    _check(x, "x", None, 2)
+    _check(weight, "weight", torch.float32, 1)
+    n, H = x.shape
+    if weight.numel() != H:
+        raise KernelError(f"norm weight has {weight.numel()} entries for width {H}")
+    out = torch.empty_like(x)
+    f = _fn("elementwise", "hb_rmsnorm",
+            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p])
+    _run(f(_p(out), _p(x), _p(weight), n, H, float(eps), _dt(x.dtype), _stream()), "rmsnorm")
+    return out
+
+
+# ------------------------------------------------------------------ rotary + cache write
+def rotary_table(positions: torch.Tensor, inv_freq: torch.Tensor):
+    """cos and sin [T, rot/2] (float32) of position * inv_freq, computed in float64."""
+    _check(positions, "positions", torch.int32, 1)
+    _check(inv_freq, "inv_freq", torch.float64, 1)
+    T, half = positions.numel(), inv_freq.numel()
+    cos = torch.empty((T, half), dtype=torch.float32, device=positions.device)
+    sin = torch.empty_like(cos)
+    f = _fn("elementwise", "hb_rotary_table",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _run(f(_p(cos), _p(sin), _p(positions), _p(inv_freq), T, half, _stream()), "rotary_table")
+    return cos, sin
+
+
+def rope_kv_write(qkv: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                  positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
+                  k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
+                  num_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
+                  write_cache: bool = True) -> None:
+    """Rotate q and k of ``qkv`` ([T, (nh + 2 nkv) hd]) by the tokens' cos/sin rows
+    ([T, rot/2], float32; None = no rotation); q stays in place, rotated k and v go to the
+    tokens' slots of the cache pages ([pages, nkv, page_size, hd])."""
+    _check(qkv, "qkv", None, 2)
+    T = qkv.shape[0]
+    if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
+        raise KernelError(f"qkv width {qkv.shape[1]} is not (nh + 2 nkv) * hd = "
+                          f"{(num_heads + 2 * num_kv_heads) * head_dim}")
+    rot = 0
+    if cos is not None:
+        _check(cos, "cos", torch.float32, 2)
+        _check(sin, "sin", torch.float32, 2)
+        if cos.shape != sin.shape or cos.shape[0] != T:
+            raise KernelError(f"cos/sin tables {tuple(cos.shape)}/{tuple(sin.shape)} do not "
+                              f"match {T} tokens")
+        rot = 2 * cos.shape[1]
+        if rot > head_dim:
+            raise KernelError(f"rotary dimension {rot} exceeds head_dim {head_dim}")
+    _check(positions, "positions", torch.int32, 1)
+    _check(seq_of_token, "seq_of_token", torch.int32, 1)
+    _check(block_table, "block_table", torch.int32, 2)
+    if write_cache:
+        for name, pages in (("k_pages", k_pages), ("v_pages", v_pages)):
+            _check(pages, name, qkv.dtype, 4)
+            if tuple(pages.shape[1:]) != (num_kv_heads, page_size, head_dim):
+                raise KernelError(f"{name} has shape {tuple(pages.shape)}, expected "
+                                  f"[pages, {num_kv_heads}, {page_size}, {head_dim}]")
+    f = _fn("elementwise", "hb_rope_kv_write",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _run(f(_p(qkv), _p(cos), _p(sin), _p(positions), _p(seq_of_token), _p(block_table),
+           block_table.shape[1], _p(k_pages) if write_cache else c_void_p(0),
+           _p(v_pages) if write_cache else c_void_p(0), T, num_heads, num_kv_heads, head_dim,
+           rot, page_size, 1 if write_cache else 0, _dt(qkv.dtype), _stream()), "rope_kv_write")
+
+
+# ------------------------------------------------------------------ attention
+def attention_generic(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                      block_table: torch.Tensor, seq_of_token: torch.Tensor,
+                      positions: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
+                      page_size: int, window: Optional[int], scale: float) -> torch.Tensor:
+    """Attention of every token of the batch over its request's pages; q is read from the
+    first ``nh * hd`` columns of ``qkv``.  Returns [T, nh * hd] in qkv's dtype."""
+    _check(qkv, "qkv", None, 2)
+    _check(k_pages, "k_pages", qkv.dtype, 4)
+    _check(v_pages, "v_pages", qkv.dtype, 4)
+    _check(block_table, "block_table", torch.int32, 2)
+    _check(seq_of_token, "seq_of_token", torch.int32, 1)
+    _check(positions, "positions", torch.int32, 1)
+    if head_dim > 256 or head_dim <= 0:
+        raise KernelError(f"head_dim {head_dim} is not supported by the attention kernels (1..256)")
+    if num_heads % num_kv_heads != 0:
+        raise KernelError(f"{num_heads} query heads are not a multiple of {num_kv_heads} KV heads")
+    if tuple(k_pages.shape[1:]) != (num_kv_heads, page_size, head_dim):
+        raise KernelError(f"k_pages has shape {tuple(k_pages.shape)}, expected "
+                          f"[pages, {num_kv_heads}, {page_size}, {head_dim}]")
+    T = qkv.shape[0]
+    out = torch.empty((T, num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    f = _fn("attention_generic", "hb_attention_generic",
+            [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+             c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+    _run(f(_p(out), _p(qkv), qkv.shape[1], _p(k_pages), _p(v_pages), _p(block_table),
+           block_table.shape[1], _p(seq_of_token), _p(positions), T, num_heads, num_kv_heads,
+           head_dim, page_size, int(window or 0), float(scale), _dt(qkv.dtype), _stream()),
+         "attention_generic")
+    return out
+
+
+# ------------------------------------------------------------------ feed-forward gate
+def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(gate) * up for ``gate_up`` = [T, 2 I] (gate columns first)."""
+    _check(gate_up, "gate_up", None, 2)
+    T, two_i = gate_up.shape
+    if two_i % 2:
+        raise KernelError("gate_up must have an even width")
+    out = torch.empty((T, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+    f = _fn("elementwise", "hb_silu_mul", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _run(f(_p(out), _p(gate_up), T, two_i // 2, _dt(gate_up.dtype), _stream()), "silu_mul")
+    return out
+
+
+# ------------------------------------------------------------------ matrix products
+def linear_f32(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x [M, K] times weight [N, K] transposed (+ bias [N]) on the float32 FMA pipes."""
+    _check(x, "x", torch.float32, 2)
+    _check(weight, "weight", torch.float32, 2)
+    M, K = x.shape
+    N, K2 = weight.shape
+    if K != K2:
+        raise KernelError(f"x has {K} columns but weight has {K2}")
+    if bias is not None:
+        _check(bias, "bias", torch.float32, 1)
+        if bias.numel() != N:
+            raise KernelError(f"bias has {bias.numel()} entries for {N} outputs")
+    out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    f = _fn("gemm_f32", "hb_gemm_f32",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _run(f(_p(out), _p(x), _p(weight), _p(bias), M, N, K, K, K, N, _stream()), "gemm_f32")
+    return out
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y = x W^T + b.  float32: this package's FMA kernel.  bfloat16: the library product
+    (cuBLAS through torch), as the reference engine uses one for its projections
+    (python/helios/exec/model.py:170-181)."""
+    if x.dtype == torch.float32:
+        return linear_f32(x, weight, bias)
+    _check(x, "x", torch.bfloat16, 2)
+    _check(weight, "weight", torch.bfloat16, 2)
+    b = None if bias is None else bias.to(torch.bfloat16)
+    return torch.nn.functional.linear(x, weight, b)
+
+
+# ------------------------------------------------------------------ sampling
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
+           top_p: torch.Tensor, seed: torch.Tensor, offset: torch.Tensor) -> torch.Tensor:
+    """One token id per row of float32 ``logits`` [R, V]; per-row options as device tensors
+    (temperature float32 with 0 = greedy, top_k int32 with 0 = off, top_p float32,
+    seed and offset int64)."""
+    _check(logits, "logits", torch.float32, 2)
+    R, V = logits.shape
+    _check(temperature, "temperature", torch.float32, 1)
+    _check(top_k, "top_k", torch.int32, 1)
+    _check(top_p, "top_p", torch.float32, 1)
+    _check(seed, "seed", torch.int64, 1)
+    _check(offset, "offset", torch.int64, 1)
+    for name, t in (("temperature", temperature), ("top_k", top_k), ("top_p", top_p),
+                    ("seed", seed), ("offset", offset)):
+        if t.numel() != R:
+            raise KernelError(f"{name} has {t.numel()} entries for {R} rows")
+    out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    f = _fn("sampling", "hb_sample",
+            [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_void_p])
+    _run(f(_p(out), _p(logits), R, V, V, _p(temperature), _p(top_k), _p(top_p), _p(seed),
+           _p(offset), _stream()), "sample")
+    return out
+
+
+def philox_uniform(seed: int, offset: int) -> float:
+    """The uniform in [0, 1) that the sampling kernel draws for (seed, offset)."""
+    lib = load_library("sampling")
+    lib.hb_philox_uniform.argtypes = [c_ulonglong, c_ulonglong]
+    lib.hb_philox_uniform.restype = c_float
+    return float(lib.hb_philox_uniform(seed & (2**64 - 1), offset & (2**64 - 1)))
+
+
+def linear_logits(rows: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """Output head: float32 logits [R, V] of ``rows`` [R, H] against ``weight`` [V, H]."""
+    if rows.dtype == torch.float32:
+        return linear_f32(rows, weight, None)
+    _check(rows, "rows", torch.bfloat16, 2)
+    _check(weight, "weight", torch.bfloat16, 2)
+    return torch.mm(rows, weight.t(), out_dtype=torch.float32)
+
+
+def attention(ctx, qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+              block_table: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
+              page_size: int, window: Optional[int], scale: float) -> torch.Tensor:
+    """Attention of the step's tokens over the cache; chooses the kernel by dtype, sizes
+    and the shape of the batch described by ``ctx``."""
+    return attention_generic(qkv, k_pages, v_pages, block_table, ctx.seq_of_token, ctx.positions,
+                             num_heads, num_kv_heads, head_dim, page_size, window, scale)

@@ -1,0 +1,80 @@
+"""Grouped-query attention over the paged cache
+(python/helios/exec/model.py:156-251; math of python/helios/exec/paged_attn.py:264-408).
+
+One fused projection gives q, k and v (+ bias where the configuration has one);
+one kernel rotates q and k and writes k and v into the request's pages before
+attending, so a portion of a prompt sees itself (model.py:203-206); attention
+runs over the cache for every token of the batch, whatever mix of prompt
+portions and single decoded tokens it is; then the output projection.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from ..csrc import ops
+from .base import LayerCache, Mixer, PagedCacheSpec, WeightSpec, register_part
+
+
+class GQAAttention(Mixer):
+    def __init__(self, width: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 scale: float, qkv_bias: bool, window: Optional[int] = None,
+                 rotary: bool = True) -> None:
+        if num_heads % num_kv_heads:
+            raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} KV heads")
+        if head_dim % 2 or head_dim > 256:
+            raise ValueError(f"head_dim {head_dim} is not supported (even, at most 256)")
+        self.width = width
+        self.num_heads = num_heads
+        self.num_kv_heads = num_kv_heads
+        self.head_dim = head_dim
+        self.scale = float(scale)
+        self.qkv_bias = qkv_bias
+        self.window = window
+        self.rotary = rotary
+        self.w_qkv = self.b_qkv = self.w_o = None
+
+    # ---------------------------------------------------------------- what it keeps
+    def cache_spec(self) -> PagedCacheSpec:
+        return PagedCacheSpec(self.num_kv_heads, self.head_dim, self.window)
+
+    # ---------------------------------------------------------------- tensors
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        q, kv = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim
+        specs = {
+            "q_proj.weight": WeightSpec((q, self.width)),
+            "k_proj.weight": WeightSpec((kv, self.width)),
+            "v_proj.weight": WeightSpec((kv, self.width)),
+            "o_proj.weight": WeightSpec((self.width, q)),
+        }
+        if self.qkv_bias:
+            specs["q_proj.bias"] = WeightSpec((q,), kind="vector", init="normal")
+            specs["k_proj.bias"] = WeightSpec((kv,), kind="vector", init="normal")
+            specs["v_proj.bias"] = WeightSpec((kv,), kind="vector", init="normal")
+        return specs
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.w_qkv = torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"],
+                                tensors["v_proj.weight"]], dim=0).contiguous()
+        self.w_o = tensors["o_proj.weight"].contiguous()
+        if self.qkv_bias:
+            self.b_qkv = torch.cat([tensors["q_proj.bias"], tensors["k_proj.bias"],
+                                    tensors["v_proj.bias"]], dim=0).contiguous()
+
+    # ---------------------------------------------------------------- forward
+    def forward(self, ctx, x: torch.Tensor, cache: LayerCache, state=None) -> torch.Tensor:
+        qkv = ops.linear(x, self.w_qkv, self.b_qkv)
+        table = ctx.block_tables[cache.group]
+        cos = ctx.rotary_cos if self.rotary else None
+        sin = ctx.rotary_sin if self.rotary else None
+        ops.rope_kv_write(qkv, cos, sin, ctx.positions, ctx.seq_of_token, table,
+                          cache.k_pages, cache.v_pages, self.num_heads, self.num_kv_heads,
+                          self.head_dim, cache.page_size, write_cache=cache.write)
+        attn = ops.attention(ctx, qkv, cache.k_pages, cache.v_pages, table, self.num_heads,
+                             self.num_kv_heads, self.head_dim, cache.page_size, self.window,
+                             self.scale)
+        return ops.linear(attn, self.w_o)
+
+
+register_part("mixer", "gqa_attention", GQAAttention)

@@ -1,0 +1,165 @@
+"""Interfaces of the parts a model is put together from.
+
+A model is a list of blocks; a block arranges a mixer and a feed-forward between
+norms; a position encoding serves whichever part asks for it.  Every part takes
+its sizes and constants as constructor parameters and does not know which model
+it is in: the plan builder of an architecture (``helios_b200/models``) reads the
+typed configuration and hands each part its numbers, layer by layer.
+
+What a part must provide
+------------------------
+``weight_specs()``  local tensor name -> ``WeightSpec`` (shape, kind, init).  The
+                    loader joins the part's prefix in the plan with the local
+                    name to get the checkpoint name.
+``bind(tensors)``   receives its tensors on the device in their final dtype
+                    (matrices in the compute dtype, vectors in float32, integer
+                    tables in int32) and may fuse or re-lay them.
+``forward(...)``    see each base class.
+
+A mixer also says what it keeps between steps: ``cache_spec()`` (keys and values
+per token, in pages, all of them or a window) and ``state_spec()`` (a tensor of
+fixed size per request, in a slot).  The cache manager sizes pools and slots
+from these alone.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+
+@dataclass(frozen=True)
+class WeightSpec:
+    shape: Tuple[int, ...]
+    kind: str = "matrix"      # "matrix": compute dtype | "vector": float32 | "table": int32
+    init: str = "normal"      # "normal": N(0, std) | "ones_jitter": 1 + N(0, std) | "ones" | "zeros"
+    std: float = 0.02
+
+
+@dataclass(frozen=True)
+class PagedCacheSpec:
+    """Keys and values a mixer stores for every token."""
+    num_kv_heads: int
+    head_dim: int
+    window: Optional[int] = None      # None: every key is needed; W: only the last W
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """State of fixed size a mixer keeps per request."""
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class LayerCache:
+    """The pages of one cache id, as a mixer sees them."""
+    k_pages: torch.Tensor         # [pages, kv heads, page_size, head_dim]
+    v_pages: torch.Tensor
+    group: int                    # index into StepContext.block_tables
+    page_size: int
+    write: bool = True            # False: this run reads what another run wrote
+
+
+class Part:
+    #: False for a part whose forward depends on host values of the batch; a step
+    #: with such a part is never captured into a CUDA graph.
+    graph_safe = True
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {}
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        if tensors:
+            raise ValueError(f"{type(self).__name__} takes no tensors")
+
+
+class Norm(Part):
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+    def add_forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor],
+                    out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``residual += delta`` in float32 (in place, unless ``rows`` selects) and the
+        normed rows in ``out_dtype``.  The default does it in two steps."""
+        if rows is not None:
+            r = residual.index_select(0, rows.long())
+            if delta is not None:
+                r = r + delta.index_select(0, rows.long()).float()
+            return self.forward(r.to(out_dtype))
+        if delta is not None:
+            residual.add_(delta.float())
+        return self.forward(residual.to(out_dtype))
+
+
+class PositionEncoding(Part):
+    def prepare(self, ctx) -> None:
+        """Called once per step before the layers; may leave tables on ``ctx``."""
+
+    def embed(self, ctx, hidden: torch.Tensor) -> torch.Tensor:
+        """An additive encoding changes the embedded tokens here; default: nothing."""
+        return hidden
+
+
+class Mixer(Part):
+    def cache_spec(self) -> Optional[PagedCacheSpec]:
+        return None
+
+    def state_spec(self) -> Optional[StateSpec]:
+        return None
+
+    def forward(self, ctx, x: torch.Tensor, cache: Optional[LayerCache],
+                state: Optional[torch.Tensor]) -> torch.Tensor:
+        """x: [T, width] in the compute dtype, the batch described by ``ctx``
+        (``engine.batch.StepContext``); returns [T, width].  ``state`` is
+        [slots, *state_spec.shape]; a request's row is ``ctx.slots[seq]``."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block:
+    """Arrangement of parts in one layer."""
+
+    def named_parts(self) -> List[Tuple[str, Part]]:
+        """(prefix below the layer's own prefix, part) for every part with tensors."""
+        raise NotImplementedError
+
+    @property
+    def mixer(self) -> Optional[Mixer]:
+        return None
+
+    def forward(self, ctx, residual: torch.Tensor, delta: Optional[torch.Tensor],
+                cache: Optional[LayerCache], state: Optional[torch.Tensor]):
+        """Takes the float32 residual stream and the not-yet-added output of the
+        block before (or None); returns the pair for the next block."""
+        raise NotImplementedError
+
+
+# ---------------------------------------------------------------------- registries
+_PART_KINDS: Dict[str, Dict[str, type]] = {
+    "mixer": {}, "feed_forward": {}, "norm": {}, "position_encoding": {}, "block": {},
+}
+
+
+def register_part(kind: str, name: str, cls: type, *, replace: bool = False) -> None:
+    table = _PART_KINDS[kind]
+    if name in table and not replace:
+        raise ValueError(f"{kind} {name!r} is already registered")
+    table[name] = cls
+
+
+def part_class(kind: str, name: str) -> type:
+    try:
+        return _PART_KINDS[kind][name]
+    except KeyError:
+        known = ", ".join(sorted(_PART_KINDS.get(kind, {}))) or "none"
+        raise ValueError(f"no {kind} named {name!r}; known: {known}") from None
+
+
+def known_parts(kind: str) -> List[str]:
+    return sorted(_PART_KINDS[kind])

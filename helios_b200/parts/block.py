@@ -1,0 +1,46 @@
+"""Pre-norm residual block (python/helios/exec/model.py:340-392):
+x + mixer(norm(x)), then x + feed_forward(norm(x)).
+
+The residual stream is float32.  A block receives the stream and the output of
+the part before that is still to be added; the add is fused into the next norm.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+
+from .base import Block, FeedForward, LayerCache, Mixer, Norm, Part, register_part
+
+
+class PreNormBlock(Block):
+    def __init__(self, mixer_norm: Norm, mixer: Mixer, ffn_norm: Norm, ffn: FeedForward,
+                 names: Tuple[str, str, str, str] = ("input_layernorm.", "self_attn.",
+                                                     "post_attention_layernorm.", "mlp.")) -> None:
+        self.mixer_norm = mixer_norm
+        self._mixer = mixer
+        self.ffn_norm = ffn_norm
+        self.ffn = ffn
+        self.names = names
+
+    @property
+    def mixer(self) -> Mixer:
+        return self._mixer
+
+    def named_parts(self) -> List[Tuple[str, Part]]:
+        return list(zip(self.names, (self.mixer_norm, self._mixer, self.ffn_norm, self.ffn)))
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(p.graph_safe for _, p in self.named_parts())
+
+    def forward(self, ctx, residual: torch.Tensor, delta: Optional[torch.Tensor],
+                cache: Optional[LayerCache], state: Optional[torch.Tensor]):
+        x = self.mixer_norm.add_forward(residual, delta, ctx.act_dtype)
+        delta = self._mixer.forward(ctx, x, cache, state)
+        x = self.ffn_norm.add_forward(residual, delta, ctx.act_dtype)
+        delta = self.ffn.forward(ctx, x)
+        return residual, delta
+
+
+register_part("block", "pre_norm", PreNormBlock)
