@@ -41,10 +41,12 @@ class EngineCore:
             self.cache.release(request_id)
 
     # ------------------------------------------------------------------ the step
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], manage_cache: bool = True) -> Optional[torch.Tensor]:
         """Run exactly the given tokens as one batch over the cache earlier steps left.
-        Requests not seen before are admitted.  Returns float32 logits
-        [sum of len(want), vocab] in the order of the entries and of their ``want``."""
+        Returns float32 logits [sum of len(want), vocab] in the order of the entries and
+        of their ``want``.  With ``manage_cache`` requests not seen before are admitted,
+        pages for the new tokens are taken and the new length is committed; a scheduler
+        that does this bookkeeping itself passes False."""
         entries = [e for e in entries]
         if not entries:
             return None
@@ -65,17 +67,26 @@ class EngineCore:
                     raise ValueError(f"request {e.request_id!r} wants place {w} of {n} tokens")
         for e in entries:
             if not self.cache.has(e.request_id):
+                if not manage_cache:
+                    raise ValueError(f"request {e.request_id!r} has no cache entry")
                 self.cache.admit(e.request_id)
             if self.max_model_len is not None and \
                     self.cache.length(e.request_id) + len(e.tokens) > self.max_model_len:
                 raise ValueError(f"request {e.request_id!r} would exceed max_model_len "
                                  f"{self.max_model_len}")
-        for e in entries:
-            self.cache.extend(e.request_id, len(e.tokens))
+        if manage_cache:
+            for e in entries:
+                self.cache.extend(e.request_id, len(e.tokens))
+        else:
+            for e in entries:
+                if any(self.cache.pages_needed(e.request_id, len(e.tokens))):
+                    raise ValueError(f"request {e.request_id!r} has no pages for its "
+                                     f"{len(e.tokens)} new tokens")
         ctx = build_context(entries, self.cache, self.model.dtype, self.model.device)
         logits = self.model.forward(ctx, self.cache)
-        for e in entries:
-            self.cache.commit(e.request_id, len(e.tokens))
+        if manage_cache:
+            for e in entries:
+                self.cache.commit(e.request_id, len(e.tokens))
         self.steps_run += 1
         self.tokens_run += ctx.num_tokens
         return logits

@@ -1,0 +1,280 @@
+"""The scheduler's decisions, with a scripted executor and no GPU
+(the reference tests its scheduler the same way: tests/scheduler/test_scheduler.py:48-80)."""
+import pytest
+
+from helios_b200.cache import CacheLayout, GroupLayout
+from helios_b200.engine.scheduler import ExecFault, Scheduler, SchedulerConfig
+from helios_b200.engine.types import FinishReason, Request, SamplingParams, SeqState
+
+
+class ScriptedExecutor:
+    """Returns token 1000 + seq_id * 100 + (number of outputs so far); can fail at a step."""
+
+    def __init__(self, fault_at=None, fault_seqs=None, eos_after=None):
+        self.plans = []
+        self.fault_at = fault_at
+        self.fault_seqs = fault_seqs
+        self.eos_after = eos_after or {}
+
+    def run(self, plan):
+        self.plans.append(plan)
+        if self.fault_at is not None and plan.step_id == self.fault_at:
+            raise ExecFault("scripted", self.fault_seqs)
+        out = {}
+        for item in plan.items:
+            if item.sample:
+                if self.eos_after.get(item.seq_id) == item.rng_offset:
+                    out[item.seq_id] = 2
+                else:
+                    out[item.seq_id] = 1000 + item.seq_id * 100 + item.rng_offset
+        return out
+
+
+def make(num_pages=64, page=4, budget=16, max_seqs=8, max_len=256, window=None, chunked=True,
+         watermark=0.0):
+    groups = [GroupLayout(None, num_pages)]
+    if window:
+        groups.append(GroupLayout(window, num_pages))
+    cache = CacheLayout(groups, page, max_slots=max_seqs, watermark=watermark)
+    sched = Scheduler(SchedulerConfig(max_num_seqs=max_seqs, max_num_batched_tokens=budget,
+                                      max_model_len=max_len, enable_chunked_prefill=chunked), cache)
+    return sched, cache
+
+
+def req(n, max_tokens=4, rid="r", **kw):
+    return Request(rid, list(range(1, n + 1)), SamplingParams(max_tokens=max_tokens, **kw))
+
+
+def run_all(sched, ex, limit=500):
+    steps = 0
+    while sched.has_work:
+        sched.step(ex)
+        sched.check_invariants()
+        steps += 1
+        assert steps < limit, "the scheduler does not finish"
+    return steps
+
+
+def test_request_validation():
+    sched, _ = make(num_pages=4, page=4, max_len=32)
+    with pytest.raises(ValueError):
+        sched.add_request(req(0))
+    with pytest.raises(ValueError):
+        sched.add_request(req(32))                       # >= max_model_len
+    with pytest.raises(ValueError):
+        sched.add_request(req(13))                       # 4 pages + 1 to grow > pool
+    with pytest.raises(ValueError):
+        sched.add_request(Request("x", [1], SamplingParams(max_tokens=0)))
+    with pytest.raises(ValueError):
+        sched.add_request(Request("x", [1], SamplingParams(top_p=0.0)))
+    sched.add_request(req(12))
+
+
+def test_prompt_is_cut_into_portions_under_the_budget():
+    sched, _ = make(budget=16)
+    sched.add_request(req(40, max_tokens=3))
+    ex = ScriptedExecutor()
+    run_all(sched, ex)
+    sizes = [[i.num_tokens for i in p.items] for p in ex.plans]
+    assert sizes == [[16], [16], [8], [1], [1]]
+    starts = [p.items[0].start_pos for p in ex.plans]
+    assert starts == [0, 16, 32, 40, 41]
+    assert [p.items[0].sample for p in ex.plans] == [False, False, True, True, True]
+    seq = sched.take_finished()[0]
+    assert seq.output_token_ids == [1000, 1001, 1002] and seq.finish_reason is FinishReason.LENGTH
+
+
+def test_decodes_claim_budget_first_and_share_a_step_with_portions():
+    sched, _ = make(budget=8)
+    sched.add_request(req(3, max_tokens=6, rid="a"))
+    ex = ScriptedExecutor()
+    sched.step(ex)                                       # a: whole prompt
+    sched.add_request(req(20, max_tokens=2, rid="b"))
+    sched.step(ex)
+    plan = ex.plans[-1]
+    by_seq = {i.seq_id: i for i in plan.items}
+    assert by_seq[0].num_tokens == 1 and by_seq[0].start_pos == 3      # a decodes
+    assert by_seq[1].num_tokens == 7 and by_seq[1].start_pos == 0      # b gets what is left
+    assert plan.num_tokens == 8
+    run_all(sched, ex)
+    assert all(p.num_tokens <= 8 for p in ex.plans)
+
+
+def test_portions_down_to_one_token_when_decodes_take_the_budget():
+    sched, _ = make(budget=4, max_seqs=4)
+    for i in range(3):
+        sched.add_request(req(2, max_tokens=30, rid=f"d{i}"))
+    ex = ScriptedExecutor()
+    sched.step(ex)
+    sched.step(ex)
+    sched.add_request(req(9, max_tokens=1, rid="long"))
+    sched.step(ex)
+    sizes = {i.seq_id: i.num_tokens for i in ex.plans[-1].items}
+    assert sizes[3] == 1 and sum(sizes.values()) == 4
+
+
+def test_without_chunking_a_long_prompt_runs_alone():
+    sched, _ = make(budget=8, chunked=False)
+    sched.add_request(req(3, max_tokens=2, rid="short"))
+    sched.add_request(req(20, max_tokens=1, rid="long"))
+    ex = ScriptedExecutor()
+    run_all(sched, ex)
+    for p in ex.plans:
+        if any(i.num_tokens == 20 for i in p.items):
+            assert len(p.items) == 1
+    assert sorted(s.request.request_id for s in sched.take_finished()) == ["long", "short"]
+
+
+def test_stop_token_finishes_and_is_kept():
+    sched, _ = make()
+    sched.add_request(req(5, max_tokens=10, stop_token_ids=[2]))
+    ex = ScriptedExecutor(eos_after={0: 2})
+    run_all(sched, ex)
+    seq = sched.take_finished()[0]
+    assert seq.output_token_ids == [1000, 1001, 2] and seq.finish_reason is FinishReason.STOP
+
+
+def test_max_model_len_finishes_with_length():
+    sched, _ = make(max_len=10)
+    sched.add_request(req(7, max_tokens=50))
+    run_all(sched, ScriptedExecutor())
+    seq = sched.take_finished()[0]
+    assert seq.total_tokens == 10 and seq.finish_reason is FinishReason.LENGTH
+
+
+def test_a_request_that_does_not_fit_waits_and_a_smaller_one_passes():
+    sched, cache = make(num_pages=10, page=4, budget=64)
+    sched.add_request(req(20, max_tokens=8, rid="big1"))       # 5 pages + growth
+    sched.add_request(req(20, max_tokens=2, rid="big2"))       # does not fit beside big1
+    sched.add_request(req(4, max_tokens=2, rid="small"))
+    ex = ScriptedExecutor()
+    sched.step(ex)
+    running = {s.request.request_id for s in sched.running}
+    assert running == {"big1", "small"}
+    assert [s.request.request_id for s in sched.waiting] == ["big2"]
+    run_all(sched, ex)
+    assert len(sched.take_finished()) == 3
+
+
+def test_head_of_queue_gets_a_reservation_after_being_passed():
+    sched, _ = make(num_pages=10, page=4, budget=64)
+    sched.config.reservation_after_steps = 3
+    sched.add_request(req(20, max_tokens=40, rid="runs"))
+    ex = ScriptedExecutor()
+    sched.step(ex)
+    sched.add_request(req(30, max_tokens=1, rid="starved"))     # 8 pages + 1: not beside "runs"
+    admitted_small = 0
+    for i in range(12):
+        sched.add_request(req(2, max_tokens=1, rid=f"s{i}"))
+        sched.step(ex)
+        sched.check_invariants()
+    small_running_late = [s for s in sched.running if s.request.request_id.startswith("s")]
+    waiting_small = [s for s in sched.waiting if s.request.request_id.startswith("s")]
+    assert waiting_small, "after the reservation small requests must wait behind the head"
+    run_all(sched, ex)
+    done = {s.request.request_id for s in sched.take_finished()}
+    assert "starved" in done
+
+
+def test_pages_run_out_before_a_step_newest_is_preempted_and_output_is_unchanged():
+    # two requests whose growth cannot both be served: the newer one is preempted,
+    # recomputed with its outputs so far, and still produces the same tokens
+    def outputs(num_pages):
+        sched, _ = make(num_pages=num_pages, page=4, budget=64)
+        sched.add_request(req(7, max_tokens=14, rid="old"))
+        sched.add_request(req(7, max_tokens=14, rid="new"))
+        ex = ScriptedExecutor()
+        run_all(sched, ex)
+        fin = {s.request.request_id: s for s in sched.take_finished()}
+        return fin, sched.stats.preemptions, ex
+
+    roomy, n0, _ = outputs(64)
+    tight, n1, ex = outputs(8)
+    assert n0 == 0 and n1 >= 1
+    for rid in ("old", "new"):
+        assert tight[rid].output_token_ids == roomy[rid].output_token_ids
+        assert len(tight[rid].output_token_ids) == 14
+    assert tight["new"].preempt_count >= 1 and tight["old"].preempt_count == 0
+    # the recomputed portion brought prompt AND outputs, and sampled the NEXT token
+    redo = [i for p in ex.plans for i in p.items if i.seq_id == 1 and i.start_pos == 0][1]
+    assert redo.num_tokens > 7 and redo.rng_offset == redo.num_tokens - 7
+
+
+def test_preempted_request_goes_to_the_front_of_the_queue():
+    sched, _ = make(num_pages=8, page=4, budget=64)
+    sched.add_request(req(7, max_tokens=14, rid="old"))
+    sched.add_request(req(7, max_tokens=14, rid="new"))
+    ex = ScriptedExecutor()
+    sched.step(ex)
+    sched.add_request(req(3, max_tokens=1, rid="later"))
+    while sched.stats.preemptions == 0:
+        sched.step(ex)
+    assert sched.waiting[0].request.request_id == "new"
+    assert sched.waiting[0].state is SeqState.PREEMPTED
+
+
+def test_the_only_running_request_is_never_preempted_and_ends_with_length():
+    sched, cache = make(num_pages=4, page=4, budget=64, max_len=200)
+    sched.add_request(req(8, max_tokens=100))
+    run_all(sched, ScriptedExecutor())
+    seq = sched.take_finished()[0]
+    assert seq.finish_reason is FinishReason.LENGTH and seq.preempt_count == 0
+    # the pool holds 16 tokens; the token sampled from the 16th needs no place of its own
+    assert seq.total_tokens == 17 and cache.pools[0].num_pages * 4 == 16
+    assert cache.pools[0].num_free == 4
+
+
+def test_fault_preempts_the_named_sequences_only():
+    sched, _ = make()
+    sched.add_request(req(5, max_tokens=6, rid="a"))
+    sched.add_request(req(5, max_tokens=6, rid="b"))
+    ex = ScriptedExecutor(fault_at=3, fault_seqs=[1])
+    run_all(sched, ex)
+    fin = {s.request.request_id: s for s in sched.take_finished()}
+    assert fin["a"].preempt_count == 0 and fin["b"].preempt_count == 1
+    assert fin["a"].output_token_ids == [1000 + k for k in range(6)]
+    assert fin["b"].output_token_ids == [1100 + k for k in range(6)]
+    assert sched.stats.faults == 1
+
+
+def test_abort_frees_everything():
+    sched, cache = make()
+    a = sched.add_request(req(9, max_tokens=50, rid="a"))
+    b = sched.add_request(req(9, max_tokens=50, rid="b"))
+    ex = ScriptedExecutor()
+    sched.step(ex)
+    assert sched.abort(a) and not sched.abort(a)
+    sched.check_invariants()
+    sched.abort(b)
+    assert cache.pools[0].num_free == 64 and not sched.has_work
+    assert {s.finish_reason for s in sched.take_finished()} == {FinishReason.ABORTED}
+
+
+def test_window_group_lets_long_requests_share_a_small_pool():
+    sched, cache = make(num_pages=40, page=4, budget=16, window=8)
+    for i in range(3):
+        sched.add_request(req(30, max_tokens=20, rid=f"w{i}"))
+    run_all(sched, ScriptedExecutor())
+    assert len(sched.take_finished()) == 3
+    assert all(p.num_free == p.num_pages for p in cache.pools)
+
+
+def test_same_requests_same_steps():
+    # python/helios/core/scheduler.py:7-20: no clock, no randomness
+    def trace():
+        sched, _ = make(num_pages=12, page=4, budget=12, max_seqs=3)
+        ex = ScriptedExecutor()
+        for i, n in enumerate([9, 14, 5, 11, 3]):
+            sched.add_request(req(n, max_tokens=5 + i, rid=f"r{i}"))
+        run_all(sched, ex)
+        return [[(i.seq_id, i.start_pos, i.num_tokens, i.sample) for i in p.items] for p in ex.plans]
+
+    assert trace() == trace()
+
+
+def test_scheduler_source_uses_no_clock_or_random():
+    import inspect
+    import helios_b200.engine.scheduler as mod
+
+    src = inspect.getsource(mod)
+    assert "import time" not in src and "import random" not in src
