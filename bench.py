@@ -1,0 +1,303 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of helios_b200 on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Default run: the layer sizes of Llama-3.1-8B with random bfloat16 weights, a decode
+batch of 8 at a context of 4,096 tokens; it prints ONE JSON line.  ``value`` is
+decoded tokens a second of the step function alone (device-timed), ``e2e`` the same
+through the Python entry point (host token ids in, sampled ids out), ``prefill`` a
+2,048-token prompt, ``points`` decoding at batch 1 and 64, ``roofline`` the bytes the
+decode step has to read over its time.  Synthetic token ids, uniform from a seed.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LLAMA_31_8B = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "vocab_size": 128256,
+    "hidden_size": 4096, "intermediate_size": 14336, "num_hidden_layers": 32,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128,
+    "max_position_embeddings": 131072, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+    "attention_bias": False, "tie_word_embeddings": False, "hidden_act": "silu",
+    "torch_dtype": "bfloat16",
+}
+FULL_LAYERS = 32
+CONTEXT = 4096
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                    "source": "measured"}
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.samples = []
+        self.proc = None
+        self.index = index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append((time.time(), line.strip()))
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self, t0=None, t1=None):
+        mhz, max_mhz, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ts, line in self.samples:
+            if t0 is not None and not (t0 <= ts <= t1 + 0.2):
+                continue
+            parts = [p.strip() for p in line.split(",")]
+            try:
+                mhz.append(int(parts[0]))
+                max_mhz = max(max_mhz, int(parts[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, parts[2:]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": max_mhz or None,
+                "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+def step_flops(cfg, layers, tokens, ctx_start):
+    """Matrix-product and attention flops of a step of ``tokens`` new tokens per request
+    starting at context ``ctx_start`` (one request)."""
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_tok = 2 * ((nh + 2 * nkv) * hd * H + nh * hd * H + 3 * H * I)
+    attn = 0
+    for i in range(tokens):
+        attn += 4 * nh * hd * (ctx_start + i + 1)
+    return layers * (per_tok * tokens + attn) + 2 * V * H
+
+
+def decode_bytes(cfg, layers, batch, ctx, dtype_bytes=2):
+    """Bytes a decode step must read: every weight it uses once, and the cache of the
+    live requests."""
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    w = layers * ((nh + 2 * nkv) * hd * H + nh * hd * H + 3 * H * I) * dtype_bytes
+    w += V * H * dtype_bytes + batch * H * dtype_bytes       # output head, embedding rows
+    kv = layers * batch * ctx * 2 * nkv * hd * dtype_bytes
+    return w + kv
+
+
+def run_reference(args):
+    print(json.dumps({"impl": "reference",
+                      "unavailable": "reference arm not wired up yet in this bench"}))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS,
+                    help="fewer layers than the model has (both numbers are reported)")
+    ap.add_argument("--context", type=int, default=CONTEXT)
+    ap.add_argument("--points", default="1,64", help="further decode batch sizes")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--seed", type=int, default=0)
+    args = ap.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.impl == "reference":
+        return run_reference(args)
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    from helios_b200.csrc import ops
+    from helios_b200.engine.batch import StepEntry
+    from helios_b200.engine.core import EngineCore
+    from helios_b200.engine.model import DecoderModel
+
+    peaks = load_peaks()
+    cfg = dict(LLAMA_31_8B, num_hidden_layers=args.layers)
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda:0")
+    model = DecoderModel.from_config(cfg, seed=args.seed, dtype="bfloat16", device=dev)
+    page = 16
+    point_batches = [int(b) for b in args.points.split(",") if b.strip()]
+    max_batch = max([args.batch] + point_batches)
+    core = EngineCore(model, page_size=page, num_pages=max_batch * (args.context // page) + 64,
+                      max_slots=max_batch, max_model_len=args.context + 1)
+    gen = torch.Generator().manual_seed(args.seed)
+
+    def tokens(n):
+        return torch.randint(0, cfg["vocab_size"], (n,), generator=gen).tolist()
+
+    def timed(fn, n):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(n):
+            fn()
+        end.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(end) / n
+
+    # ---------------------------------------------------------------- prefill
+    prefill = None
+    if not args.no_prefill:
+        times = []
+        for i in range(4):
+            toks = tokens(PREFILL_TOKENS)
+            ms = timed(lambda: core.step([StepEntry("p", toks, [PREFILL_TOKENS - 1])]), 1)
+            core.end("p")
+            if i >= 1:
+                times.append(ms)
+        ms = statistics.median(times)
+        flops = step_flops(cfg, args.layers, PREFILL_TOKENS, 0)
+        prefill = {"value": round(PREFILL_TOKENS / ms * 1e3, 1), "tokens": PREFILL_TOKENS,
+                   "ms": round(ms, 3),
+                   "frac": round(flops / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
+
+    # ---------------------------------------------------------------- decode
+    def fill(batch, ctx0):
+        """``batch`` requests with ``ctx0`` tokens of real prompt in the cache."""
+        for b in range(batch):
+            left = ctx0
+            while left > 0:
+                n = min(left, PREFILL_TOKENS)
+                core.step([StepEntry(f"d{b}", tokens(n), [])])
+                left -= n
+
+    def decode_run(batch, steps, warmup):
+        ctx0 = args.context - steps - warmup
+        fill(batch, ctx0)
+        last = tokens(batch)
+
+        def one():
+            core.step([StepEntry(f"d{b}", [last[b]], [0]) for b in range(batch)])
+
+        for _ in range(warmup):
+            one()
+        before = ops.launch_count
+        ms = timed(one, steps)
+        launches = ops.launch_count - before
+        for b in range(batch):
+            core.end(f"d{b}")
+        return ms, launches, ctx0 + warmup + steps // 2
+
+    sampler = ClockSampler()
+    sampler.start()
+    t0 = time.time()
+    ms, launches, mean_ctx = decode_run(args.batch, args.steps, args.warmup)
+    t1 = time.time()
+    clocks = sampler.summary(t0, t1)
+    value = args.batch / ms * 1e3
+    need = decode_bytes(cfg, args.layers, args.batch, mean_ctx)
+    achieved = need / (ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
+                "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
+                "peak_source": peaks["source"]}
+
+    points = {}
+    for b in point_batches:
+        pms, _, _ = decode_run(b, max(8, args.steps // 2), args.warmup)
+        points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
+
+    # ---------------------------------------------------------------- end to end
+    e2e = None
+    if not args.no_e2e:
+        from helios_b200.config import EngineConfig
+        from helios_b200.engine.llm import LLMEngine
+        from helios_b200.engine.types import SamplingParams
+
+        del core
+        torch.cuda.empty_cache()
+        engine = LLMEngine(EngineConfig(
+            model_dir="", dtype="bfloat16", block_size=page, max_num_seqs=args.batch,
+            max_num_batched_tokens=PREFILL_TOKENS, max_model_len=args.context + 8,
+            num_blocks=args.batch * (args.context // page + 2) + 8, watermark=0.0), model=model)
+        ctx0 = args.context - args.steps - args.warmup
+        for b in range(args.batch):
+            engine.add_request(f"e{b}", tokens(ctx0), SamplingParams(max_tokens=args.steps + args.warmup + 4))
+        while any(s.num_pending_tokens > 1 for s in engine.scheduler.running) or engine.scheduler.waiting:
+            engine.step()
+        for _ in range(args.warmup):
+            engine.step()
+        torch.cuda.synchronize()
+        w0 = time.perf_counter()
+        for _ in range(args.steps):
+            engine.step()
+        torch.cuda.synchronize()
+        wall = (time.perf_counter() - w0) / args.steps
+        h2d = 4 * (args.batch * 8 + args.batch * (args.context // page + 1)) + args.batch * 28
+        e2e = {"value": round(args.batch / wall, 1), "unit": "tokens/s",
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch}
+    sampler.stop()
+
+    line = {
+        "metric": "decode tokens/s (Llama-3.1-8B sizes, bf16, batch 8, context 4096)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic token ids (uniform, seeded), random weights N(0, 0.02)",
+        "impl": "ours",
+        "config": {"model": "Llama-3.1-8B sizes", "layers": args.layers, "layers_full": FULL_LAYERS,
+                   "hidden": 4096, "heads": 32, "kv_heads": 8, "head_dim": 128,
+                   "intermediate": 14336, "vocab": 128256, "global_batch": args.batch,
+                   "seq_len": args.context, "page_size": page, "parallelism": "single GPU",
+                   "l2": "inputs (weights + cache) larger than L2", "seed": args.seed},
+        "clocks": clocks, "gpu_launches": launches, "prefill": prefill, "roofline": roofline,
+        "points": points, "e2e": e2e,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -52,7 +52,13 @@ def _p(t: Optional[torch.Tensor]) -> c_void_p:
     return c_void_p(0 if t is None else t.data_ptr())
 
 
+#: launches of this package's own kernels since import (library products are not counted)
+launch_count = 0
+
+
 def _run(status: int, what: str) -> None:
+    global launch_count
+    launch_count += 1
     if status != 0:
         raise KernelError(f"{what}: {_STATUS.get(status, f'status {status}')}")
 
