@@ -215,6 +215,8 @@ class DenseDecoderConfig:
             out["use_sliding_window"] = self.use_sliding_window
             if self.max_window_layers is not None:
                 out["max_window_layers"] = self.max_window_layers
+            out["layer_types"] = ["full_attention" if w is None else "sliding_attention"
+                                  for w in self.layer_windows]
         if self.bos_token_id is not None:
             out["bos_token_id"] = self.bos_token_id
         if self.eos_token_ids:

@@ -1,0 +1,525 @@
+// bfloat16 attention over the paged cache on the tensor cores (mma.sync m16n8k16,
+// float32 accumulate), for head sizes 32, 64, 96 and 128.
+//
+//   * decode: one query token per request.  A block takes one (request, KV head,
+//     slice of the context); the query heads that share the KV head are the rows
+//     of one MMA tile, so every key and value is read once for the whole group.
+//     Slices are merged by a second kernel (flash-decoding).
+//   * prefill / mixed: tiles of query tokens of one request against the keys the
+//     cache holds for it, causal by position (and a window), whatever mix of
+//     prompt portions and single tokens the batch is.
+//
+// Math follows python/helios/exec/paged_attn.py:264-408 (scores = q.k * scale, mask,
+// softmax in float32, times V); pages are [page, kv head, slot, head_dim] as in
+// paged_attn.py:49.  Scores, the running maximum, the sum and the output
+// accumulators are float32; probabilities are rounded to bfloat16 for the PV
+// product, as the reference casts them to the value dtype (paged_attn.py:293).
+#include "common.cuh"
+
+namespace {
+
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, int src_bytes) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(src_bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// One query row group (16 rows) against a tile of NT*8 keys held in shared memory
+// (rows of HD + 8 bfloat16): S += Q K^T.
+template <int HD, int NT>
+__device__ __forceinline__ void qk_tile(float (&s)[NT][4], const uint32_t (&qa)[HD / 16][4],
+                                        const __nv_bfloat16* k_tile, int lane) {
+  constexpr int RS = HD + 8;
+#pragma unroll
+  for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+    for (int np = 0; np < NT / 2; ++np) {
+      uint32_t r[4];
+      const int row = 16 * np + (lane >> 4) * 8 + (lane & 7);
+      const int col = ks * 16 + ((lane >> 3) & 1) * 8;
+      ldmatrix_x4(r, k_tile + row * RS + col);
+      mma_bf16(s[2 * np], qa[ks], r[0], r[1]);
+      mma_bf16(s[2 * np + 1], qa[ks], r[2], r[3]);
+    }
+  }
+}
+
+// O += P V for the same tile; P comes from the score fragments.
+template <int HD, int NT>
+__device__ __forceinline__ void pv_tile(float (&o)[HD / 8][4], const float (&p)[NT][4],
+                                        const __nv_bfloat16* v_tile, int lane) {
+  constexpr int RS = HD + 8;
+#pragma unroll
+  for (int kk = 0; kk < NT / 2; ++kk) {
+    uint32_t pa[4];
+    pa[0] = pack_bf16(p[2 * kk][0], p[2 * kk][1]);
+    pa[1] = pack_bf16(p[2 * kk][2], p[2 * kk][3]);
+    pa[2] = pack_bf16(p[2 * kk + 1][0], p[2 * kk + 1][1]);
+    pa[3] = pack_bf16(p[2 * kk + 1][2], p[2 * kk + 1][3]);
+#pragma unroll
+    for (int dp = 0; dp < HD / 16; ++dp) {
+      uint32_t r[4];
+      const int row = 16 * kk + ((lane >> 3) & 1) * 8 + (lane & 7);
+      const int col = 16 * dp + (lane >> 4) * 8;
+      ldmatrix_x4_trans(r, v_tile + row * RS + col);
+      mma_bf16(o[2 * dp], pa, r[0], r[1]);
+      mma_bf16(o[2 * dp + 1], pa, r[2], r[3]);
+    }
+  }
+}
+
+// Online softmax step over the masked scores of a tile (log2 domain).
+template <int HD, int NT>
+__device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&m)[2], float (&l)[2],
+                                             float (&o)[HD / 8][4]) {
+  float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    mx[0] = fmaxf(mx[0], fmaxf(s[nt][0], s[nt][1]));
+    mx[1] = fmaxf(mx[1], fmaxf(s[nt][2], s[nt][3]));
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+    const float m_new = fmaxf(m[r], mx[r]);
+    const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+    const float corr = exp2f(m[r] - m_use);
+    m[r] = m_new;
+    l[r] *= corr;
+#pragma unroll
+    for (int nt = 0; nt < HD / 8; ++nt) {
+      o[nt][2 * r] *= corr;
+      o[nt][2 * r + 1] *= corr;
+    }
+    float sum = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      s[nt][2 * r] = exp2f(s[nt][2 * r] - m_use);
+      s[nt][2 * r + 1] = exp2f(s[nt][2 * r + 1] - m_use);
+      sum += s[nt][2 * r] + s[nt][2 * r + 1];
+    }
+    l[r] += sum;
+  }
+}
+
+// ------------------------------------------------------------------------ decode
+constexpr int DEC_WARPS = 4;
+constexpr int DEC_TILE = 32;   // keys per warp tile
+
+template <int HD>
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
+                        float* __restrict__ part_ml, const __nv_bfloat16* __restrict__ q,
+                        int q_stride, const __nv_bfloat16* __restrict__ k_pages,
+                        const __nv_bfloat16* __restrict__ v_pages,
+                        const int* __restrict__ block_table, int bt_stride,
+                        const int* __restrict__ positions, int nh, int nkv, int page_size,
+                        int window, float scale_log2, int n_splits) {
+  constexpr int RS = HD + 8;
+  constexpr int TILE_ELEMS = DEC_TILE * RS;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+
+  const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = nh / nkv;
+  const int pos = positions[seq];
+  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int n_keys = pos - lo + 1;
+  // slices of whole tiles
+  const int tiles_total = (n_keys + DEC_TILE - 1) / DEC_TILE;
+  const int tiles_per_split = (tiles_total + n_splits - 1) / n_splits;
+  const int tile_begin = split * tiles_per_split;
+  const int tile_end = min(tiles_total, tile_begin + tiles_per_split);
+  const int k_end = pos + 1;
+  const int* table = block_table + (size_t)seq * bt_stride;
+
+  // query fragments: rows = the group's heads (zero beyond G)
+  uint32_t qa[HD / 16][4];
+  {
+    const int g0 = lane >> 2, c0 = 2 * (lane & 3);
+    const __nv_bfloat16* qrow = q + (size_t)seq * q_stride + (size_t)kvh * G * HD;
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int row = g0 + (e & 1) * 8;
+        const int col = ks * 16 + c0 + (e >> 1) * 8;
+        qa[ks][e] = (row < G) ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)row * HD + col) : 0u;
+      }
+    }
+  }
+
+  __nv_bfloat16* my = smem + (size_t)warp * 4 * TILE_ELEMS;   // [stage][k|v][tile]
+  auto load_tile = [&](int tile, int stage) {
+    const int key = lo + tile * DEC_TILE + lane;
+    const bool valid = key < k_end;
+    size_t base = 0;
+    if (valid) {
+      const int page = table[key / page_size];
+      base = (((size_t)page * nkv + kvh) * page_size + key % page_size) * HD;
+    }
+    __nv_bfloat16* kd = my + (size_t)(stage * 2) * TILE_ELEMS + lane * RS;
+    __nv_bfloat16* vd = kd + TILE_ELEMS;
+    const int bytes = valid ? 16 : 0;
+#pragma unroll
+    for (int c = 0; c < HD / 8; ++c) {
+      cp_async16(kd + c * 8, k_pages + base + c * 8, bytes);
+      cp_async16(vd + c * 8, v_pages + base + c * 8, bytes);
+    }
+  };
+
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+  int tile = tile_begin + warp;
+  if (tile < tile_end) load_tile(tile, 0);
+  cp_async_commit();
+  int stage = 0;
+  for (; tile < tile_end; tile += DEC_WARPS, stage ^= 1) {
+    if (tile + DEC_WARPS < tile_end) load_tile(tile + DEC_WARPS, stage ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncwarp();
+    const __nv_bfloat16* kt = my + (size_t)(stage * 2) * TILE_ELEMS;
+    const __nv_bfloat16* vt = kt + TILE_ELEMS;
+    float s[DEC_TILE / 8][4];
+#pragma unroll
+    for (int i = 0; i < DEC_TILE / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+    qk_tile<HD, DEC_TILE / 8>(s, qa, kt, lane);
+    const int key0 = lo + tile * DEC_TILE + 2 * (lane & 3);
+#pragma unroll
+    for (int nt = 0; nt < DEC_TILE / 8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = key0 + nt * 8 + (e & 1);
+        s[nt][e] = (key < k_end) ? s[nt][e] * scale_log2 : -INFINITY;
+      }
+    }
+    softmax_step<HD, DEC_TILE / 8>(s, m, l, o);
+    pv_tile<HD, DEC_TILE / 8>(o, s, vt, lane);
+    __syncwarp();
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+  }
+
+  // merge the block's warps through shared memory (reusing the tile buffers)
+  __syncthreads();
+  float* red_o = reinterpret_cast<float*>(smem_raw);                 // [warps][16][HD]
+  float* red_m = red_o + DEC_WARPS * 16 * HD;                        // [warps][16]
+  float* red_l = red_m + DEC_WARPS * 16;
+  {
+    const int g0 = lane >> 2, c0 = 2 * (lane & 3);
+#pragma unroll
+    for (int nt = 0; nt < HD / 8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int row = g0 + (e >> 1) * 8, col = nt * 8 + c0 + (e & 1);
+        red_o[((size_t)warp * 16 + row) * HD + col] = o[nt][e];
+      }
+    }
+    if ((lane & 3) == 0) {
+      red_m[warp * 16 + g0] = m[0];
+      red_m[warp * 16 + g0 + 8] = m[1];
+      red_l[warp * 16 + g0] = l[0];
+      red_l[warp * 16 + g0 + 8] = l[1];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * HD; idx += DEC_WARPS * 32) {
+    const int row = idx / HD, d = idx - row * HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, red_m[w * 16 + row]);
+    const float m_use = (M == -INFINITY) ? 0.f : M;
+    float L = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) {
+      const float f = exp2f(red_m[w * 16 + row] - m_use);
+      L += red_l[w * 16 + row] * f;
+      acc += red_o[((size_t)w * 16 + row) * HD + d] * f;
+    }
+    const int h = kvh * G + row;
+    if (n_splits == 1) {
+      out[((size_t)seq * nh + h) * HD + d] = __float2bfloat16_rn(acc / L);
+    } else {
+      const size_t p = ((size_t)seq * nh + h) * n_splits + split;
+      part_o[p * HD + d] = acc;
+      if (d == 0) {
+        part_ml[p * 2] = M;
+        part_ml[p * 2 + 1] = L;
+      }
+    }
+  }
+}
+
+template <int HD>
+__global__ void decode_merge_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o,
+                                    const float* __restrict__ part_ml, int n_splits) {
+  const size_t row = blockIdx.x;   // seq * nh + head
+  const float* ml = part_ml + row * n_splits * 2;
+  float M = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, ml[2 * s]);
+  float L = 0.f;
+  for (int s = 0; s < n_splits; ++s) L += ml[2 * s + 1] * exp2f(ml[2 * s] - M);
+  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < n_splits; ++s)
+      acc += part_o[(row * n_splits + s) * HD + d] * exp2f(ml[2 * s] - M);
+    out[row * HD + d] = __float2bfloat16_rn(acc / L);
+  }
+}
+
+// ------------------------------------------------------------------------ prefill / mixed
+constexpr int PRE_WARPS = 8;
+constexpr int PRE_TILE = 64;   // keys per block tile
+
+template <int HD>
+__global__ void __launch_bounds__(PRE_WARPS * 32)
+prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ q,
+                         int q_stride, const __nv_bfloat16* __restrict__ k_pages,
+                         const __nv_bfloat16* __restrict__ v_pages,
+                         const int* __restrict__ block_table, int bt_stride,
+                         const int* __restrict__ q_tiles, const int* __restrict__ cu_tokens,
+                         const int* __restrict__ start_pos, int nh, int nkv, int heads_per_block,
+                         int token_subtiles, int page_size, int window, float scale_log2) {
+  constexpr int RS = HD + 8;
+  constexpr int TILE_ELEMS = PRE_TILE * RS;
+  constexpr int CHUNKS = HD / 8;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [stage][k|v][tile]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = nh / nkv;
+  const int head_blocks = (G + heads_per_block - 1) / heads_per_block;
+  const int kvh = blockIdx.y / head_blocks, hb = blockIdx.y - kvh * head_blocks;
+  const int seq = q_tiles[2 * blockIdx.x], t0 = q_tiles[2 * blockIdx.x + 1];
+  const int tok0 = cu_tokens[seq], n_tok = cu_tokens[seq + 1] - tok0;
+  const int sp = start_pos[seq];
+  const int BQ = 16 * token_subtiles;
+  const int p_first = sp + t0;
+  const int p_last = sp + min(n_tok, t0 + BQ) - 1;
+  const int k_min = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
+  const int* table = block_table + (size_t)seq * bt_stride;
+
+  const int head_local = warp % heads_per_block, sub = warp / heads_per_block;
+  const int g_in_kv = hb * heads_per_block + head_local;
+  const bool active = sub < token_subtiles && g_in_kv < G && (t0 + sub * 16) < n_tok;
+  const int h = kvh * G + g_in_kv;
+  const int g0 = lane >> 2, c0 = 2 * (lane & 3);
+  // the two rows of this thread: local tokens and their positions
+  const int tl0 = t0 + sub * 16 + g0, tl1 = tl0 + 8;
+  const int pr0 = sp + tl0, pr1 = sp + tl1;
+
+  uint32_t qa[HD / 16][4];
+#pragma unroll
+  for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int tl = (e & 1) ? tl1 : tl0;
+      const int col = ks * 16 + c0 + (e >> 1) * 8;
+      qa[ks][e] = (active && tl < n_tok)
+          ? *reinterpret_cast<const uint32_t*>(q + (size_t)(tok0 + tl) * q_stride + (size_t)h * HD + col)
+          : 0u;
+    }
+  }
+
+  auto load_tile = [&](int kt, int stage) {
+    __nv_bfloat16* kd = smem + (size_t)(stage * 2) * TILE_ELEMS;
+    __nv_bfloat16* vd = kd + TILE_ELEMS;
+    for (int idx = threadIdx.x; idx < PRE_TILE * CHUNKS; idx += PRE_WARPS * 32) {
+      const int row = idx / CHUNKS, c = idx - row * CHUNKS;
+      const int key = kt * PRE_TILE + row;
+      const bool valid = key >= k_min && key <= p_last;
+      size_t base = 0;
+      if (valid) {
+        const int page = table[key / page_size];
+        base = (((size_t)page * nkv + kvh) * page_size + key % page_size) * HD + c * 8;
+      }
+      const int bytes = valid ? 16 : 0;
+      cp_async16(kd + row * RS + c * 8, k_pages + base, bytes);
+      cp_async16(vd + row * RS + c * 8, v_pages + base, bytes);
+    }
+  };
+
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+  const int kt_begin = k_min / PRE_TILE, kt_end = p_last / PRE_TILE + 1;
+  // the key range this warp's 16 rows can see
+  const int w_pmin = sp + t0 + sub * 16, w_pmax = min(w_pmin + 15, p_last);
+  const int w_kmin = (window > 0 && w_pmin - window + 1 > 0) ? w_pmin - window + 1 : 0;
+
+  load_tile(kt_begin, 0);
+  cp_async_commit();
+  int stage = 0;
+  for (int kt = kt_begin; kt < kt_end; ++kt, stage ^= 1) {
+    if (kt + 1 < kt_end) load_tile(kt + 1, stage ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const int key_base = kt * PRE_TILE;
+    if (active && key_base <= w_pmax && key_base + PRE_TILE - 1 >= w_kmin) {
+      const __nv_bfloat16* ktile = smem + (size_t)(stage * 2) * TILE_ELEMS;
+      const __nv_bfloat16* vtile = ktile + TILE_ELEMS;
+      float s[PRE_TILE / 8][4];
+#pragma unroll
+      for (int i = 0; i < PRE_TILE / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+      qk_tile<HD, PRE_TILE / 8>(s, qa, ktile, lane);
+#pragma unroll
+      for (int nt = 0; nt < PRE_TILE / 8; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = key_base + nt * 8 + c0 + (e & 1);
+          const int pr = (e >> 1) ? pr1 : pr0;
+          const bool ok = key <= pr && (window <= 0 || key > pr - window);
+          s[nt][e] = ok ? s[nt][e] * scale_log2 : -INFINITY;
+        }
+      }
+      softmax_step<HD, PRE_TILE / 8>(s, m, l, o);
+      pv_tile<HD, PRE_TILE / 8>(o, s, vtile, lane);
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  if (!active) return;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int tl = r ? tl1 : tl0;
+    if (tl >= n_tok) continue;
+    const float inv = 1.f / l[r];
+    __nv_bfloat16* orow = out + ((size_t)(tok0 + tl) * nh + h) * HD;
+#pragma unroll
+    for (int nt = 0; nt < HD / 8; ++nt) {
+      *reinterpret_cast<uint32_t*>(orow + nt * 8 + c0) =
+          pack_bf16(o[nt][2 * r] * inv, o[nt][2 * r + 1] * inv);
+    }
+  }
+}
+
+template <int HD>
+int launch_decode(void* out, float* part_o, float* part_ml, const void* q, int q_stride,
+                  const void* k_pages, const void* v_pages, const int* block_table, int bt_stride,
+                  const int* positions, int S, int nh, int nkv, int page_size, int window,
+                  float scale, int n_splits, cudaStream_t stream) {
+  constexpr int RS = HD + 8;
+  size_t smem = (size_t)DEC_WARPS * 4 * DEC_TILE * RS * sizeof(__nv_bfloat16);
+  const size_t red = (size_t)DEC_WARPS * 16 * (HD + 2) * sizeof(float);
+  if (red > smem) smem = red;
+  auto kernel = decode_attention_kernel<HD>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    return HB_LAUNCH_FAILED;
+  dim3 grid(n_splits, nkv, S);
+  kernel<<<grid, DEC_WARPS * 32, smem, stream>>>(
+      (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, q_stride,
+      (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, bt_stride,
+      positions, nh, nkv, page_size, window, scale * LOG2E, n_splits);
+  if (n_splits > 1)
+    decode_merge_kernel<HD><<<S * nh, HD < 128 ? HD : 128, 0, stream>>>(
+        (__nv_bfloat16*)out, part_o, part_ml, n_splits);
+  return hb_check_launch();
+}
+
+template <int HD>
+int launch_prefill(void* out, const void* q, int q_stride, const void* k_pages, const void* v_pages,
+                   const int* block_table, int bt_stride, const int* q_tiles, int n_tiles,
+                   const int* cu_tokens, const int* start_pos, int nh, int nkv, int heads_per_block,
+                   int token_subtiles, int page_size, int window, float scale, cudaStream_t stream) {
+  constexpr int RS = HD + 8;
+  const size_t smem = (size_t)4 * PRE_TILE * RS * sizeof(__nv_bfloat16);
+  auto kernel = prefill_attention_kernel<HD>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    return HB_LAUNCH_FAILED;
+  const int G = nh / nkv;
+  const int head_blocks = (G + heads_per_block - 1) / heads_per_block;
+  dim3 grid(n_tiles, nkv * head_blocks);
+  kernel<<<grid, PRE_WARPS * 32, smem, stream>>>(
+      (__nv_bfloat16*)out, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pages,
+      (const __nv_bfloat16*)v_pages, block_table, bt_stride, q_tiles, cu_tokens, start_pos, nh, nkv,
+      heads_per_block, token_subtiles, page_size, window, scale * LOG2E);
+  return hb_check_launch();
+}
+
+}  // namespace
+
+#define HB_DISPATCH_HD(hd, ...)                         \
+  switch (hd) {                                         \
+    case 32: { constexpr int HD = 32; __VA_ARGS__; }    \
+    case 64: { constexpr int HD = 64; __VA_ARGS__; }    \
+    case 96: { constexpr int HD = 96; __VA_ARGS__; }    \
+    case 128: { constexpr int HD = 128; __VA_ARGS__; }  \
+    default: return HB_BAD_ARGUMENT;                    \
+  }
+
+// Decode: S requests, one token each (token i belongs to request i).  Needs the group
+// size nh / nkv <= 16.  part_o: float [S, nh, n_splits, hd], part_ml: float
+// [S, nh, n_splits, 2]; both unused when n_splits == 1.
+HB_EXPORT int hb_attention_decode_bf16(void* out, float* part_o, float* part_ml, const void* q,
+                                       int q_stride, const void* k_pages, const void* v_pages,
+                                       const int* block_table, int bt_stride, const int* positions,
+                                       int S, int nh, int nkv, int hd, int page_size, int window,
+                                       float scale, int n_splits, cudaStream_t stream) {
+  if (S <= 0) return HB_OK;
+  if (nkv <= 0 || nh % nkv != 0 || nh / nkv > 16 || page_size <= 0 || n_splits < 1)
+    return HB_BAD_ARGUMENT;
+  HB_DISPATCH_HD(hd, return launch_decode<HD>(out, part_o, part_ml, q, q_stride, k_pages, v_pages,
+                                              block_table, bt_stride, positions, S, nh, nkv,
+                                              page_size, window, scale, n_splits, stream));
+}
+
+// Prefill / mixed: q_tiles holds (request, first local token) for every tile of
+// 16 * token_subtiles query tokens; heads_per_block * token_subtiles <= 8.
+HB_EXPORT int hb_attention_prefill_bf16(void* out, const void* q, int q_stride, const void* k_pages,
+                                        const void* v_pages, const int* block_table, int bt_stride,
+                                        const int* q_tiles, int n_tiles, const int* cu_tokens,
+                                        const int* start_pos, int nh, int nkv, int hd,
+                                        int heads_per_block, int token_subtiles, int page_size,
+                                        int window, float scale, cudaStream_t stream) {
+  if (n_tiles <= 0) return HB_OK;
+  if (nkv <= 0 || nh % nkv != 0 || page_size <= 0 || heads_per_block < 1 || token_subtiles < 1 ||
+      heads_per_block * token_subtiles > PRE_WARPS)
+    return HB_BAD_ARGUMENT;
+  HB_DISPATCH_HD(hd, return launch_prefill<HD>(out, q, q_stride, k_pages, v_pages, block_table,
+                                               bt_stride, q_tiles, n_tiles, cu_tokens, start_pos,
+                                               nh, nkv, heads_per_block, token_subtiles, page_size,
+                                               window, scale, stream));
+}

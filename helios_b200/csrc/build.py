@@ -32,6 +32,7 @@ _SRC_DIR = Path(__file__).resolve().parent
 LIBRARIES: Dict[str, str] = {
     "elementwise": "elementwise.cu",
     "attention_generic": "attention_generic.cu",
+    "attention_bf16": "attention_bf16.cu",
     "gemm_f32": "gemm_f32.cu",
     "sampling": "sampling.cu",
 }

@@ -306,10 +306,130 @@ def linear_logits(rows: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     return torch.mm(rows, weight.t(), out_dtype=torch.float32)
 
 
+TILED_HEAD_DIMS = (32, 64, 96, 128)
+_SM_COUNT = 148
+
+
+def decode_splits(num_seqs: int, num_kv_heads: int, max_context: int) -> int:
+    """Slices of the context per (request, KV head): enough blocks for two per SM, but
+    at least 256 keys a slice."""
+    blocks = max(1, num_seqs * num_kv_heads)
+    want = -(-2 * _SM_COUNT // blocks)
+    most = max(1, max_context // 256)
+    return max(1, min(want, most, 32))
+
+
+def attention_decode_bf16(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                          block_table: torch.Tensor, positions: torch.Tensor, num_heads: int,
+                          num_kv_heads: int, head_dim: int, page_size: int,
+                          window: Optional[int], scale: float, n_splits: int) -> torch.Tensor:
+    """Decode attention (token i is the one new token of request i) on the tensor cores;
+    bfloat16, head_dim in TILED_HEAD_DIMS, at most 16 query heads per KV head."""
+    _check(qkv, "qkv", torch.bfloat16, 2)
+    _check(k_pages, "k_pages", torch.bfloat16, 4)
+    _check(v_pages, "v_pages", torch.bfloat16, 4)
+    _check(block_table, "block_table", torch.int32, 2)
+    _check(positions, "positions", torch.int32, 1)
+    if head_dim not in TILED_HEAD_DIMS:
+        raise KernelError(f"head_dim {head_dim} is not one of {TILED_HEAD_DIMS}")
+    if num_heads % num_kv_heads or num_heads // num_kv_heads > 16:
+        raise KernelError(f"{num_heads} query heads on {num_kv_heads} KV heads: the decode kernel "
+                          "takes groups of at most 16")
+    if tuple(k_pages.shape[1:]) != (num_kv_heads, page_size, head_dim) or k_pages.shape != v_pages.shape:
+        raise KernelError(f"cache pages have shape {tuple(k_pages.shape)}, expected "
+                          f"[pages, {num_kv_heads}, {page_size}, {head_dim}]")
+    S = qkv.shape[0]
+    if block_table.shape[0] != S or positions.numel() != S:
+        raise KernelError("decode attention needs one token per request")
+    out = torch.empty((S, num_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
+    part_o = part_ml = None
+    if n_splits > 1:
+        part_o = torch.empty((S, num_heads, n_splits, head_dim), dtype=torch.float32, device=qkv.device)
+        part_ml = torch.empty((S, num_heads, n_splits, 2), dtype=torch.float32, device=qkv.device)
+    f = _fn("attention_bf16", "hb_attention_decode_bf16",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+    _run(f(_p(out), _p(part_o), _p(part_ml), _p(qkv), qkv.shape[1], _p(k_pages), _p(v_pages),
+           _p(block_table), block_table.shape[1], _p(positions), S, num_heads, num_kv_heads,
+           head_dim, page_size, int(window or 0), float(scale), int(n_splits), _stream()),
+         "attention_decode_bf16")
+    return out
+
+
+def prefill_tiling(num_heads: int, num_kv_heads: int):
+    """(query heads per block, 16-token sub-tiles per block) of the prefill kernel."""
+    group = num_heads // num_kv_heads
+    heads = min(group, 8)
+    return heads, max(1, 8 // heads)
+
+
+def attention_prefill_bf16(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                           block_table: torch.Tensor, q_tiles: torch.Tensor,
+                           cu_tokens: torch.Tensor, start_pos: torch.Tensor, num_heads: int,
+                           num_kv_heads: int, head_dim: int, page_size: int,
+                           window: Optional[int], scale: float) -> torch.Tensor:
+    """Attention of query-token tiles over the cache, causal by position; ``q_tiles`` is
+    int32 [tiles, 2] = (request, first local token) for tiles of
+    ``16 * prefill_tiling(...)[1]`` tokens."""
+    _check(qkv, "qkv", torch.bfloat16, 2)
+    _check(k_pages, "k_pages", torch.bfloat16, 4)
+    _check(v_pages, "v_pages", torch.bfloat16, 4)
+    _check(block_table, "block_table", torch.int32, 2)
+    _check(q_tiles, "q_tiles", torch.int32, 2)
+    _check(cu_tokens, "cu_tokens", torch.int32, 1)
+    _check(start_pos, "start_pos", torch.int32, 1)
+    if head_dim not in TILED_HEAD_DIMS:
+        raise KernelError(f"head_dim {head_dim} is not one of {TILED_HEAD_DIMS}")
+    if num_heads % num_kv_heads:
+        raise KernelError(f"{num_heads} query heads are not a multiple of {num_kv_heads} KV heads")
+    if tuple(k_pages.shape[1:]) != (num_kv_heads, page_size, head_dim) or k_pages.shape != v_pages.shape:
+        raise KernelError(f"cache pages have shape {tuple(k_pages.shape)}, expected "
+                          f"[pages, {num_kv_heads}, {page_size}, {head_dim}]")
+    heads, subtiles = prefill_tiling(num_heads, num_kv_heads)
+    T = qkv.shape[0]
+    out = torch.empty((T, num_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
+    f = _fn("attention_bf16", "hb_attention_prefill_bf16",
+            [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _run(f(_p(out), _p(qkv), qkv.shape[1], _p(k_pages), _p(v_pages), _p(block_table),
+           block_table.shape[1], _p(q_tiles), q_tiles.shape[0], _p(cu_tokens), _p(start_pos),
+           num_heads, num_kv_heads, head_dim, heads, subtiles, page_size, int(window or 0),
+           float(scale), _stream()), "attention_prefill_bf16")
+    return out
+
+
+def query_tiles(tokens_per_seq, tile: int, device) -> torch.Tensor:
+    """int32 [tiles, 2] on ``device``: (request, first local token) of every tile."""
+    rows = [(i, t0) for i, n in enumerate(tokens_per_seq) for t0 in range(0, n, tile)]
+    host = torch.tensor(rows, dtype=torch.int32).reshape(-1, 2)
+    if torch.device(device).type == "cuda":
+        host = host.pin_memory()
+    return host.to(device, non_blocking=True)
+
+
 def attention(ctx, qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
               block_table: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
               page_size: int, window: Optional[int], scale: float) -> torch.Tensor:
     """Attention of the step's tokens over the cache; chooses the kernel by dtype, sizes
-    and the shape of the batch described by ``ctx``."""
+    and the shape of the batch described by ``ctx``.  bfloat16 with a tiled head size
+    runs on the tensor cores (split-context decode kernel for batches of single tokens,
+    tiled kernel otherwise); everything else, and float32, on the generic kernel."""
+    if qkv.dtype == torch.bfloat16 and head_dim in TILED_HEAD_DIMS:
+        if ctx.decode_only and num_heads // num_kv_heads <= 16:
+            splits = ctx.extras.get("decode_splits")
+            if splits is None:
+                splits = decode_splits(ctx.num_seqs, num_kv_heads, ctx.max_context_len)
+            return attention_decode_bf16(qkv, k_pages, v_pages, block_table, ctx.positions,
+                                         num_heads, num_kv_heads, head_dim, page_size, window,
+                                         scale, splits)
+        _heads, subtiles = prefill_tiling(num_heads, num_kv_heads)
+        key = ("q_tiles", 16 * subtiles)
+        tiles = ctx.extras.get(key)
+        if tiles is None:
+            tiles = query_tiles([s.num_tokens for s in ctx.seqs], 16 * subtiles, qkv.device)
+            ctx.extras[key] = tiles
+        return attention_prefill_bf16(qkv, k_pages, v_pages, block_table, tiles, ctx.cu_tokens,
+                                      ctx.start_pos, num_heads, num_kv_heads, head_dim, page_size,
+                                      window, scale)
     return attention_generic(qkv, k_pages, v_pages, block_table, ctx.seq_of_token, ctx.positions,
                              num_heads, num_kv_heads, head_dim, page_size, window, scale)

@@ -62,8 +62,22 @@ TINY_WINDOW = {
     "sliding_window": 40, "use_sliding_window": True, "max_window_layers": 1,
     "hidden_act": "silu", "torch_dtype": "float32",
 }
-TINY_CONFIGS = {"tiny_llama": TINY_LLAMA, "tiny_qwen": TINY_QWEN, "tiny_window": TINY_WINDOW}
-TINY_SEEDS = {"tiny_llama": 11, "tiny_qwen": 22, "tiny_window": 33}
+# Head sizes the tensor-core attention kernels take (32), GQA 6/2, a window on every
+# second layer by an explicit layer_types list, other scaling constants.
+TINY_TILED = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "vocab_size": 270, "hidden_size": 96, "intermediate_size": 160, "num_hidden_layers": 3,
+    "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 32,
+    "max_position_embeddings": 2048, "rms_norm_eps": 2e-5, "rope_theta": 10000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 4.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 2.0, "original_max_position_embeddings": 32},
+    "attention_bias": False, "tie_word_embeddings": True, "hidden_act": "silu",
+    "sliding_window": 70, "layer_types": ["full_attention", "sliding_attention", "full_attention"],
+    "torch_dtype": "float32",
+}
+TINY_CONFIGS = {"tiny_llama": TINY_LLAMA, "tiny_qwen": TINY_QWEN, "tiny_window": TINY_WINDOW,
+                "tiny_tiled": TINY_TILED}
+TINY_SEEDS = {"tiny_llama": 11, "tiny_qwen": 22, "tiny_window": 33, "tiny_tiled": 44}
 
 # float32 path against the plain implementation in float64
 F32_ATOL = 2e-5

@@ -177,6 +177,7 @@ def forward_logits(cfg: dict, weights: Dict[str, torch.Tensor], token_ids: List[
         h = decoder_layer(cfg, w, i, h, positions, inv_freq, windows[i])
     h = rms_norm(h, w["model.norm.weight"], cfg.get("rms_norm_eps", 1e-5))
     head = w["lm_head.weight"] if "lm_head.weight" in w else w["model.embed_tokens.weight"]
+    assert "lm_head.weight" in w or cfg.get("tie_word_embeddings", False)
     return h @ head.T
 
 

@@ -33,7 +33,8 @@ def test_random_folder_round_trip(model_folders, name):
     assert set(tensors) == want
     assert all(t.dtype == torch.float32 for t in tensors.values())
     # seeded: the same again
-    again = random_tensors(_plan(cfg), {"tiny_llama": 11, "tiny_qwen": 22, "tiny_window": 33}[name])
+    from conftest import TINY_SEEDS
+    again = random_tensors(_plan(cfg), TINY_SEEDS[name])
     assert all(torch.equal(again[k], tensors[k]) for k in tensors)
     # norm weights around one, matrices around zero with std 0.02
     assert abs(float(tensors["model.norm.weight"].mean()) - 1.0) < 0.02
