@@ -130,7 +130,8 @@ __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&m)[2], f
 
 // ------------------------------------------------------------------------ decode
 constexpr int DEC_WARPS = 4;
-constexpr int DEC_TILE = 32;   // keys per warp tile
+constexpr int DEC_TILE = 16;    // keys per warp tile
+constexpr int DEC_STAGES = 3;   // tiles a warp keeps in shared memory (two in flight)
 
 template <int HD>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
@@ -176,22 +177,31 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     }
   }
 
-  __nv_bfloat16* my = smem + (size_t)warp * 4 * TILE_ELEMS;   // [stage][k|v][tile]
+  __nv_bfloat16* my = smem + (size_t)warp * DEC_STAGES * 2 * TILE_ELEMS;   // [stage][k|v][tile]
+  // A tile is DEC_TILE rows of HD/8 16-byte chunks.  Lane r first finds the cache row of
+  // key r (its page and slot); then consecutive lanes copy consecutive chunks, so a warp
+  // instruction reads 512 contiguous bytes.
   auto load_tile = [&](int tile, int stage) {
-    const int key = lo + tile * DEC_TILE + lane;
-    const bool valid = key < k_end;
-    size_t base = 0;
-    if (valid) {
-      const int page = table[key / page_size];
-      base = (((size_t)page * nkv + kvh) * page_size + key % page_size) * HD;
+    constexpr int CH = HD / 8;
+    int row_id = -1;
+    if (lane < DEC_TILE) {
+      const int key = lo + tile * DEC_TILE + lane;
+      if (key < k_end) {
+        const int page = table[key / page_size];
+        row_id = (page * nkv + kvh) * page_size + key % page_size;
+      }
     }
-    __nv_bfloat16* kd = my + (size_t)(stage * 2) * TILE_ELEMS + lane * RS;
+    __nv_bfloat16* kd = my + (size_t)(stage * 2) * TILE_ELEMS;
     __nv_bfloat16* vd = kd + TILE_ELEMS;
-    const int bytes = valid ? 16 : 0;
 #pragma unroll
-    for (int c = 0; c < HD / 8; ++c) {
-      cp_async16(kd + c * 8, k_pages + base + c * 8, bytes);
-      cp_async16(vd + c * 8, v_pages + base + c * 8, bytes);
+    for (int it = 0; it < DEC_TILE * CH / 32; ++it) {
+      const int idx = it * 32 + lane;
+      const int row = idx / CH, c = idx - row * CH;
+      const int rid = __shfl_sync(0xffffffffu, row_id, row);
+      const size_t base = (size_t)(rid < 0 ? 0 : rid) * HD + c * 8;
+      const int bytes = rid < 0 ? 0 : 16;
+      cp_async16(kd + row * RS + c * 8, k_pages + base, bytes);
+      cp_async16(vd + row * RS + c * 8, v_pages + base, bytes);
     }
   };
 
@@ -200,14 +210,21 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
   for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
+  // prologue: DEC_STAGES - 1 tiles in flight
   int tile = tile_begin + warp;
-  if (tile < tile_end) load_tile(tile, 0);
-  cp_async_commit();
-  int stage = 0;
-  for (; tile < tile_end; tile += DEC_WARPS, stage ^= 1) {
-    if (tile + DEC_WARPS < tile_end) load_tile(tile + DEC_WARPS, stage ^ 1);
+#pragma unroll
+  for (int p = 0; p < DEC_STAGES - 1; ++p) {
+    if (tile + p * DEC_WARPS < tile_end) load_tile(tile + p * DEC_WARPS, p);
     cp_async_commit();
-    cp_async_wait<1>();
+  }
+  int stage = 0;
+  for (; tile < tile_end; tile += DEC_WARPS) {
+    const int ahead = tile + (DEC_STAGES - 1) * DEC_WARPS;
+    int put = stage + DEC_STAGES - 1;
+    if (put >= DEC_STAGES) put -= DEC_STAGES;
+    if (ahead < tile_end) load_tile(ahead, put);
+    cp_async_commit();
+    cp_async_wait<DEC_STAGES - 1>();
     __syncwarp();
     const __nv_bfloat16* kt = my + (size_t)(stage * 2) * TILE_ELEMS;
     const __nv_bfloat16* vt = kt + TILE_ELEMS;
@@ -227,6 +244,7 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     softmax_step<HD, DEC_TILE / 8>(s, m, l, o);
     pv_tile<HD, DEC_TILE / 8>(o, s, vt, lane);
     __syncwarp();
+    if (++stage == DEC_STAGES) stage = 0;
   }
   cp_async_wait<0>();
 #pragma unroll
@@ -442,7 +460,7 @@ int launch_decode(void* out, float* part_o, float* part_ml, const void* q, int q
                   const int* positions, int S, int nh, int nkv, int page_size, int window,
                   float scale, int n_splits, cudaStream_t stream) {
   constexpr int RS = HD + 8;
-  size_t smem = (size_t)DEC_WARPS * 4 * DEC_TILE * RS * sizeof(__nv_bfloat16);
+  size_t smem = (size_t)DEC_WARPS * DEC_STAGES * 2 * DEC_TILE * RS * sizeof(__nv_bfloat16);
   const size_t red = (size_t)DEC_WARPS * 16 * (HD + 2) * sizeof(float);
   if (red > smem) smem = red;
   auto kernel = decode_attention_kernel<HD>;

@@ -34,6 +34,7 @@ LIBRARIES: Dict[str, str] = {
     "attention_generic": "attention_generic.cu",
     "attention_bf16": "attention_bf16.cu",
     "gemm_f32": "gemm_f32.cu",
+    "gemm_bf16": "gemm_bf16.cu",
     "sampling": "sampling.cu",
 }
 _HEADERS = ["common.cuh"]

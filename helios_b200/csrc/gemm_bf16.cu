@@ -1,0 +1,496 @@
+// bfloat16 matrix products y = x W^T on the 5th-generation tensor cores:
+// tcgen05.mma (cta_group::1, kind::f16, float32 accumulators in tensor memory),
+// operands staged in shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle)
+// through an mbarrier ring, accumulators read back with tcgen05.ld for the epilogue.
+// (python/helios/exec/model.py:236-238, 250-251, 336-337, 493-496 are the products; the
+// reference runs them in a library.)
+//
+// One kernel, two orientations:
+//   * tokens on the 128-row MMA M axis, output features on N (prefill);
+//   * "swapped" for few tokens (decode): 128 output features on the M axis, the tokens
+//     on a narrow N axis, so that a step streams every weight once at full width; the
+//     K range can be split over several blocks, whose partial sums the last block to
+//     finish adds in a fixed order (scratch memory + a ticket per tile).
+// Epilogues: + bias, bfloat16 or float32 out; or SwiGLU, where the block accumulates the
+// gate tile and the up tile of the same feature range side by side and writes
+// silu(gate) * up.
+//
+// One thread issues TMA, one issues MMA, four warps run the epilogue.  Every wait on an
+// mbarrier is bounded: when it runs out the block raises an error word in global
+// memory, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;          // rows of the A-side tile = MMA M
+constexpr int BK = 64;           // 64 bfloat16 = 128 bytes = one swizzle span
+constexpr int UMMA_K = 16;
+constexpr int GEMM_THREADS = 192;  // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-5: epilogue
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+enum { EPI_STORE = 0, EPI_GLU = 1 };
+
+struct GemmArgs {
+  void* out;            // [T, ldo] bfloat16 or float32
+  const float* bias;    // [N] or null
+  float* scratch;       // partial sums when the K range is split
+  int* tickets;         // one per output tile, zero between launches
+  int* error;           // set non-zero when a wait ran out
+  int T, N, K;          // tokens, output features (for GLU: of the result, = half the weight rows), reduction
+  int ldo;
+  int glu_offset;       // GLU: row of the weight where the second half ("up") begins
+  int out_f32;
+  int k_splits;
+};
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when it gave up (or another role already did).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* error, int code) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (i > 32) {
+      __nanosleep(64);
+      if (*abort_flag) return false;
+    }
+  }
+  *abort_flag = 1;
+  atomicCAS(error, 0, code);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols));
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols));
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t addr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(addr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory operand descriptor: K-major tile of 128-byte rows, 128-byte swizzle, groups
+// of 8 rows 1024 bytes apart; version 1 (sm_100).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3FFF);
+  d |= (uint64_t)1 << 16;              // leading byte offset: not used by swizzled K-major
+  d |= (uint64_t)(1024 >> 4) << 32;    // stride byte offset
+  d |= (uint64_t)1 << 46;              // descriptor version
+  d |= (uint64_t)2 << 61;              // SWIZZLE_128B
+  return d;
+}
+// kind::f16 instruction descriptor: float32 accumulate, bfloat16 A and B, both K-major.
+__host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+constexpr uint32_t pow2_cols(int n) { return n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : n <= 256 ? 256 : 512; }
+
+template <int BN, bool SWAP, int EPI>
+struct Config {
+  // A-side tiles per stage: two for the swapped SwiGLU (gate rows, up rows)
+  static constexpr int A_TILES = (SWAP && EPI == EPI_GLU) ? 2 : 1;
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_TILES * A_BYTES + B_BYTES;
+  static constexpr int STAGES_FIT = (196 * 1024) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
+  static constexpr int ACC_COLS = BN * A_TILES;            // float32 columns of tensor memory in use
+  static constexpr uint32_t TMEM_COLS = pow2_cols(ACC_COLS);
+  static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
+};
+
+// out feature / token of accumulator element (row r of the A-side tile, column c)
+template <int BN, bool SWAP, int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 GemmArgs args) {
+  using Cfg = Config<BN, SWAP, EPI>;
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* aligned = smem_raw + (base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + (size_t)Cfg::STAGES * Cfg::STAGE_BYTES);
+  // bars[0..S): full, bars[S..2S): empty, bars[2S]: accumulators ready
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * Cfg::STAGES + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* last_flag = const_cast<int*>(abort_flag) + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile_a = blockIdx.x, tile_b = blockIdx.y, split = blockIdx.z;
+  const int kb_total = (args.K + BK - 1) / BK;
+  const int kb_per = (kb_total + args.k_splits - 1) / args.k_splits;
+  const int kb_begin = split * kb_per;
+  const int kb_end = min(kb_total, kb_begin + kb_per);
+  const int n_kb = max(0, kb_end - kb_begin);
+
+  auto full_bar = [&](int s) { return smem_u32(bars + s); };
+  auto empty_bar = [&](int s) { return smem_u32(bars + Cfg::STAGES + s); };
+  const uint32_t acc_bar = smem_u32(bars + 2 * Cfg::STAGES);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(acc_bar, 1);
+    *abort_flag = 0;
+    *last_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // rows of the two operands this block reads
+  int a_row0, a_row1 = 0, b_row0, b_row1 = 0;
+  if (SWAP) {
+    a_row0 = tile_a * BM;                       // weight rows (features)
+    a_row1 = args.glu_offset + tile_a * BM;     // GLU: the up rows
+    b_row0 = tile_b * BN;                       // token rows
+  } else {
+    a_row0 = tile_a * BM;                       // token rows
+    if (EPI == EPI_GLU) {
+      b_row0 = tile_b * (BN / 2);               // gate rows
+      b_row1 = args.glu_offset + tile_b * (BN / 2);
+    } else {
+      b_row0 = tile_b * BN;
+    }
+  }
+
+  if (warp == 0) {
+   if (lane == 0) {
+    // ------------------------------------------------------------ TMA producer
+    for (int i = 0; i < n_kb; ++i) {
+      const int s = i % Cfg::STAGES;
+      const uint32_t ph = (i / Cfg::STAGES) & 1;
+      if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, args.error, 1)) break;
+      const uint32_t sa = base + s * Cfg::STAGE_BYTES;
+      const uint32_t sb = sa + Cfg::A_TILES * Cfg::A_BYTES;
+      mbar_expect_tx(full_bar(s), Cfg::STAGE_BYTES);
+      const int k0 = (kb_begin + i) * BK;
+      tma_load_2d(sa, &map_a, full_bar(s), k0, a_row0);
+      if (Cfg::A_TILES == 2) tma_load_2d(sa + Cfg::A_BYTES, &map_a, full_bar(s), k0, a_row1);
+      if (!SWAP && EPI == EPI_GLU) {
+        tma_load_2d(sb, &map_b, full_bar(s), k0, b_row0);
+        tma_load_2d(sb + Cfg::B_BYTES / 2, &map_b, full_bar(s), k0, b_row1);
+      } else {
+        tma_load_2d(sb, &map_b, full_bar(s), k0, b_row0);
+      }
+    }
+   }
+   __syncwarp();
+  } else if (warp == 1) {
+   if (lane == 0) {
+    // ------------------------------------------------------------ MMA issuer
+    constexpr uint32_t idesc = instr_desc(BM, BN);
+    bool ok = true;
+    for (int i = 0; i < n_kb && ok; ++i) {
+      const int s = i % Cfg::STAGES;
+      const uint32_t ph = (i / Cfg::STAGES) & 1;
+      ok = mbar_wait(full_bar(s), ph, abort_flag, args.error, 2);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t sa = base + s * Cfg::STAGE_BYTES;
+      const uint32_t sb = sa + Cfg::A_TILES * Cfg::A_BYTES;
+#pragma unroll
+      for (int k = 0; k < BK / UMMA_K; ++k) {
+        const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+        const uint64_t db = smem_desc(sb + k * UMMA_K * 2);
+        umma_bf16(tmem_base, smem_desc(sa + k * UMMA_K * 2), db, idesc, acc);
+        if (Cfg::A_TILES == 2)
+          umma_bf16(tmem_base + BN, smem_desc(sa + Cfg::A_BYTES + k * UMMA_K * 2), db, idesc, acc);
+      }
+      umma_commit(empty_bar(s));      // the stage is free once these MMAs have read it
+    }
+    umma_commit(acc_bar);             // accumulators complete
+   }
+   __syncwarp();
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;                  // the 32 lanes of tensor memory this warp may read
+    const int r = quarter * 32 + lane;             // row of the A-side tile
+    bool ok = true;
+    if (n_kb > 0) ok = mbar_wait(acc_bar, 0, abort_flag, args.error, 3);
+    if (*abort_flag) ok = false;
+    tc_fence_after();
+    const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const int tile_id = tile_b * gridDim.x + tile_a;
+    const size_t tile_elems = (size_t)BM * Cfg::ACC_COLS;
+    bool finalize = ok;
+    if (ok && args.k_splits > 1) {
+      // park the partial sums; the last block of the tile adds them up
+      float* mine = args.scratch + ((size_t)tile_id * args.k_splits + split) * tile_elems;
+      for (int c = 0; c < Cfg::ACC_COLS; c += 16) {
+        float v[16];
+        if (n_kb > 0) {
+          tmem_ld16(taddr + c, v);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) mine[(size_t)(c + j) * BM + r] = v[j];
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");        // the four epilogue warps
+      if (threadIdx.x == 64) {
+        const int ticket = atomicAdd(args.tickets + tile_id, 1);
+        const int last = (ticket == args.k_splits - 1) ? 1 : 0;
+        if (last) args.tickets[tile_id] = 0;                 // ready for the next launch
+        *last_flag = last;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      finalize = (*last_flag != 0);
+      if (finalize) __threadfence();
+    }
+    if (finalize) {
+      const float* parts = args.scratch + (size_t)tile_id * args.k_splits * tile_elems;
+      auto load_chunk = [&](int c, float (&v)[16]) {
+        if (args.k_splits > 1) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = 0.f;
+          for (int sp = 0; sp < args.k_splits; ++sp) {
+            const float* p = parts + (size_t)sp * tile_elems;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] += __ldcg(p + (size_t)(c + j) * BM + r);
+          }
+        } else if (n_kb > 0) {
+          tmem_ld16(taddr + c, v);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = 0.f;
+        }
+      };
+      auto store = [&](int t, int n, float val) {
+        if (t < args.T && n < args.N) {
+          if (args.bias) val += args.bias[n];
+          if (args.out_f32) reinterpret_cast<float*>(args.out)[(size_t)t * args.ldo + n] = val;
+          else reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)t * args.ldo + n] = __float2bfloat16_rn(val);
+        }
+      };
+      if (EPI == EPI_GLU) {
+        constexpr int HALF = SWAP ? BN : BN / 2;   // columns of the gate accumulator
+        for (int c = 0; c < HALF; c += 16) {
+          float g[16], u[16];
+          load_chunk(c, g);
+          load_chunk(HALF + c, u);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float val = g[j] / (1.f + __expf(-g[j])) * u[j];
+            if (SWAP) store(tile_b * BN + c + j, tile_a * BM + r, val);
+            else store(tile_a * BM + r, tile_b * HALF + c + j, val);
+          }
+        }
+      } else {
+        for (int c = 0; c < BN; c += 16) {
+          float v[16];
+          load_chunk(c, v);
+          if (SWAP) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) store(tile_b * BN + c + j, tile_a * BM + r, v[j]);
+          } else {
+            const int t = tile_a * BM + r, n0 = tile_b * BN + c;
+            if (!args.out_f32 && t < args.T && n0 + 16 <= args.N && (args.ldo & 7) == 0) {
+              // 16 bfloat16 of one row: two 16-byte stores
+              uint32_t packed[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                float lo = v[2 * j], hi = v[2 * j + 1];
+                if (args.bias) { lo += args.bias[n0 + 2 * j]; hi += args.bias[n0 + 2 * j + 1]; }
+                __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+                packed[j] = *reinterpret_cast<uint32_t*>(&p);
+              }
+              uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(args.out) + (size_t)t * args.ldo + n0);
+              dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+              dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) store(t, n0 + j, v[j]);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0) {
+    // copies of this block may still be in flight: give them time to land before the
+    // shared memory is handed to another block
+    for (int i = 0; i < 2000; ++i) __nanosleep(100);
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// [rows, k] bfloat16, row stride ld elements; box = box_rows x 64 elements, 128-byte swizzle,
+// zero fill outside the tensor.
+bool make_map(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t k, uint64_t ld, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[2] = {k, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {BK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, bool SWAP, int EPI>
+int launch(const void* x, const void* w, const GemmArgs& args, int w_rows, int ldx, int ldw,
+           cudaStream_t stream) {
+  using Cfg = Config<BN, SWAP, EPI>;
+  CUtensorMap map_a, map_b;
+  // box rows of the weight-side map: a full tile, or half of it for the two SwiGLU halves
+  if (SWAP) {
+    if (!make_map(&map_a, w, w_rows, args.K, ldw, BM)) return HB_LAUNCH_FAILED;
+    if (!make_map(&map_b, x, args.T, args.K, ldx, BN)) return HB_LAUNCH_FAILED;
+  } else {
+    if (!make_map(&map_a, x, args.T, args.K, ldx, BM)) return HB_LAUNCH_FAILED;
+    if (!make_map(&map_b, w, w_rows, args.K, ldw, EPI == EPI_GLU ? BN / 2 : BN)) return HB_LAUNCH_FAILED;
+  }
+  auto kernel = gemm_bf16_kernel<BN, SWAP, EPI>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM) != cudaSuccess)
+      return HB_LAUNCH_FAILED;
+    configured = true;
+  }
+  dim3 grid;
+  if (SWAP) {
+    grid = dim3((args.N + BM - 1) / BM, (args.T + BN - 1) / BN, args.k_splits);
+  } else {
+    const int per_tile = (EPI == EPI_GLU) ? BN / 2 : BN;
+    grid = dim3((args.T + BM - 1) / BM, (args.N + per_tile - 1) / per_tile, args.k_splits);
+  }
+  kernel<<<grid, GEMM_THREADS, Cfg::SMEM, stream>>>(map_a, map_b, args);
+  return hb_check_launch();
+}
+
+}  // namespace
+
+// Output tiles of a call (N counts the result's features), and the scratch floats it needs
+// (0 when the K range is not split).  swap_bn = 0: tiles of 128 tokens x 256 features (128
+// result features for SwiGLU); else 128 features x swap_bn tokens.
+HB_EXPORT int hb_gemm_bf16_tiles(int T, int N, int swap_bn, int glu) {
+  if (swap_bn == 0) {
+    const int per = glu ? 128 : 256;
+    return ((T + BM - 1) / BM) * ((N + per - 1) / per);
+  }
+  return ((N + BM - 1) / BM) * ((T + swap_bn - 1) / swap_bn);
+}
+HB_EXPORT long long hb_gemm_bf16_scratch_floats(int T, int N, int swap_bn, int glu, int k_splits) {
+  if (k_splits <= 1) return 0;
+  const long long cols = swap_bn == 0 ? 256 : (long long)swap_bn * (glu ? 2 : 1);
+  return (long long)hb_gemm_bf16_tiles(T, N, swap_bn, glu) * k_splits * BM * cols;
+}
+
+// y[T, N] = x[T, K] w[N, K]^T (+ bias), or SwiGLU over w = [gate rows; up rows] with the up
+// rows starting at row glu_offset (then N counts the result's features).
+//   swap_bn = 0: tokens on the M axis (tile 128 x 256).  swap_bn in {16, 32, 64, 128}: swapped,
+//   that many tokens per tile.  With k_splits > 1 scratch and tickets are needed.
+HB_EXPORT int hb_gemm_bf16(void* out, const void* x, const void* w, const float* bias, float* scratch,
+                           int* tickets, int* error, int T, int N, int K, int ldx, int ldw, int ldo,
+                           int w_rows, int glu, int glu_offset, int out_f32, int swap_bn, int k_splits,
+                           cudaStream_t stream) {
+  if (T <= 0 || N <= 0) return HB_OK;
+  if (K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || k_splits < 1) return HB_BAD_ARGUMENT;
+  if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return HB_BAD_ARGUMENT;
+  if (k_splits > 1 && (scratch == nullptr || tickets == nullptr)) return HB_BAD_ARGUMENT;
+  if (k_splits > (K + BK - 1) / BK) return HB_BAD_ARGUMENT;
+  if (error == nullptr) return HB_BAD_ARGUMENT;
+  GemmArgs a;
+  a.out = out; a.bias = bias; a.scratch = scratch; a.tickets = tickets; a.error = error;
+  a.T = T; a.N = N; a.K = K; a.ldo = ldo; a.glu_offset = glu_offset; a.out_f32 = out_f32;
+  a.k_splits = k_splits;
+#define HB_GEMM_CASE(BN_, SWAP_)                                                              \
+  return glu ? launch<BN_, SWAP_, EPI_GLU>(x, w, a, w_rows, ldx, ldw, stream)                 \
+             : launch<BN_, SWAP_, EPI_STORE>(x, w, a, w_rows, ldx, ldw, stream)
+  switch (swap_bn) {
+    case 0: HB_GEMM_CASE(256, false);
+    case 16: HB_GEMM_CASE(16, true);
+    case 32: HB_GEMM_CASE(32, true);
+    case 64: HB_GEMM_CASE(64, true);
+    case 128: HB_GEMM_CASE(128, true);
+    default: return HB_BAD_ARGUMENT;
+  }
+#undef HB_GEMM_CASE
+}

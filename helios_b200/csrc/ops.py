@@ -251,16 +251,135 @@ def linear_f32(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tenso
     return out
 
 
+# Fixed work space of the tensor-core products on a device: partial sums of split
+# reductions, one ticket per output tile (zero between launches), and an error word
+# that a kernel sets when one of its bounded waits ran out.  Its addresses never
+# change, so captured CUDA graphs stay valid.
+_GEMM_SCRATCH_FLOATS = 16 * 1024 * 1024
+_GEMM_TICKETS = 1 << 16
+_gemm_ws = {}
+
+
+def _gemm_workspace(device):
+    ws = _gemm_ws.get(device)
+    if ws is None:
+        ws = (torch.empty(_GEMM_SCRATCH_FLOATS, dtype=torch.float32, device=device),
+              torch.zeros(_GEMM_TICKETS, dtype=torch.int32, device=device),
+              torch.zeros(1, dtype=torch.int32, device=device))
+        _gemm_ws[device] = ws
+    return ws
+
+
+def check_kernel_errors(device=None) -> None:
+    """Raise if a kernel of this package gave up a bounded wait (synchronises)."""
+    for dev, (_s, _t, err) in _gemm_ws.items():
+        if device is not None and dev != torch.device(device):
+            continue
+        code = int(err.item())
+        if code:
+            err.zero_()
+            role = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue"}.get(code, "a role")
+            raise KernelError(f"gemm_bf16: {role} gave up waiting on an mbarrier (code {code}); "
+                              "the results of that launch are not valid")
+
+
+def gemm_plan(T: int, N: int, K: int, glu: bool):
+    """(swap_bn, k_splits) of the tensor-core product for T tokens, N result features."""
+    k_blocks = -(-K // 64)
+    if T <= 128:
+        bn = 16 if T <= 16 else 32 if T <= 32 else 64 if T <= 64 else 128
+    else:
+        bn = 0
+    if bn:
+        tiles = -(-N // 128) * -(-T // bn)
+        cols = bn * (2 if glu else 1)
+    else:
+        tiles = -(-T // 128) * -(-N // (128 if glu else 256))
+        cols = 256
+    splits = 1
+    if tiles < _SM_COUNT:
+        splits = max(1, min(_SM_COUNT // tiles, k_blocks // 4, 16))
+        while splits > 1 and tiles * splits * 128 * cols > _GEMM_SCRATCH_FLOATS:
+            splits -= 1
+    return bn, splits
+
+
+def tc_gemm_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 2
+            and weight.dim() == 2 and x.shape[1] == weight.shape[1] and x.shape[1] % 8 == 0
+            and x.is_contiguous() and weight.is_contiguous()
+            and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                glu: bool = False, out_dtype: torch.dtype = torch.bfloat16,
+                plan=None) -> torch.Tensor:
+    """y = x W^T (+ bias) on tcgen05 tensor cores; bfloat16 operands, float32 accumulate.
+
+    With ``glu`` the weight is [gate rows; up rows] ([2 I, K]) and the result is
+    silu(x gate^T) * (x up^T), [T, I].  ``out_dtype`` bfloat16 or float32.  K must be a
+    multiple of 8 (TMA rows are 16-byte aligned); any T and N."""
+    _check(x, "x", torch.bfloat16, 2)
+    _check(weight, "weight", torch.bfloat16, 2)
+    T, K = x.shape
+    rows, K2 = weight.shape
+    if K != K2:
+        raise KernelError(f"x has {K} columns but weight has {K2}")
+    if K % 8:
+        raise KernelError(f"the tensor-core product needs K to be a multiple of 8, got {K}")
+    if glu and rows % 2:
+        raise KernelError("a SwiGLU weight needs an even number of rows")
+    N = rows // 2 if glu else rows
+    if bias is not None:
+        if glu:
+            raise KernelError("the SwiGLU epilogue takes no bias")
+        _check(bias, "bias", torch.float32, 1)
+        if bias.numel() != N:
+            raise KernelError(f"bias has {bias.numel()} entries for {N} outputs")
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError(f"out_dtype {out_dtype} is not supported")
+    out = torch.empty((T, N), dtype=out_dtype, device=x.device)
+    if T == 0:
+        return out
+    bn, splits = plan if plan is not None else gemm_plan(T, N, K, glu)
+    scratch, tickets, err = _gemm_workspace(x.device)
+    lib = load_library("gemm_bf16")
+    if splits > 1:
+        lib.hb_gemm_bf16_scratch_floats.restype = ctypes.c_longlong
+        need = lib.hb_gemm_bf16_scratch_floats(T, N, bn, int(glu), splits)
+        tiles = lib.hb_gemm_bf16_tiles(T, N, bn, int(glu))
+        if need > scratch.numel() or tiles > tickets.numel():
+            raise KernelError(f"split reduction needs {need} scratch floats and {tiles} tickets; "
+                              f"the work space holds {scratch.numel()} and {tickets.numel()}")
+    f = _fn("gemm_bf16", "hb_gemm_bf16",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _run(f(_p(out), _p(x), _p(weight), _p(bias), _p(scratch), _p(tickets), _p(err), T, N, K, K, K, N,
+           rows, int(glu), N if glu else 0, 1 if out_dtype == torch.float32 else 0, bn, splits,
+           _stream()), "gemm_bf16")
+    return out
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """y = x W^T + b.  float32: this package's FMA kernel.  bfloat16: the library product
-    (cuBLAS through torch), as the reference engine uses one for its projections
-    (python/helios/exec/model.py:170-181)."""
+    """y = x W^T + b.  float32: this package's FMA kernel.  bfloat16: the tcgen05 kernel;
+    a K that is no multiple of 8 goes to the library product (cuBLAS through torch), as the
+    reference engine uses one for all its projections (python/helios/exec/model.py:170-181)."""
     if x.dtype == torch.float32:
         return linear_f32(x, weight, bias)
     _check(x, "x", torch.bfloat16, 2)
     _check(weight, "weight", torch.bfloat16, 2)
+    if tc_gemm_supported(x, weight):
+        return linear_bf16(x, weight, bias)
     b = None if bias is None else bias.to(torch.bfloat16)
     return torch.nn.functional.linear(x, weight, b)
+
+
+def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(x gate^T) * (x up^T) for ``w_gate_up`` = [gate rows; up rows]; fused into the
+    product's epilogue in bfloat16, two kernels otherwise."""
+    if x.dtype == torch.bfloat16 and tc_gemm_supported(x, w_gate_up):
+        return linear_bf16(x, w_gate_up, glu=True)
+    return silu_mul(linear(x, w_gate_up))
 
 
 # ------------------------------------------------------------------ sampling
@@ -303,6 +422,8 @@ def linear_logits(rows: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
         return linear_f32(rows, weight, None)
     _check(rows, "rows", torch.bfloat16, 2)
     _check(weight, "weight", torch.bfloat16, 2)
+    if tc_gemm_supported(rows, weight):
+        return linear_bf16(rows, weight, out_dtype=torch.float32)
     return torch.mm(rows, weight.t(), out_dtype=torch.float32)
 
 

@@ -29,7 +29,7 @@ class SwiGLU(FeedForward):
         self.w_down = tensors["down_proj.weight"].contiguous()
 
     def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
-        return ops.linear(ops.silu_mul(ops.linear(x, self.w_gate_up)), self.w_down)
+        return ops.linear(ops.linear_swiglu(x, self.w_gate_up), self.w_down)
 
 
 register_part("feed_forward", "swiglu", SwiGLU)

@@ -1,0 +1,93 @@
+"""The tcgen05 matrix product alone, against float64, over both orientations, split
+reductions, the SwiGLU epilogue, float32 output and ragged sizes."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def ops():
+    from helios_b200.csrc import ops as _ops
+    return _ops
+
+
+def _case(T, N, K, seed, glu=False):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn((2 * N if glu else N), K, generator=g) / K ** 0.5).to(torch.bfloat16)
+    b = torch.randn(N, generator=g)
+    return x, w, b
+
+
+def _close(got, want, scale=1.0):
+    torch.testing.assert_close(got.double().cpu(), want, atol=2e-2 * scale, rtol=2e-2)
+
+
+@pytest.mark.parametrize("T", [1, 8, 16, 17, 40, 64, 100, 128, 129, 300, 1000])
+@pytest.mark.parametrize("N,K", [(128, 64), (200, 72), (384, 4096), (1000, 520), (4096, 1024)])
+def test_plain_and_bias(T, N, K):
+    x, w, b = _case(T, N, K, T + N)
+    want = x.double() @ w.double().T
+    _close(ops().linear_bf16(x.to(DEV), w.to(DEV)), want)
+    _close(ops().linear_bf16(x.to(DEV), w.to(DEV), b.to(DEV)), want + b.double())
+    got32 = ops().linear_bf16(x.to(DEV), w.to(DEV), out_dtype=torch.float32)
+    assert got32.dtype == torch.float32
+    torch.testing.assert_close(got32.double().cpu(), want, atol=2e-3, rtol=1e-3)
+    ops().check_kernel_errors()
+
+
+@pytest.mark.parametrize("bn", [0, 16, 32, 64, 128])
+@pytest.mark.parametrize("splits", [1, 2, 5])
+@pytest.mark.parametrize("glu", [False, True])
+def test_every_orientation_and_split(bn, splits, glu):
+    T = {0: 260, 16: 9, 32: 32, 64: 50, 128: 128}[bn]
+    N, K = 392, 1024 + 64 * 3
+    x, w, b = _case(T, N, K, bn + splits, glu)
+    xd, wd = x.double(), w.double()
+    if glu:
+        gate, up = xd @ wd[:N].T, xd @ wd[N:].T
+        want = gate * torch.sigmoid(gate) * up
+        got = ops().linear_bf16(x.to(DEV), w.to(DEV), glu=True, plan=(bn, splits))
+    else:
+        want = xd @ wd.T + b.double()
+        got = ops().linear_bf16(x.to(DEV), w.to(DEV), b.to(DEV), plan=(bn, splits))
+    _close(got, want)
+    ops().check_kernel_errors()
+
+
+def test_split_sum_is_the_same_every_time_and_tickets_return_to_zero():
+    x, w, _ = _case(8, 4096, 14336, 3)
+    xd, wd = x.to(DEV), w.to(DEV)
+    first = ops().linear_bf16(xd, wd, plan=(16, 7))
+    for _ in range(5):
+        assert torch.equal(ops().linear_bf16(xd, wd, plan=(16, 7)), first)
+    _, tickets, _ = ops()._gemm_workspace(torch.device(DEV))
+    assert int(tickets.abs().sum()) == 0
+    _close(first, x.double() @ w.double().T)
+    ops().check_kernel_errors()
+
+
+@pytest.mark.parametrize("T", [3, 64, 2048])
+def test_model_sized_products(T):
+    # the shapes of the 8B model's layer: fused QKV, output, gate/up with SwiGLU, down
+    for N, K, glu in [(6144, 4096, False), (4096, 4096, False), (14336, 4096, True), (4096, 14336, False)]:
+        x, w, _ = _case(T, N, K, T + N, glu)
+        xd, wd = x.double(), w.double()
+        if glu:
+            gate, up = xd @ wd[:N].T, xd @ wd[N:].T
+            want = gate * torch.sigmoid(gate) * up
+            got = ops().linear_swiglu(x.to(DEV), w.to(DEV))
+        else:
+            want = xd @ wd.T
+            got = ops().linear(x.to(DEV), w.to(DEV))
+        _close(got, want)
+    ops().check_kernel_errors()
+
+
+def test_k_that_is_no_multiple_of_8_goes_to_the_library_and_is_refused_by_the_kernel():
+    x, w, _ = _case(5, 64, 100, 1)
+    got = ops().linear(x.to(DEV), w.to(DEV))
+    _close(got, x.double() @ w.double().T)
+    with pytest.raises(ops().KernelError):
+        ops().linear_bf16(x.to(DEV), w.to(DEV))
