@@ -73,7 +73,8 @@ class KVCacheManager(CacheLayout):
             counts[g] += 1
         self.storage: List[torch.Tensor] = []
         for g, spec in enumerate(specs):
-            shape = (counts[g], 2, num_pages[g], spec.num_kv_heads, page_size, spec.head_dim)
+            # one page more than the pool hands out: padding rows of captured graphs write there
+            shape = (counts[g], 2, num_pages[g] + 1, spec.num_kv_heads, page_size, spec.head_dim)
             t = torch.empty(shape, dtype=dtype, device=self.device)
             t.fill_(poison) if poison is not None else t.zero_()
             self.storage.append(t)
@@ -86,6 +87,8 @@ class KVCacheManager(CacheLayout):
                 self.states[entry] = torch.zeros((max_slots,) + tuple(spec.shape),
                                                  dtype=spec.dtype, device=self.device)
         self._views: Dict[int, LayerCache] = {}
+        #: per group, the id of the spare page no request ever gets
+        self.pad_pages: List[int] = list(num_pages)
 
     # ------------------------------------------------------------------ views
     def layer_cache(self, entry: int) -> Optional[LayerCache]:

@@ -65,23 +65,44 @@ def _align4(n: int) -> int:
     return (n + 3) & ~3
 
 
-def build_context(entries: Sequence[StepEntry], cache, act_dtype: torch.dtype,
-                  device: torch.device, table_width: Optional[List[int]] = None) -> StepContext:
-    """``cache`` is the cache manager: it knows every request's length, slot and block
-    tables (pages for the new tokens must have been taken already)."""
-    S = len(entries)
-    T = sum(len(e.tokens) for e in entries)
-    n_groups = len(cache.groups)
+class MetaLayout:
+    """Where each integer array of a step lies in the one int32 buffer that is copied to
+    the device: token ids, positions, request of each token, cumulative tokens, first
+    position, context length and slot of each request, wanted rows, and one block table
+    [requests, width] per cache group."""
+
+    def __init__(self, num_seqs: int, num_tokens: int, num_wanted: int, table_widths: List[int]) -> None:
+        self.S, self.T, self.R = num_seqs, num_tokens, num_wanted
+        self.widths = list(table_widths)
+        sizes = [num_tokens, num_tokens, num_tokens, num_seqs + 1, num_seqs, num_seqs, num_seqs,
+                 num_wanted] + [num_seqs * w for w in self.widths]
+        self.sizes = sizes
+        self.offsets, total = [], 0
+        for n in sizes:
+            self.offsets.append(total)
+            total += _align4(n)
+        self.total = max(total, 4)
+
+    def host_views(self, host: np.ndarray) -> List[np.ndarray]:
+        return [host[o:o + n] for o, n in zip(self.offsets, self.sizes)]
+
+    def device_views(self, dev: torch.Tensor) -> List[torch.Tensor]:
+        return [dev[o:o + n] for o, n in zip(self.offsets, self.sizes)]
+
+
+def fill_meta(layout: MetaLayout, host: np.ndarray, entries: Sequence[StepEntry], cache,
+              pad_page: Optional[List[int]] = None) -> List[SeqSlice]:
+    """Write the step's arrays into ``host`` (int32, ``layout.total`` long).  Requests
+    beyond ``len(entries)`` up to ``layout.S`` are padding: one token at position 0 whose
+    keys and values go to the spare page ``pad_page[group]`` that no request ever gets."""
+    v = layout.host_views(host)
+    token_ids, positions, seq_of_token, cu, start, ctx_len, slots, want = v[:8]
+    tables = [t.reshape(layout.S, w) for t, w in zip(v[8:], layout.widths)]
+    for t in tables:
+        t.fill(-1)
     seqs: List[SeqSlice] = []
-    token_ids = np.empty(T, np.int32)
-    positions = np.empty(T, np.int32)
-    seq_of_token = np.empty(T, np.int32)
-    cu = np.zeros(S + 1, np.int32)
-    start = np.empty(S, np.int32)
-    ctx_len = np.empty(S, np.int32)
-    slots = np.empty(S, np.int32)
-    want: List[int] = []
-    off = 0
+    off, nw = 0, 0
+    cu[0] = 0
     for i, e in enumerate(entries):
         n = len(e.tokens)
         p0 = cache.length(e.request_id)
@@ -90,42 +111,52 @@ def build_context(entries: Sequence[StepEntry], cache, act_dtype: torch.dtype,
         positions[off:off + n] = np.arange(p0, p0 + n, dtype=np.int32)
         seq_of_token[off:off + n] = i
         start[i], ctx_len[i], slots[i] = p0, p0 + n, seqs[-1].slot
-        want.extend(off + int(w) for w in e.want)
+        for w in e.want:
+            want[nw] = off + int(w)
+            nw += 1
         off += n
         cu[i + 1] = off
-    want_rows = np.asarray(want, np.int32)
-    tables = []
-    for g in range(n_groups):
-        width = max([len(cache.table(e.request_id, g)) for e in entries] + [1])
-        if table_width is not None:
-            width = max(width, table_width[g])
-        t = np.full((S, width), -1, np.int32)
-        for i, e in enumerate(entries):
+        for g, t in enumerate(tables):
             row = cache.table(e.request_id, g)
             t[i, :len(row)] = row
-        tables.append(t)
+    for i in range(len(entries), layout.S):          # padding requests (captured graphs)
+        token_ids[off], positions[off], seq_of_token[off] = 0, 0, i
+        start[i], ctx_len[i], slots[i] = 0, 1, 0
+        want[nw] = off
+        nw += 1
+        off += 1
+        cu[i + 1] = off
+        for g, t in enumerate(tables):
+            t[i, 0] = pad_page[g]
+    return seqs
 
-    arrays = [token_ids, positions, seq_of_token, cu, start, ctx_len, slots, want_rows] + \
-             [t.reshape(-1) for t in tables]
-    offsets, total = [], 0
-    for a in arrays:
-        offsets.append(total)
-        total += _align4(a.size)
-    host = torch.empty(max(total, 4), dtype=torch.int32, pin_memory=(device.type == "cuda"))
-    hv = host.numpy()
-    for a, o in zip(arrays, offsets):
-        hv[o:o + a.size] = a
-    dev = host.to(device, non_blocking=True)
 
-    def view(i):
-        return dev[offsets[i]:offsets[i] + arrays[i].size]
-
-    n_max = max((len(e.tokens) for e in entries), default=0)
+def context_from_views(layout: MetaLayout, dev: torch.Tensor, seqs: List[SeqSlice],
+                       act_dtype: torch.dtype, device: torch.device, max_tokens_per_seq: int,
+                       max_context_len: int) -> StepContext:
+    v = layout.device_views(dev)
     return StepContext(
-        act_dtype=act_dtype, device=device, num_tokens=T, num_seqs=S, num_wanted=len(want),
-        seqs=seqs, token_ids=view(0), positions=view(1), seq_of_token=view(2), cu_tokens=view(3),
-        start_pos=view(4), context_len=view(5), slots=view(6), want_rows=view(7),
-        block_tables=[view(8 + g).view(S, tables[g].shape[1]) for g in range(n_groups)],
-        decode_only=(n_max == 1), max_tokens_per_seq=n_max,
-        max_context_len=int(ctx_len.max()) if S else 0,
-    )
+        act_dtype=act_dtype, device=device, num_tokens=layout.T, num_seqs=layout.S,
+        num_wanted=layout.R, seqs=seqs, token_ids=v[0], positions=v[1], seq_of_token=v[2],
+        cu_tokens=v[3], start_pos=v[4], context_len=v[5], slots=v[6], want_rows=v[7],
+        block_tables=[t.view(layout.S, w) for t, w in zip(v[8:], layout.widths)],
+        decode_only=(max_tokens_per_seq == 1), max_tokens_per_seq=max_tokens_per_seq,
+        max_context_len=max_context_len)
+
+
+def build_context(entries: Sequence[StepEntry], cache, act_dtype: torch.dtype,
+                  device: torch.device) -> StepContext:
+    """``cache`` is the cache manager: it knows every request's length, slot and block
+    tables (pages for the new tokens must have been taken already)."""
+    S = len(entries)
+    T = sum(len(e.tokens) for e in entries)
+    R = sum(len(e.want) for e in entries)
+    widths = [max([len(cache.table(e.request_id, g)) for e in entries] + [1])
+              for g in range(len(cache.groups))]
+    layout = MetaLayout(S, T, R, widths)
+    host = torch.empty(layout.total, dtype=torch.int32, pin_memory=(device.type == "cuda"))
+    seqs = fill_meta(layout, host.numpy(), entries, cache)
+    dev = host.to(device, non_blocking=True)
+    n_max = max((len(e.tokens) for e in entries), default=0)
+    max_ctx = max((s.start_pos + s.num_tokens for s in seqs), default=0)
+    return context_from_views(layout, dev, seqs, act_dtype, device, n_max, max_ctx)

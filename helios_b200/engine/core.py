@@ -8,14 +8,58 @@ from typing import Hashable, List, Optional, Sequence
 import torch
 
 from ..cache.manager import KVCacheManager, bytes_per_page
-from .batch import StepEntry, build_context
+from .batch import MetaLayout, StepEntry, build_context, context_from_views, fill_meta
 from .model import DecoderModel
+
+
+class _DecodeGraph:
+    """A captured decode step for a fixed number of requests (padded) and fixed block-table
+    widths: static inputs, one CUDA graph, static logits."""
+
+    def __init__(self, core: "EngineCore", bucket: int) -> None:
+        cache, model = core.cache, core.model
+        self.bucket = bucket
+        self.layout = MetaLayout(bucket, bucket, bucket, core.graph_table_widths)
+        self.host = torch.empty(self.layout.total, dtype=torch.int32, pin_memory=True)
+        self.dev = torch.zeros(self.layout.total, dtype=torch.int32, device=model.device)
+        self.ctx = context_from_views(self.layout, self.dev, [], model.dtype, model.device, 1,
+                                      core.graph_max_context)
+        from ..csrc import ops
+        self.ctx.extras["decode_splits"] = ops.decode_splits(
+            bucket, max(s.num_kv_heads for s in cache.specs) if cache.specs else 1,
+            core.graph_max_context)
+        self.graph = None
+        self.logits = None
+        self.launches = 0
+        self.copied = torch.cuda.Event()
+
+    def fill(self, entries, cache) -> None:
+        self.copied.synchronize()        # the staging buffer is free again
+        self.ctx.seqs = fill_meta(self.layout, self.host.numpy(), entries, cache, cache.pad_pages)
+        self.dev.copy_(self.host, non_blocking=True)
+        self.copied.record()
+
+    def capture(self, core: "EngineCore") -> None:
+        from ..csrc import ops
+        before = ops.launch_count
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.logits = core.model.forward(self.ctx, core.cache)
+        self.launches = ops.launch_count - before
+        ops.launch_count = before
+        self.graph = graph
+
+    def replay(self) -> torch.Tensor:
+        from ..csrc import ops
+        self.graph.replay()
+        ops.launch_count += self.launches
+        return self.logits
 
 
 class EngineCore:
     def __init__(self, model: DecoderModel, page_size: int, num_pages, max_slots: int,
                  watermark: float = 0.0, max_model_len: Optional[int] = None,
-                 poison_cache: Optional[float] = None) -> None:
+                 poison_cache: Optional[float] = None, use_cuda_graphs: bool = True) -> None:
         self.model = model
         self.cache = KVCacheManager(model.plan, page_size, num_pages, max_slots, model.dtype,
                                     model.device, watermark=watermark, poison=poison_cache)
@@ -23,6 +67,14 @@ class EngineCore:
         self.vocab_size = model.plan.embedding.vocab
         self.steps_run = 0
         self.tokens_run = 0
+        # decode steps (one token per request) run as captured CUDA graphs, one per
+        # padded batch size; a size is captured the second time it is seen
+        self.use_cuda_graphs = bool(use_cuda_graphs) and model.plan.graph_safe
+        pool_tokens = max(p.num_pages for p in self.cache.pools) * page_size if self.cache.pools else 0
+        self.graph_max_context = min(max_model_len or pool_tokens, pool_tokens) or 1
+        self.graph_table_widths = [-(-self.graph_max_context // page_size)] * len(self.cache.groups)
+        self._graphs = {}
+        self._bucket_seen = {}
 
     @staticmethod
     def pages_for_bytes(model: DecoderModel, page_size: int, kv_cache_bytes: int) -> int:
@@ -82,11 +134,43 @@ class EngineCore:
                 if any(self.cache.pages_needed(e.request_id, len(e.tokens))):
                     raise ValueError(f"request {e.request_id!r} has no pages for its "
                                      f"{len(e.tokens)} new tokens")
-        ctx = build_context(entries, self.cache, self.model.dtype, self.model.device)
-        logits = self.model.forward(ctx, self.cache)
+        logits = None
+        if self.use_cuda_graphs and all(len(e.tokens) == 1 for e in entries):
+            logits = self._graph_step(entries)
+        if logits is None:
+            ctx = build_context(entries, self.cache, self.model.dtype, self.model.device)
+            logits = self.model.forward(ctx, self.cache)
         if manage_cache:
             for e in entries:
                 self.cache.commit(e.request_id, len(e.tokens))
         self.steps_run += 1
-        self.tokens_run += ctx.num_tokens
+        self.tokens_run += sum(len(e.tokens) for e in entries)
         return logits
+
+    # ------------------------------------------------------------------ captured decode steps
+    def _graph_step(self, entries) -> Optional[torch.Tensor]:
+        S = len(entries)
+        bucket = 1
+        while bucket < S:
+            bucket *= 2
+        if any(self.cache.length(e.request_id) + 1 > self.graph_max_context for e in entries):
+            return None
+        g = self._graphs.get(bucket)
+        if g is None:
+            seen = self._bucket_seen.get(bucket, 0)
+            self._bucket_seen[bucket] = seen + 1
+            if seen == 0:
+                return None                    # first time: run eagerly (also warms everything up)
+            g = _DecodeGraph(self, bucket)
+            g.fill(entries, self.cache)
+            torch.cuda.synchronize(self.model.device)
+            g.capture(self)
+            self._graphs[bucket] = g
+        g.fill(entries, self.cache)
+        logits = g.replay()
+        if all(len(e.want) == 1 for e in entries):
+            return logits[:S]
+        rows = [i for i, e in enumerate(entries) if e.want]
+        if not rows:
+            return None
+        return logits.index_select(0, torch.tensor(rows, device=logits.device))

@@ -58,7 +58,8 @@ class LLMEngine:
         self.max_model_len = max_len
         self.num_blocks = num_pages
         self.core = EngineCore(self.model, config.block_size, num_pages, config.max_num_seqs,
-                               watermark=config.watermark, max_model_len=max_len)
+                               watermark=config.watermark, max_model_len=max_len,
+                               use_cuda_graphs=config.use_cuda_graphs)
         self.scheduler = Scheduler(
             SchedulerConfig(max_num_seqs=config.max_num_seqs,
                             max_num_batched_tokens=config.max_num_batched_tokens,
