@@ -142,8 +142,12 @@ struct Config {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_TILES * A_BYTES + B_BYTES;
-  static constexpr int STAGES_FIT = (196 * 1024) / STAGE_BYTES;
-  static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
+  // swapped (decode): two blocks per SM, each with about 108 KB of stages; otherwise one
+  // block per SM with 196 KB
+  static constexpr int BUDGET = SWAP ? 108 * 1024 : 196 * 1024;
+  static constexpr int STAGES_FIT = BUDGET / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_FIT > 8 ? 8 : (STAGES_FIT < 2 ? 2 : STAGES_FIT);
+  static constexpr int MIN_BLOCKS = SWAP ? 2 : 1;
   static constexpr int ACC_COLS = BN * A_TILES;            // float32 columns of tensor memory in use
   static constexpr uint32_t TMEM_COLS = pow2_cols(ACC_COLS);
   static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
@@ -151,7 +155,7 @@ struct Config {
 
 // out feature / token of accumulator element (row r of the A-side tile, column c)
 template <int BN, bool SWAP, int EPI>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(GEMM_THREADS, Config<BN, SWAP, EPI>::MIN_BLOCKS)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  GemmArgs args) {
   using Cfg = Config<BN, SWAP, EPI>;

@@ -284,21 +284,23 @@ def check_kernel_errors(device=None) -> None:
 
 
 def gemm_plan(T: int, N: int, K: int, glu: bool):
-    """(swap_bn, k_splits) of the tensor-core product for T tokens, N result features."""
+    """(swap_bn, k_splits) of the tensor-core product for T tokens, N result features.
+    Up to 128 tokens run swapped (features on the MMA M axis) with the reduction split so
+    that the blocks fill the SMs (two resident per SM, at least 8 k-blocks a slice)."""
     k_blocks = -(-K // 64)
     if T <= 128:
         bn = 16 if T <= 16 else 32 if T <= 32 else 64 if T <= 64 else 128
-    else:
-        bn = 0
-    if bn:
         tiles = -(-N // 128) * -(-T // bn)
         cols = bn * (2 if glu else 1)
+        slots = 2 * _SM_COUNT
     else:
+        bn = 0
         tiles = -(-T // 128) * -(-N // (128 if glu else 256))
         cols = 256
+        slots = _SM_COUNT
     splits = 1
-    if tiles < _SM_COUNT:
-        splits = max(1, min(_SM_COUNT // tiles, k_blocks // 4, 16))
+    if tiles < slots:
+        splits = _wave_splits(tiles, slots, max(1, min(16, k_blocks // 8)))
         while splits > 1 and tiles * splits * 128 * cols > _GEMM_SCRATCH_FLOATS:
             splits -= 1
     return bn, splits
@@ -431,13 +433,26 @@ TILED_HEAD_DIMS = (32, 64, 96, 128)
 _SM_COUNT = 148
 
 
+def _wave_splits(blocks: int, slots: int, most: int) -> int:
+    """Number of slices per block so that blocks * slices fills ``slots`` resident blocks
+    as evenly as possible: the largest count that still fits one round, or, when even one
+    slice per block overflows it, the count with the fullest last round."""
+    if blocks >= slots:
+        best, best_eff = 1, 0.0
+        for s in range(1, most + 1):
+            total = blocks * s
+            eff = total / (-(-total // slots) * slots)
+            if eff > best_eff + 0.03:
+                best, best_eff = s, eff
+        return best
+    return max(1, min(most, slots // blocks))
+
+
 def decode_splits(num_seqs: int, num_kv_heads: int, max_context: int) -> int:
-    """Slices of the context per (request, KV head): enough blocks for two per SM, but
-    at least 256 keys a slice."""
-    blocks = max(1, num_seqs * num_kv_heads)
-    want = -(-2 * _SM_COUNT // blocks)
-    most = max(1, max_context // 256)
-    return max(1, min(want, most, 32))
+    """Slices of the context per (request, KV head) of the decode attention kernel: two
+    blocks are resident per SM; a slice has at least 128 keys."""
+    return _wave_splits(max(1, num_seqs * num_kv_heads), 2 * _SM_COUNT,
+                        max(1, min(32, max_context // 128)))
 
 
 def attention_decode_bf16(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
