@@ -263,18 +263,27 @@ def main():
             max_num_batched_tokens=PREFILL_TOKENS, max_model_len=args.context + 8,
             num_blocks=args.batch * (args.context // page + 2) + 8, watermark=0.0), model=model)
         ctx0 = args.context - args.steps - args.warmup
+        # every request must still be decoding when the timed steps end, whenever its
+        # prompt was finished
         for b in range(args.batch):
-            engine.add_request(f"e{b}", tokens(ctx0), SamplingParams(max_tokens=args.steps + args.warmup + 4))
+            engine.add_request(f"e{b}", tokens(ctx0 - 64),
+                               SamplingParams(max_tokens=args.steps + args.warmup + 64))
         while any(s.num_pending_tokens > 1 for s in engine.scheduler.running) or engine.scheduler.waiting:
             engine.step()
         for _ in range(args.warmup):
             engine.step()
         torch.cuda.synchronize()
+        per_step = []
         w0 = time.perf_counter()
         for _ in range(args.steps):
+            s0 = time.perf_counter()
             engine.step()
+            per_step.append(time.perf_counter() - s0)
         torch.cuda.synchronize()
         wall = (time.perf_counter() - w0) / args.steps
+        if os.environ.get("HELIOS_BENCH_DEBUG"):
+            print("e2e per-step ms:", [round(x * 1e3, 2) for x in per_step], file=sys.stderr)
+            print("running:", len(engine.scheduler.running), engine.stats_snapshot(), file=sys.stderr)
         h2d = 4 * (args.batch * 8 + args.batch * (args.context // page + 1)) + args.batch * 28
         e2e = {"value": round(args.batch / wall, 1), "unit": "tokens/s",
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch}

@@ -142,6 +142,8 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
                         const int* __restrict__ block_table, int bt_stride,
                         const int* __restrict__ positions, int nh, int nkv, int page_size,
                         int window, float scale_log2, int n_splits) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int RS = HD + 8;
   constexpr int TILE_ELEMS = DEC_TILE * RS;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -306,6 +308,8 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
 template <int HD>
 __global__ void decode_merge_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o,
                                     const float* __restrict__ part_ml, int n_splits) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t row = blockIdx.x;   // seq * nh + head
   const float* ml = part_ml + row * n_splits * 2;
   float M = -INFINITY;
@@ -333,6 +337,8 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
                          const int* __restrict__ q_tiles, const int* __restrict__ cu_tokens,
                          const int* __restrict__ start_pos, int nh, int nkv, int heads_per_block,
                          int token_subtiles, int page_size, int window, float scale_log2) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int RS = HD + 8;
   constexpr int TILE_ELEMS = PRE_TILE * RS;
   constexpr int CHUNKS = HD / 8;
@@ -464,15 +470,19 @@ int launch_decode(void* out, float* part_o, float* part_ml, const void* q, int q
   const size_t red = (size_t)DEC_WARPS * 16 * (HD + 2) * sizeof(float);
   if (red > smem) smem = red;
   auto kernel = decode_attention_kernel<HD>;
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-    return HB_LAUNCH_FAILED;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return HB_LAUNCH_FAILED;
+    configured = true;
+  }
   dim3 grid(n_splits, nkv, S);
-  kernel<<<grid, DEC_WARPS * 32, smem, stream>>>(
+  hb_launch(kernel, dim3(grid), dim3(DEC_WARPS * 32), smem, stream, 
       (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, q_stride,
       (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, bt_stride,
       positions, nh, nkv, page_size, window, scale * LOG2E, n_splits);
   if (n_splits > 1)
-    decode_merge_kernel<HD><<<S * nh, HD < 128 ? HD : 128, 0, stream>>>(
+    hb_launch(decode_merge_kernel<HD>, dim3(S * nh), dim3(HD < 128 ? HD : 128), 0, stream, 
         (__nv_bfloat16*)out, part_o, part_ml, n_splits);
   return hb_check_launch();
 }
@@ -485,12 +495,16 @@ int launch_prefill(void* out, const void* q, int q_stride, const void* k_pages, 
   constexpr int RS = HD + 8;
   const size_t smem = (size_t)4 * PRE_TILE * RS * sizeof(__nv_bfloat16);
   auto kernel = prefill_attention_kernel<HD>;
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-    return HB_LAUNCH_FAILED;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return HB_LAUNCH_FAILED;
+    configured = true;
+  }
   const int G = nh / nkv;
   const int head_blocks = (G + heads_per_block - 1) / heads_per_block;
   dim3 grid(n_tiles, nkv * head_blocks);
-  kernel<<<grid, PRE_WARPS * 32, smem, stream>>>(
+  hb_launch(kernel, dim3(grid), dim3(PRE_WARPS * 32), smem, stream, 
       (__nv_bfloat16*)out, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pages,
       (const __nv_bfloat16*)v_pages, block_table, bt_stride, q_tiles, cu_tokens, start_pos, nh, nkv,
       heads_per_block, token_subtiles, page_size, window, scale * LOG2E);

@@ -21,6 +21,8 @@ __global__ void attention_generic_kernel(
     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ seq_of_token,
     const int* __restrict__ positions, int n_rows, int nh, int nkv, int hd, int page_size,
     int window, float scale) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float q_smem[ATTN_WARPS][ATTN_MAX_HD];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * ATTN_WARPS + warp;
@@ -93,7 +95,7 @@ HB_EXPORT int hb_attention_generic(void* out, const void* q, int q_stride, const
   const int n_rows = T * nh;
   const int blocks = (n_rows + ATTN_WARPS - 1) / ATTN_WARPS;
   HB_DISPATCH_DTYPE(act_dt, TA,
-    attention_generic_kernel<TA><<<blocks, ATTN_WARPS * 32, 0, stream>>>(
+    hb_launch(attention_generic_kernel<TA>, dim3(blocks), dim3(ATTN_WARPS * 32), 0, stream, 
         (TA*)out, (const TA*)q, q_stride, (const TA*)k_pages, (const TA*)v_pages, block_table,
         bt_stride, seq_of_token, positions, n_rows, nh, nkv, hd, page_size, window, scale));
   return hb_check_launch();

@@ -56,6 +56,43 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
   return scratch[32];
 }
 
+// Programmatic dependent launch: a kernel lets the next kernel of the stream start while it
+// still runs (launch_dependents) and itself waits for the kernel before it to finish, with
+// its writes visible, before touching anything that kernel may have written (wait).  What a
+// kernel does before its wait (set-up, fetching weights) overlaps the tail of its
+// predecessor.  Without the launch attribute both instructions do nothing.
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+#include <cstdlib>
+static inline bool hb_pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = std::getenv("HELIOS_B200_NO_PDL");
+    on = (e != nullptr && e[0] == '1') ? 0 : 1;
+  }
+  return on == 1;
+}
+
+// Launch with the programmatic-stream-serialization attribute (plain launch when disabled).
+template <typename... KArgs, typename... Args>
+static inline void hb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                             cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = hb_pdl_enabled() ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 static inline int hb_check_launch() {
   return cudaGetLastError() == cudaSuccess ? HB_OK : HB_LAUNCH_FAILED;
 }

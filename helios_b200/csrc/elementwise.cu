@@ -11,6 +11,8 @@
 template <typename T>
 __global__ void embedding_kernel(float* __restrict__ out, const T* __restrict__ table,
                                  const int* __restrict__ ids, int H, int V) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   int id = ids[t];
   if (id < 0 || id >= V) id = 0;  // ids are validated on the host
@@ -22,6 +24,8 @@ __global__ void embedding_kernel(float* __restrict__ out, const T* __restrict__ 
 // bfloat16 table, rows of whole 16-byte chunks: 8 values per thread and trip
 __global__ void embedding_bf16x8_kernel(float* __restrict__ out, const __nv_bfloat16* __restrict__ table,
                                         const int* __restrict__ ids, int H, int V) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   int id = ids[t];
   if (id < 0 || id >= V) id = 0;
@@ -39,11 +43,11 @@ HB_EXPORT int hb_embedding(float* out, const void* table, const int* ids, int T,
                            int table_dt, cudaStream_t stream) {
   if (T <= 0) return HB_OK;
   if (table_dt == HB_BF16 && H % 8 == 0 && (uintptr_t)table % 16 == 0 && (uintptr_t)out % 16 == 0) {
-    embedding_bf16x8_kernel<<<T, 256, 0, stream>>>(out, (const __nv_bfloat16*)table, ids, H, V);
+    hb_launch(embedding_bf16x8_kernel, dim3(T), dim3(256), 0, stream, out, (const __nv_bfloat16*)table, ids, H, V);
     return hb_check_launch();
   }
   HB_DISPATCH_DTYPE(table_dt, TT,
-    embedding_kernel<TT><<<T, 256, 0, stream>>>(out, (const TT*)table, ids, H, V));
+    hb_launch(embedding_kernel<TT>, dim3(T), dim3(256), 0, stream, out, (const TT*)table, ids, H, V));
   return hb_check_launch();
 }
 
@@ -88,6 +92,8 @@ template <typename TA, bool VEC>
 __global__ void __launch_bounds__(NORM_THREADS)
 add_rmsnorm_kernel(TA* __restrict__ out, float* __restrict__ residual, const TA* __restrict__ delta,
                    const float* __restrict__ weight, const int* __restrict__ rows, int H, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float scratch[33];
   const int i = blockIdx.x;
   const int r = rows ? rows[i] : i;
@@ -162,9 +168,9 @@ HB_EXPORT int hb_add_rmsnorm(void* out, float* residual, const void* delta, cons
                    ((uintptr_t)delta % 16 == 0) && ((uintptr_t)weight % 16 == 0) &&
                    (act_dt == HB_F32 || H % 8 == 0);
   HB_DISPATCH_DTYPE(act_dt, TA,
-    if (vec) add_rmsnorm_kernel<TA, true><<<n_out, NORM_THREADS, 0, stream>>>(
+    if (vec) hb_launch(add_rmsnorm_kernel<TA, true>, dim3(n_out), dim3(NORM_THREADS), 0, stream, 
         (TA*)out, residual, (const TA*)delta, weight, rows, H, eps);
-    else add_rmsnorm_kernel<TA, false><<<n_out, NORM_THREADS, 0, stream>>>(
+    else hb_launch(add_rmsnorm_kernel<TA, false>, dim3(n_out), dim3(NORM_THREADS), 0, stream, 
         (TA*)out, residual, (const TA*)delta, weight, rows, H, eps));
   return hb_check_launch();
 }
@@ -173,6 +179,8 @@ HB_EXPORT int hb_add_rmsnorm(void* out, float* residual, const void* delta, cons
 template <typename T>
 __global__ void rmsnorm_kernel(T* __restrict__ out, const T* __restrict__ x,
                                const float* __restrict__ weight, int H, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float scratch[33];
   const T* xr = x + (size_t)blockIdx.x * H;
   float ss = 0.f;
@@ -187,7 +195,7 @@ HB_EXPORT int hb_rmsnorm(void* out, const void* x, const float* weight, int n, i
                          int act_dt, cudaStream_t stream) {
   if (n <= 0) return HB_OK;
   HB_DISPATCH_DTYPE(act_dt, TA,
-    rmsnorm_kernel<TA><<<n, 256, 0, stream>>>((TA*)out, (const TA*)x, weight, H, eps));
+    hb_launch(rmsnorm_kernel<TA>, dim3(n), dim3(256), 0, stream, (TA*)out, (const TA*)x, weight, H, eps));
   return hb_check_launch();
 }
 
@@ -198,6 +206,8 @@ HB_EXPORT int hb_rmsnorm(void* out, const void* x, const float* weight, int n, i
 __global__ void rotary_table_kernel(float* __restrict__ cos_out, float* __restrict__ sin_out,
                                     const int* __restrict__ positions,
                                     const double* __restrict__ inv_freq, int T, int half) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= T * half) return;
   const int t = idx / half, j = idx - t * half;
@@ -211,7 +221,7 @@ HB_EXPORT int hb_rotary_table(float* cos_out, float* sin_out, const int* positio
                               const double* inv_freq, int T, int half, cudaStream_t stream) {
   if (T <= 0 || half <= 0) return HB_OK;
   const int total = T * half;
-  rotary_table_kernel<<<(total + 127) / 128, 128, 0, stream>>>(cos_out, sin_out, positions,
+  hb_launch(rotary_table_kernel, dim3((total + 127) / 128), dim3(128), 0, stream, cos_out, sin_out, positions,
                                                                inv_freq, T, half);
   return hb_check_launch();
 }
@@ -232,6 +242,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
                                      T* __restrict__ k_pages, T* __restrict__ v_pages,
                                      int nh, int nkv, int hd, int rot, int page_size,
                                      int write_cache) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int half = rot >> 1;
@@ -289,6 +301,8 @@ __global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, const float* __res
                                          const int* __restrict__ block_table, int bt_stride,
                                          T* __restrict__ k_pages, T* __restrict__ v_pages,
                                          int nh, int nkv, int hd, int page_size, int write_cache) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int item = blockIdx.y * blockDim.x + threadIdx.x;
   const int half = hd >> 1, quads = half >> 2;            // groups of 4 pairs per head
@@ -350,13 +364,13 @@ HB_EXPORT int hb_rope_kv_write(void* qkv, const float* cos_tab, const float* sin
     const int items = (nh + nkv) * (hd / 8) + (write_cache ? nkv * (hd / 8) : 0);
     dim3 grid(T, (items + 127) / 128);
     HB_DISPATCH_DTYPE(act_dt, TA,
-      rope_kv_write_vec_kernel<TA><<<grid, 128, 0, stream>>>(
+      hb_launch(rope_kv_write_vec_kernel<TA>, dim3(grid), dim3(128), 0, stream, 
           (TA*)qkv, cos_tab, sin_tab, positions, seq_of_token, block_table, bt_stride,
           (TA*)k_pages, (TA*)v_pages, nh, nkv, hd, page_size, write_cache));
     return hb_check_launch();
   }
   HB_DISPATCH_DTYPE(act_dt, TA,
-    rope_kv_write_kernel<TA><<<T, 256, 0, stream>>>(
+    hb_launch(rope_kv_write_kernel<TA>, dim3(T), dim3(256), 0, stream, 
         (TA*)qkv, cos_tab, sin_tab, positions, seq_of_token, block_table, bt_stride,
         (TA*)k_pages, (TA*)v_pages, nh, nkv, hd, rot, page_size, write_cache));
   return hb_check_launch();
@@ -366,6 +380,8 @@ HB_EXPORT int hb_rope_kv_write(void* qkv, const float* cos_tab, const float* sin
 // out[t, i] = silu(gu[t, i]) * gu[t, I + i]        python/helios/exec/model.py:336-337
 template <typename T>
 __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, size_t total, int I) {
+  pdl_launch_dependents();
+  pdl_wait();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / I;
@@ -384,6 +400,6 @@ HB_EXPORT int hb_silu_mul(void* out, const void* gate_up, int T, int I, int act_
   size_t blocks = (total + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;
   HB_DISPATCH_DTYPE(act_dt, TA,
-    silu_mul_kernel<TA><<<(unsigned)blocks, threads, 0, stream>>>((TA*)out, (const TA*)gate_up, total, I));
+    hb_launch(silu_mul_kernel<TA>, dim3((unsigned)blocks), dim3(threads), 0, stream, (TA*)out, (const TA*)gate_up, total, I));
   return hb_check_launch();
 }

@@ -22,6 +22,10 @@
 
 #include "common.cuh"
 
+#ifndef HB_SWAP_BUDGET_KB
+#define HB_SWAP_BUDGET_KB 72
+#endif
+
 namespace {
 
 constexpr int BM = 128;          // rows of the A-side tile = MMA M
@@ -142,12 +146,13 @@ struct Config {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_TILES * A_BYTES + B_BYTES;
-  // swapped (decode): two blocks per SM, each with about 108 KB of stages; otherwise one
-  // block per SM with 196 KB
-  static constexpr int BUDGET = SWAP ? 108 * 1024 : 196 * 1024;
+  // swapped (decode): about 72 KB of stages, so that three blocks fit an SM: grids are
+  // sized for two per SM and the blocks of the next kernel move in (and fetch their
+  // weights) while the last blocks of this one drain; otherwise one block per SM, 196 KB
+  static constexpr int BUDGET = SWAP ? HB_SWAP_BUDGET_KB * 1024 : 196 * 1024;
   static constexpr int STAGES_FIT = BUDGET / STAGE_BYTES;
   static constexpr int STAGES = STAGES_FIT > 8 ? 8 : (STAGES_FIT < 2 ? 2 : STAGES_FIT);
-  static constexpr int MIN_BLOCKS = SWAP ? 2 : 1;
+  static constexpr int MIN_BLOCKS = SWAP ? (HB_SWAP_BUDGET_KB <= 72 ? 3 : 2) : 1;
   static constexpr int ACC_COLS = BN * A_TILES;            // float32 columns of tensor memory in use
   static constexpr uint32_t TMEM_COLS = pow2_cols(ACC_COLS);
   static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
@@ -168,6 +173,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* last_flag = const_cast<int*>(abort_flag) + 1;
 
+  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile_a = blockIdx.x, tile_b = blockIdx.y, split = blockIdx.z;
   const int kb_total = (args.K + BK - 1) / BK;
@@ -218,22 +224,43 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   if (warp == 0) {
    if (lane == 0) {
     // ------------------------------------------------------------ TMA producer
-    for (int i = 0; i < n_kb; ++i) {
-      const int s = i % Cfg::STAGES;
-      const uint32_t ph = (i / Cfg::STAGES) & 1;
-      if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, args.error, 1)) break;
+    // The weights do not depend on the kernel before this one: their copies for the
+    // first stages start at once; the activations follow once that kernel is done.
+    auto load_weights = [&](int i, int s) {
       const uint32_t sa = base + s * Cfg::STAGE_BYTES;
       const uint32_t sb = sa + Cfg::A_TILES * Cfg::A_BYTES;
-      mbar_expect_tx(full_bar(s), Cfg::STAGE_BYTES);
       const int k0 = (kb_begin + i) * BK;
-      tma_load_2d(sa, &map_a, full_bar(s), k0, a_row0);
-      if (Cfg::A_TILES == 2) tma_load_2d(sa + Cfg::A_BYTES, &map_a, full_bar(s), k0, a_row1);
-      if (!SWAP && EPI == EPI_GLU) {
+      if (SWAP) {
+        tma_load_2d(sa, &map_a, full_bar(s), k0, a_row0);
+        if (Cfg::A_TILES == 2) tma_load_2d(sa + Cfg::A_BYTES, &map_a, full_bar(s), k0, a_row1);
+      } else if (EPI == EPI_GLU) {
         tma_load_2d(sb, &map_b, full_bar(s), k0, b_row0);
         tma_load_2d(sb + Cfg::B_BYTES / 2, &map_b, full_bar(s), k0, b_row1);
       } else {
         tma_load_2d(sb, &map_b, full_bar(s), k0, b_row0);
       }
+    };
+    auto load_activations = [&](int i, int s) {
+      const uint32_t sa = base + s * Cfg::STAGE_BYTES;
+      const uint32_t sb = sa + Cfg::A_TILES * Cfg::A_BYTES;
+      const int k0 = (kb_begin + i) * BK;
+      if (SWAP) tma_load_2d(sb, &map_b, full_bar(s), k0, b_row0);
+      else tma_load_2d(sa, &map_a, full_bar(s), k0, a_row0);
+    };
+    const int pre = n_kb < Cfg::STAGES ? n_kb : Cfg::STAGES;
+    for (int i = 0; i < pre; ++i) {
+      mbar_expect_tx(full_bar(i), Cfg::STAGE_BYTES);
+      load_weights(i, i);
+    }
+    pdl_wait();
+    for (int i = 0; i < pre; ++i) load_activations(i, i);
+    for (int i = pre; i < n_kb; ++i) {
+      const int s = i % Cfg::STAGES;
+      const uint32_t ph = (i / Cfg::STAGES) & 1;
+      if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, args.error, 1)) break;
+      mbar_expect_tx(full_bar(s), Cfg::STAGE_BYTES);
+      load_weights(i, s);
+      load_activations(i, s);
     }
    }
    __syncwarp();
@@ -265,6 +292,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
    __syncwarp();
   } else {
     // ------------------------------------------------------------ epilogue
+    pdl_wait();                                    // nothing is written before the kernel before is done
     const int quarter = warp & 3;                  // the 32 lanes of tensor memory this warp may read
     const int r = quarter * 32 + lane;             // row of the A-side tile
     bool ok = true;
@@ -445,7 +473,7 @@ int launch(const void* x, const void* w, const GemmArgs& args, int w_rows, int l
     const int per_tile = (EPI == EPI_GLU) ? BN / 2 : BN;
     grid = dim3((args.T + BM - 1) / BM, (args.N + per_tile - 1) / per_tile, args.k_splits);
   }
-  kernel<<<grid, GEMM_THREADS, Cfg::SMEM, stream>>>(map_a, map_b, args);
+  hb_launch(kernel, grid, dim3(GEMM_THREADS), Cfg::SMEM, stream, map_a, map_b, args);
   return hb_check_launch();
 }
 

@@ -10,6 +10,8 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(float* __restrict__ C, const float* __restrict__ A, const float* __restrict__ W,
                 const float* __restrict__ bias, int M, int N, int K, int lda, int ldw, int ldc) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -64,6 +66,6 @@ HB_EXPORT int hb_gemm_f32(float* C, const float* A, const float* W, const float*
   if (K <= 0) return HB_BAD_ARGUMENT;
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   if (grid.y > 65535) return HB_BAD_ARGUMENT;
-  gemm_f32_kernel<<<grid, 256, 0, stream>>>(C, A, W, bias, M, N, K, lda, ldw, ldc);
+  hb_launch(gemm_f32_kernel, dim3(grid), dim3(256), 0, stream, C, A, W, bias, M, N, K, lda, ldw, ldc);
   return hb_check_launch();
 }

@@ -43,6 +43,8 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int V, in
               const float* __restrict__ temperature, const int* __restrict__ top_k,
               const float* __restrict__ top_p, const unsigned long long* __restrict__ seed,
               const unsigned long long* __restrict__ offset) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float scratch[33];
   __shared__ float s_val[32];
   __shared__ int s_idx[32];
@@ -166,7 +168,7 @@ HB_EXPORT int hb_sample(int* out, const float* logits, int R, int V, int ld, con
                         const unsigned long long* offset, cudaStream_t stream) {
   if (R <= 0) return HB_OK;
   if (V <= 0) return HB_BAD_ARGUMENT;
-  sample_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(out, logits, V, ld, temperature, top_k, top_p,
+  hb_launch(sample_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, stream, out, logits, V, ld, temperature, top_k, top_p,
                                                   seed, offset);
   return hb_check_launch();
 }
