@@ -23,7 +23,7 @@
 #include "common.cuh"
 
 #ifndef HB_SWAP_BUDGET_KB
-#define HB_SWAP_BUDGET_KB 72
+#define HB_SWAP_BUDGET_KB 108
 #endif
 
 namespace {
