@@ -35,9 +35,12 @@ LIBRARIES: Dict[str, str] = {
     "attention_bf16": "attention_bf16.cu",
     "gemm_f32": "gemm_f32.cu",
     "gemm_bf16": "gemm_bf16.cu",
+    "gemm_bf16_noalloc": "gemm_bf16_noalloc.cu",
     "sampling": "sampling.cu",
 }
 _HEADERS = ["common.cuh"]
+# further files a library's source includes
+_INCLUDES: Dict[str, List[str]] = {"gemm_bf16_noalloc": ["gemm_bf16.cu", "gemm_bf16_noalloc.h"]}
 
 NVCC_FLAGS = [
     "-O3", "-std=c++17",
@@ -91,7 +94,7 @@ def build_dir() -> Path:
 
 def _digest(name: str, extra_flags: List[str]) -> str:
     h = hashlib.sha256()
-    for f in [LIBRARIES[name]] + _HEADERS:
+    for f in [LIBRARIES[name]] + _HEADERS + _INCLUDES.get(name, []):
         h.update(f.encode())
         h.update((_SRC_DIR / f).read_bytes())
     h.update(" ".join(NVCC_FLAGS + extra_flags).encode())

@@ -479,6 +479,7 @@ int launch(const void* x, const void* w, const GemmArgs& args, int w_rows, int l
 
 }  // namespace
 
+#ifndef HB_GEMM_BF16_NO_EXPORTS
 // Output tiles of a call (N counts the result's features), and the scratch floats it needs
 // (0 when the K range is not split).  swap_bn = 0: tiles of 128 tokens x 256 features (128
 // result features for SwiGLU); else 128 features x swap_bn tokens.
@@ -526,3 +527,4 @@ HB_EXPORT int hb_gemm_bf16(void* out, const void* x, const void* w, const float*
   }
 #undef HB_GEMM_CASE
 }
+#endif  // HB_GEMM_BF16_NO_EXPORTS
