@@ -1,0 +1,318 @@
+"""Each part of a layer alone against the plain function it stands for, and what the
+part interfaces promise: a model assembled from a list that names a layer twice or lets
+a layer read another layer's cache, and a toy mixer with state of its own, defined here,
+registered, built and stepped without touching the package's files."""
+import math
+
+import pytest
+import torch
+
+import plain_model
+from conftest import TINY_LLAMA, assert_logits_close, random_tokens
+from kernel_util import dense_attention, make_paged_case, step_ctx
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+
+
+def _ctx(entries_tokens, dtype, page_size=8, num_pages=64):
+    """A StepContext over fresh requests without a model: a bare cache layout."""
+    from helios_b200.cache import CacheLayout, GroupLayout
+    from helios_b200.engine.batch import StepEntry, build_context
+
+    lay = CacheLayout([GroupLayout(None, num_pages)], page_size, max_slots=8)
+    entries = []
+    for i, toks in enumerate(entries_tokens):
+        lay.admit(i)
+        lay.extend(i, len(toks))
+        entries.append(StepEntry(i, toks, list(range(len(toks)))))
+    return build_context(entries, lay, dtype, DEV), lay
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_part(dtype):
+    from helios_b200.parts import RMSNorm
+
+    g = torch.Generator().manual_seed(0)
+    norm = RMSNorm(200, 3e-6)
+    assert norm.weight_specs()["weight"].shape == (200,)
+    w = 1 + 0.1 * torch.randn(200, generator=g)
+    norm.bind({"weight": w.to(DEV)})
+    x = torch.randn(11, 200, generator=g).to(dtype)
+    tol = dict(atol=2e-6, rtol=2e-6) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(norm.forward(x.to(DEV)).cpu().double(),
+                               plain_model.rms_norm(x.double(), w.double(), 3e-6), **tol)
+
+
+def test_rotary_part_against_the_plain_tables():
+    from helios_b200.config import DenseDecoderConfig
+    from helios_b200.parts import RotaryEncoding
+
+    cfg = DenseDecoderConfig.from_hf(TINY_LLAMA)
+    rope = RotaryEncoding(cfg.head_dim, cfg.rope_theta, cfg.rope_scaling)
+    want = plain_model.rope_inv_freq(cfg.head_dim, TINY_LLAMA["rope_theta"], TINY_LLAMA["rope_scaling"])
+    torch.testing.assert_close(rope.inv_freq64, want, atol=0, rtol=1e-14)
+    ctx, _ = _ctx([[1, 2, 3], [4] * 70], torch.float32)
+    rope.prepare(ctx)
+    pos = torch.tensor([0, 1, 2] + list(range(70)), dtype=torch.float64)
+    torch.testing.assert_close(ctx.rotary_cos.cpu().double(), (pos[:, None] * want[None]).cos(), atol=1e-7, rtol=0)
+    assert ctx.rotary_sin.shape == (73, cfg.head_dim // 2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,bias,window", [(4, 2, 16, False, None), (6, 1, 32, True, 20), (5, 5, 48, True, None)])
+def test_attention_part_alone(dtype, nh, nkv, hd, bias, window):
+    """The mixer with its projections, rotation, cache write and attention, for two
+    requests in one batch, against the plain functions on whole sequences."""
+    from helios_b200.parts import GQAAttention, LayerCache, RotaryEncoding
+
+    H, page = 72, 8
+    g = torch.Generator().manual_seed(nh * hd)
+    attn = GQAAttention(H, nh, nkv, hd, 1 / math.sqrt(hd), bias, window=window)
+    specs = attn.weight_specs()
+    assert ("q_proj.bias" in specs) == bias
+    tensors = {k: torch.randn(s.shape, generator=g) * (0.1 if len(s.shape) == 2 else 0.5) for k, s in specs.items()}
+    if dtype == torch.bfloat16:
+        tensors = {k: (v.to(torch.bfloat16).float() if v.dim() == 2 else v) for k, v in tensors.items()}
+    attn.bind({k: v.to(DEV, dtype if v.dim() == 2 else torch.float32) for k, v in tensors.items()})
+    lens = [37, 5]
+    ctx, lay = _ctx([[0] * n for n in lens], dtype, page_size=page)
+    rope = RotaryEncoding(hd, 10000.0)
+    rope.prepare(ctx)
+    x = torch.randn(sum(lens), H, generator=g)
+    if dtype == torch.bfloat16:
+        x = x.to(torch.bfloat16).float()
+    spec = attn.cache_spec()
+    assert (spec.num_kv_heads, spec.head_dim, spec.window) == (nkv, hd, window)
+    k_pages = torch.full((64, nkv, page, hd), float("nan"), dtype=dtype, device=DEV)
+    cache = LayerCache(k_pages, k_pages.clone(), group=0, page_size=page)
+    out = attn.forward(ctx, x.to(DEV, dtype), cache, None)
+
+    t = {k: v.double() for k, v in tensors.items()}
+    want, off = [], 0
+    inv = plain_model.rope_inv_freq(hd, 10000.0, None)
+    for n in lens:
+        xs = x[off:off + n].double()
+        q = xs @ t["q_proj.weight"].T + (t["q_proj.bias"] if bias else 0)
+        k = xs @ t["k_proj.weight"].T + (t["k_proj.bias"] if bias else 0)
+        v = xs @ t["v_proj.weight"].T + (t["v_proj.bias"] if bias else 0)
+        pos = torch.arange(n)
+        q = plain_model.apply_rope(q.view(n, nh, hd), pos, inv)
+        k = plain_model.apply_rope(k.view(n, nkv, hd), pos, inv)
+        a = plain_model.causal_attention(q, k, v.view(n, nkv, hd), 1 / math.sqrt(hd), window)
+        want.append(a.reshape(n, nh * hd) @ t["o_proj.weight"].T)
+        off += n
+    tol = dict(atol=2e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=3e-2, rtol=3e-2)
+    torch.testing.assert_close(out.cpu().double(), torch.cat(want), **tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu_part_alone(dtype):
+    from helios_b200.parts import SwiGLU
+
+    g = torch.Generator().manual_seed(1)
+    ffn = SwiGLU(80, 176)
+    t = {k: torch.randn(s.shape, generator=g) * 0.1 for k, s in ffn.weight_specs().items()}
+    if dtype == torch.bfloat16:
+        t = {k: v.to(torch.bfloat16).float() for k, v in t.items()}
+    ffn.bind({k: v.to(DEV, dtype) for k, v in t.items()})
+    x = torch.randn(19, 80, generator=g).to(dtype)
+    want = plain_model.swiglu(x.double(), t["gate_proj.weight"].double(), t["up_proj.weight"].double(),
+                              t["down_proj.weight"].double())
+    tol = dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=3e-2)
+    torch.testing.assert_close(ffn.forward(None, x.to(DEV)).cpu().double(), want, **tol)
+
+
+def test_embedding_and_head_parts():
+    from helios_b200.parts import OutputHead, TokenEmbedding
+
+    g = torch.Generator().manual_seed(2)
+    table = torch.randn(331, 40, generator=g)
+    emb, head = TokenEmbedding(331, 40), OutputHead(331, 40)
+    emb.bind({"weight": table.to(DEV)})
+    head.bind({"weight": table.to(DEV)})
+    ctx, _ = _ctx([[5, 330, 0]], torch.float32)
+    torch.testing.assert_close(emb.forward(ctx).cpu(), table[[5, 330, 0]])
+    rows = torch.randn(4, 40, generator=g)
+    torch.testing.assert_close(head.forward(ctx, rows.to(DEV)).cpu().double(), rows.double() @ table.double().T,
+                               atol=1e-5, rtol=1e-5)
+
+
+# ---------------------------------------------------------------------- the schedule is data
+def _toy_plan(schedule, layers=2):
+    from helios_b200.config import DenseDecoderConfig
+    from helios_b200.models import build_dense_decoder_plan
+    from helios_b200.parts import Run
+
+    cfg = DenseDecoderConfig.from_hf(dict(TINY_LLAMA, num_hidden_layers=layers))
+    plan = build_dense_decoder_plan(cfg)
+    plan.schedule = [Run(*r) if isinstance(r, tuple) else Run(r) for r in schedule]
+    plan.__post_init__()
+    return cfg, plan
+
+
+def _run_plan(plan, toks, cut, dtype=torch.float32):
+    from helios_b200.engine.batch import StepEntry
+    from helios_b200.engine.core import EngineCore
+    from helios_b200.engine.model import DecoderModel
+    from helios_b200.weights import bind_random_weights
+
+    bind_random_weights(plan, 3, dtype, DEV)
+    core = EngineCore(DecoderModel(plan, dtype, DEV), page_size=8, num_pages=32, max_slots=2,
+                      poison_cache=float("nan"), use_cuda_graphs=False)
+    outs = []
+    for a, b in zip(cut[:-1], cut[1:]):
+        outs.append(core.step([StepEntry("r", toks[a:b], list(range(b - a)))]).clone())
+    return torch.cat(outs), core
+
+
+def test_a_layer_named_twice_runs_twice_with_a_cache_for_each_run():
+    toks = random_tokens(256, 30, 5)
+    cfg, plan = _toy_plan([0, 1, 0])
+    whole, core = _run_plan(plan, toks, [0, 30])
+    assert len(core.cache._where) == 3                       # three runs, three caches
+    # the same weights laid out as a three-layer model give the same logits
+    hf = dict(TINY_LLAMA, num_hidden_layers=3)
+    tensors = _export(plan)
+    for name, t in list(tensors.items()):
+        if name.startswith("model.layers.0."):
+            tensors[name.replace("layers.0.", "layers.2.")] = t
+    want = plain_model.forward_logits(hf, tensors, toks)
+    assert_logits_close(whole, want, "float32", "layer named twice")
+    # and cutting the sequence changes nothing
+    cfg2, plan2 = _toy_plan([0, 1, 0])
+    parts, _ = _run_plan(plan2, toks, [0, 7, 9, 30])
+    assert_logits_close(parts, want, "float32", "layer named twice, in portions")
+
+
+def _export(plan):
+    """Checkpoint tensors (float32, CPU) back out of the bound parts of a dense plan."""
+    cfg = plan.config
+    q, kv = cfg.q_size, cfg.kv_size
+    out = {"model.embed_tokens.weight": plan.embedding.table.float().cpu(),
+           "model.norm.weight": plan.final_norm.weight.float().cpu(),
+           "lm_head.weight": plan.head.weight.float().cpu()}
+    for i, block in enumerate(plan.layers):
+        p = f"model.layers.{i}."
+        m, f = block.mixer, block.ffn
+        w = m.w_qkv.float().cpu()
+        out[p + "self_attn.q_proj.weight"], out[p + "self_attn.k_proj.weight"], out[p + "self_attn.v_proj.weight"] = \
+            w[:q], w[q:q + kv], w[q + kv:]
+        out[p + "self_attn.o_proj.weight"] = m.w_o.float().cpu()
+        gu = f.w_gate_up.float().cpu()
+        out[p + "mlp.gate_proj.weight"], out[p + "mlp.up_proj.weight"] = gu[:f.inner], gu[f.inner:]
+        out[p + "mlp.down_proj.weight"] = f.w_down.float().cpu()
+        out[p + "input_layernorm.weight"] = block.mixer_norm.weight.float().cpu()
+        out[p + "post_attention_layernorm.weight"] = block.ffn_norm.weight.float().cpu()
+    return out
+
+
+def test_a_layer_may_read_another_layers_cache():
+    """Entry 1 runs layer 1's weights but attends over the keys and values entry 0 wrote
+    (its own k and v are computed and dropped).  Whole and in portions must agree, which
+    they only do if the shared cache is read correctly across steps."""
+    toks = random_tokens(256, 26, 6)
+    _, plan = _toy_plan([0, (1, 0, False)])
+    whole, core = _run_plan(plan, toks, [0, 26])
+    assert len(core.cache._where) == 1 and core.cache.storage[0].shape[0] == 1
+    _, plan2 = _toy_plan([0, (1, 0, False)])
+    parts, _ = _run_plan(plan2, toks, [0, 3, 4, 20, 26])
+    torch.testing.assert_close(parts, whole, atol=2e-5, rtol=0)
+    # and it is not the same as two ordinary layers
+    _, plain_plan = _toy_plan([0, 1])
+    ordinary, _ = _run_plan(plain_plan, toks, [0, 26])
+    assert (ordinary - whole).abs().max() > 1e-4
+    with pytest.raises(ValueError):
+        _toy_plan([0, (1, 0, True)])          # a shared cache must not be written twice
+    with pytest.raises(ValueError):
+        _toy_plan([(0, 1, False), 1])         # nor read before anyone owns it
+
+
+# ---------------------------------------------------------------------- a toy mixer with state
+def test_a_toy_mixer_with_state_of_its_own_is_registered_built_and_stepped():
+    """A running mean over the request's tokens: state of fixed size per request (sum and
+    count), no pages.  Defined here, registered under a name, chosen by a toy
+    architecture's plan builder for every second layer; whole sequences, portions and a
+    batch of two requests must agree, and a slot handed to a new request starts from zero."""
+    from helios_b200.config import DenseDecoderConfig, register_architecture, unregister_architecture
+    from helios_b200.engine.batch import StepEntry
+    from helios_b200.engine.core import EngineCore
+    from helios_b200.engine.model import DecoderModel
+    from helios_b200.parts import (Mixer, ModelPlan, OutputHead, StateSpec, TokenEmbedding, WeightSpec,
+                                   part_class, register_part)
+
+    class RunningMean(Mixer):
+        graph_safe = False                      # it walks the requests on the host
+
+        def __init__(self, width):
+            self.width = width
+
+        def state_spec(self):
+            return StateSpec((self.width + 1,), torch.float32)     # sum, count
+
+        def weight_specs(self):
+            return {"mix.weight": WeightSpec((self.width, self.width))}
+
+        def bind(self, tensors):
+            self.w = tensors["mix.weight"]
+
+        def forward(self, ctx, x, cache, state):
+            assert cache is None
+            out = torch.empty_like(x)
+            for seq in ctx.seqs:
+                rows = slice(seq.token_offset, seq.token_offset + seq.num_tokens)
+                xs = x[rows].float()
+                st = state[seq.slot]
+                csum = st[: self.width] + xs.cumsum(0)
+                cnt = st[self.width] + torch.arange(1, seq.num_tokens + 1, device=x.device)
+                out[rows] = ((csum / cnt[:, None]) @ self.w.float().T).to(x.dtype)
+                st[: self.width] = csum[-1]
+                st[self.width] = cnt[-1]
+            return out
+
+    register_part("mixer", "toy_running_mean", RunningMean, replace=True)
+
+    def build(cfg):
+        norm, ffn, block = part_class("norm", "rmsnorm"), part_class("feed_forward", "swiglu"), part_class("block", "pre_norm")
+        attn, toy = part_class("mixer", "gqa_attention"), part_class("mixer", "toy_running_mean")
+        layers = []
+        for i in range(cfg.num_hidden_layers):
+            mixer = toy(cfg.hidden_size) if i % 2 else attn(cfg.hidden_size, cfg.num_attention_heads,
+                                                            cfg.num_key_value_heads, cfg.head_dim,
+                                                            cfg.attention_scale, False)
+            layers.append(block(norm(cfg.hidden_size, cfg.rms_norm_eps), mixer,
+                                norm(cfg.hidden_size, cfg.rms_norm_eps), ffn(cfg.hidden_size, cfg.intermediate_size)))
+        return ModelPlan(config=cfg, embedding=TokenEmbedding(cfg.vocab_size, cfg.hidden_size),
+                         position=part_class("position_encoding", "rotary")(cfg.head_dim, cfg.rope_theta),
+                         layers=layers, layer_prefixes=[f"model.layers.{i}." for i in range(cfg.num_hidden_layers)],
+                         final_norm=norm(cfg.hidden_size, cfg.rms_norm_eps),
+                         head=OutputHead(cfg.vocab_size, cfg.hidden_size))
+
+    register_architecture("ToyMeanForCausalLM", lambda d: DenseDecoderConfig.from_hf(d, "ToyMeanForCausalLM"),
+                          build, replace=True)
+    try:
+        cfg_json = dict(TINY_LLAMA, architectures=["ToyMeanForCausalLM"], num_hidden_layers=3, rope_scaling=None)
+        for dtype in ("float32", "bfloat16"):
+            model = DecoderModel.from_config(cfg_json, seed=4, dtype=dtype)
+            assert not model.plan.graph_safe
+            core = EngineCore(model, page_size=8, num_pages=32, max_slots=2)
+            assert list(core.cache.states) == [1] and core.cache.states[1].shape == (2, 65)
+            assert len(core.cache._where) == 2               # only the attention layers have pages
+            a, b = random_tokens(256, 23, 1), random_tokens(256, 9, 2)
+            whole_a = core.step([StepEntry("a", a, list(range(23)))]).clone()
+            core.end("a")
+            whole_b = core.step([StepEntry("b", b, list(range(9)))]).clone()     # reuses a's slot: zeroed
+            core.end("b")
+            got_a, got_b = [], []
+            for (sa, ea), (sb, eb) in zip([(0, 5), (5, 6), (6, 20), (20, 23)], [(0, 2), (2, 3), (3, 8), (8, 9)]):
+                out = core.step([StepEntry("a", a[sa:ea], list(range(ea - sa))),
+                                 StepEntry("b", b[sb:eb], list(range(eb - sb)))])
+                got_a.append(out[: ea - sa].clone())
+                got_b.append(out[ea - sa:].clone())
+            tol = dict(atol=3e-5, rtol=0) if dtype == "float32" else dict(atol=3e-2, rtol=3e-2)
+            torch.testing.assert_close(torch.cat(got_a), whole_a, **tol)
+            torch.testing.assert_close(torch.cat(got_b), whole_b, **tol)
+            # the toy layer matters: without the state carried over, portions would differ
+            assert (whole_a[5] - whole_a[4]).abs().max() > 0
+    finally:
+        unregister_architecture("ToyMeanForCausalLM")
