@@ -77,6 +77,19 @@ def _fn(lib: str, name: str, argtypes):
     return f
 
 
+def preload(dtype: torch.dtype) -> None:
+    """Compile (in parallel) and load the libraries a model of this dtype uses, so that
+    the first step does not stop at each one in turn.  float32 never needs the bfloat16
+    tensor-core kernels and the other way round."""
+    from .build import build_all
+
+    names = ["elementwise", "attention_generic"]
+    names += ["gemm_f32"] if dtype == torch.float32 else ["attention_bf16", "gemm_bf16"]
+    build_all(names)
+    for n in names:
+        load_library(n)
+
+
 # ------------------------------------------------------------------ embedding
 def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
     """float32 [T, H] rows of ``table`` ([V, H], float32 or bfloat16) at int32 ``ids``."""

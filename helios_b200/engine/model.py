@@ -42,6 +42,8 @@ class DecoderModel:
         self.config = plan.config
         self.dtype = dtype
         self.device = device
+        from ..csrc import ops
+        ops.preload(dtype)
 
     # ------------------------------------------------------------------ construction
     @classmethod
