@@ -129,8 +129,132 @@ def decode_bytes(cfg, layers, batch, ctx, dtype_bytes=2):
 
 
 def run_reference(args):
-    print(json.dumps({"impl": "reference",
-                      "unavailable": "reference arm not wired up yet in this bench"}))
+    """The unmodified reference (installed under baseline/_ref) through its own public
+    API, ``LLMEngine(EngineConfig(...))`` / ``add_request`` / ``step``, on the same model
+    sizes, batch and context.  Only the model folder (random weights in its checkpoint
+    layout) is written here; nothing of helios_b200 runs."""
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "helios")):
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "baseline/_ref is missing (pip install --no-index --no-deps --target baseline/_ref)"}))
+        return 0
+    sys.path.insert(0, ref)
+    try:
+        import torch
+        from helios.core.types import SamplingParams
+        from helios.engine import EngineConfig, LLMEngine
+    except Exception as exc:                                    # noqa: BLE001
+        print(json.dumps({"impl": "reference", "unavailable": f"import failed: {exc!r}"[:200]}))
+        return 0
+    if not torch.cuda.is_available():
+        print(json.dumps({"impl": "reference", "unavailable": "no CUDA device"}))
+        return 0
+
+    layers = args.ref_layers
+    cfg = dict(LLAMA_31_8B, num_hidden_layers=layers)
+    folder = os.path.join(args.ref_dir, f"helios_ref_llama8b_L{layers}_s{args.seed}")
+    t_setup = time.time()
+    if not os.path.exists(os.path.join(folder, "model.safetensors")):
+        from safetensors.torch import save_file
+        os.makedirs(folder, exist_ok=True)
+        gen = torch.Generator(device="cuda").manual_seed(args.seed)
+        H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+        q, kv = cfg["num_attention_heads"] * cfg["head_dim"], cfg["num_key_value_heads"] * cfg["head_dim"]
+
+        def rnd(*shape):
+            return (torch.randn(*shape, generator=gen, device="cuda") * 0.02).half().cpu()
+
+        tensors = {"model.embed_tokens.weight": rnd(V, H), "lm_head.weight": rnd(V, H),
+                   "model.norm.weight": torch.ones(H, dtype=torch.float16)}
+        for i in range(layers):
+            p = f"model.layers.{i}."
+            tensors.update({
+                p + "self_attn.q_proj.weight": rnd(q, H), p + "self_attn.k_proj.weight": rnd(kv, H),
+                p + "self_attn.v_proj.weight": rnd(kv, H), p + "self_attn.o_proj.weight": rnd(H, q),
+                p + "mlp.gate_proj.weight": rnd(I, H), p + "mlp.up_proj.weight": rnd(I, H),
+                p + "mlp.down_proj.weight": rnd(H, I),
+                p + "input_layernorm.weight": torch.ones(H, dtype=torch.float16),
+                p + "post_attention_layernorm.weight": torch.ones(H, dtype=torch.float16)})
+        save_file(tensors, os.path.join(folder, "model.safetensors"))
+        del tensors
+        with open(os.path.join(folder, "config.json"), "w") as f:
+            json.dump(dict(cfg, torch_dtype="float16"), f)
+        torch.cuda.empty_cache()
+
+    page = 16
+    pool_tokens = args.batch * (args.context + 2 * page) + 8 * page
+    kv_bytes = pool_tokens * 2 * layers * cfg["num_key_value_heads"] * cfg["head_dim"] * 2
+    engine = LLMEngine(EngineConfig(
+        model_dir=folder, kv_cache_bytes=kv_bytes, block_size=page, max_num_seqs=args.batch,
+        max_num_batched_tokens=PREFILL_TOKENS, max_model_len=args.context + 8, device="cuda",
+        watermark=0.0))
+    setup_s = time.time() - t_setup
+    gen = torch.Generator().manual_seed(args.seed)
+
+    def tokens(n):
+        return torch.randint(0, cfg["vocab_size"], (n,), generator=gen).tolist()
+
+    # prefill of one 2,048-token prompt
+    prefill = None
+    if not args.no_prefill:
+        engine.add_request("warm", tokens(PREFILL_TOKENS), SamplingParams(max_tokens=1))
+        engine.run_until_complete()
+        torch.cuda.synchronize()
+        engine.add_request("p", tokens(PREFILL_TOKENS), SamplingParams(max_tokens=1))
+        t0 = time.perf_counter()
+        engine.run_until_complete()
+        torch.cuda.synchronize()
+        ms = (time.perf_counter() - t0) * 1e3
+        prefill = {"value": round(PREFILL_TOKENS / ms * 1e3, 1), "tokens": PREFILL_TOKENS,
+                   "ms": round(ms, 3),
+                   "frac": round(step_flops(cfg, layers, PREFILL_TOKENS, 0) / (ms * 1e-3)
+                                 / (load_peaks()["bf16_tflops"] * 1e12), 4)}
+
+    steps, warmup = args.steps, max(3, args.warmup)
+    ctx0 = args.context - steps - warmup - 64
+    for b in range(args.batch):
+        engine.add_request(f"e{b}", tokens(ctx0), SamplingParams(max_tokens=steps + warmup + 64))
+    guard = 0
+    while engine.scheduler.waiting or any(not s.is_prefill_done for s in engine.scheduler.running):
+        engine.step()
+        guard += 1
+        if guard > 10000:
+            break
+    for _ in range(warmup):
+        engine.step()
+    sampler = ClockSampler()
+    sampler.start()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.time()
+    w0 = time.perf_counter()
+    start.record()
+    for _ in range(steps):
+        engine.step()
+    end.record()
+    torch.cuda.synchronize()
+    wall = (time.perf_counter() - w0) / steps
+    t1 = time.time()
+    sampler.stop()
+    ms = start.elapsed_time(end) / steps
+    running = len(engine.scheduler.running)
+    line = {
+        "impl": "reference",
+        "metric": "decode tokens/s (Llama-3.1-8B sizes, batch 8, context 4096)",
+        "value": round(running / ms * 1e3, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
+        "warmup": warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "fp16 (the reference's own choice on CUDA)",
+        "data": "synthetic token ids (uniform, seeded), random weights N(0, 0.02)",
+        "config": {"model": "Llama-3.1-8B sizes", "layers": layers, "layers_full": FULL_LAYERS,
+                   "hidden": 4096, "heads": 32, "kv_heads": 8, "head_dim": 128, "intermediate": 14336,
+                   "vocab": 128256, "global_batch": args.batch, "live_requests": running,
+                   "seq_len": args.context, "page_size": page, "parallelism": "single GPU",
+                   "api": "helios.engine.LLMEngine.step", "setup_s": round(setup_s, 1)},
+        "clocks": sampler.summary(t0, t1), "gpu_launches": 0, "prefill": prefill,
+        "e2e": {"value": round(running / wall, 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": 16 * args.batch, "d2h_bytes_per_step": 8 * args.batch},
+    }
+    print(json.dumps(line))
     return 0
 
 
@@ -148,6 +272,10 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--ref-layers", type=int, default=FULL_LAYERS,
+                    help="layers of the reference arm's model (its loader builds the model in "
+                         "float32 on the host first)")
+    ap.add_argument("--ref-dir", default="/tmp", help="where the reference arm's model folder is written")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
