@@ -272,6 +272,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--no-graphs", action="store_true",
+                    help="run decode steps kernel by kernel (for profilers) instead of as captured graphs")
     ap.add_argument("--ref-layers", type=int, default=FULL_LAYERS,
                     help="layers of the reference arm's model (its loader builds the model in "
                          "float32 on the host first)")
@@ -300,7 +302,8 @@ def main():
     point_batches = [int(b) for b in args.points.split(",") if b.strip()]
     max_batch = max([args.batch] + point_batches)
     core = EngineCore(model, page_size=page, num_pages=max_batch * (args.context // page) + 64,
-                      max_slots=max_batch, max_model_len=args.context + 1)
+                      max_slots=max_batch, max_model_len=args.context + 1,
+                      use_cuda_graphs=not args.no_graphs)
     gen = torch.Generator().manual_seed(args.seed)
 
     def tokens(n):
