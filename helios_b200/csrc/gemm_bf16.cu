@@ -47,6 +47,8 @@ struct GemmArgs {
   int glu_offset;       // GLU: row of the weight where the second half ("up") begins
   int out_f32;
   int k_splits;
+  int cluster_reduce;   // the K slices of a tile form a thread-block cluster and add their
+                        // partial sums through distributed shared memory (no scratch)
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -119,6 +121,19 @@ __device__ __forceinline__ void tmem_ld16(uint32_t addr, float (&v)[16]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Cluster-wide barrier (every thread of every block of the cluster arrives and waits).
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Read a float from the same shared-memory offset in the block of rank `rank` of the cluster.
+__device__ __forceinline__ float ld_peer_smem(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
 }
 
 // Shared-memory operand descriptor: K-major tile of 128-byte rows, 128-byte swizzle, groups
@@ -303,7 +318,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int tile_id = tile_b * gridDim.x + tile_a;
     const size_t tile_elems = (size_t)BM * Cfg::ACC_COLS;
     bool finalize = ok;
-    if (ok && args.k_splits > 1) {
+    if (args.cluster_reduce) {
+      // Slices of one tile are the blocks of one cluster.  Each parks its partial sums in
+      // its own shared memory (the stage buffers are free now), column-major [col][128].
+      finalize = false;
+      float* part = reinterpret_cast<float*>(aligned);
+      for (int c = 0; c < Cfg::ACC_COLS; c += 16) {
+        float v[16];
+        if (ok && n_kb > 0) {
+          tmem_ld16(taddr + c, v);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) part[(c + j) * BM + r] = v[j];
+      }
+    } else if (ok && args.k_splits > 1) {
       // park the partial sums; the last block of the tile adds them up
       float* mine = args.scratch + ((size_t)tile_id * args.k_splits + split) * tile_elems;
       for (int c = 0; c < Cfg::ACC_COLS; c += 16) {
@@ -399,6 +430,48 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
   }
 
+  if (args.cluster_reduce) {
+    // ---------------------------------------------------------------- reduction inside the cluster
+    // After the barrier every block adds up its share of the tile's elements, reading the
+    // partial sums of all slices (in slice order) from its peers' shared memory, and writes
+    // the result; the second barrier keeps every block's memory alive until all have read.
+    cluster_sync_all();
+    if (warp >= 2 && !*abort_flag) {
+      constexpr int OUT_COLS = (EPI == EPI_GLU && !SWAP) ? BN / 2 : BN;   // columns of the result tile
+      constexpr int GLU_SHIFT = (EPI == EPI_GLU) ? (SWAP ? BN : BN / 2) : 0;
+      const uint32_t part_addr = base;
+      const int S = args.k_splits;
+      const int total = OUT_COLS * BM;
+      const int per = (total + S - 1) / S;
+      const int e_begin = split * per, e_end = min(total, e_begin + per);
+      for (int e = e_begin + (int)threadIdx.x - 64; e < e_end; e += 128) {
+        const int c = e / BM, rr = e - c * BM;
+        // all loads first (a cluster has at most 8 blocks), then the sum in slice order
+        float gv[8], uv[8];
+#pragma unroll
+        for (int sp = 0; sp < 8; ++sp) {
+          gv[sp] = sp < S ? ld_peer_smem(part_addr + (uint32_t)(c * BM + rr) * 4u, sp) : 0.f;
+          uv[sp] = (EPI == EPI_GLU && sp < S)
+                       ? ld_peer_smem(part_addr + (uint32_t)((GLU_SHIFT + c) * BM + rr) * 4u, sp) : 0.f;
+        }
+        float g = 0.f, u = 0.f;
+#pragma unroll
+        for (int sp = 0; sp < 8; ++sp) { g += gv[sp]; u += uv[sp]; }
+        float val = g;
+        if (EPI == EPI_GLU) val = g / (1.f + __expf(-g)) * u;
+        int t, n;
+        if (SWAP) { t = tile_b * BN + c; n = tile_a * BM + rr; }
+        else { t = tile_a * BM + rr; n = tile_b * OUT_COLS + c; }
+        if (t < args.T && n < args.N) {
+          if (args.bias) val += args.bias[n];
+          if (args.out_f32) reinterpret_cast<float*>(args.out)[(size_t)t * args.ldo + n] = val;
+          else reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)t * args.ldo + n] = __float2bfloat16_rn(val);
+        }
+      }
+    }
+    cluster_sync_all();
+  }
+
   // ---------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
@@ -473,13 +546,74 @@ int launch(const void* x, const void* w, const GemmArgs& args, int w_rows, int l
     const int per_tile = (EPI == EPI_GLU) ? BN / 2 : BN;
     grid = dim3((args.T + BM - 1) / BM, (args.N + per_tile - 1) / per_tile, args.k_splits);
   }
-  hb_launch(kernel, grid, dim3(GEMM_THREADS), Cfg::SMEM, stream, map_a, map_b, args);
+  if (args.cluster_reduce) {
+    // the partial sums of a block must fit the stage buffers they reuse
+    if ((size_t)Cfg::ACC_COLS * BM * sizeof(float) > (size_t)Cfg::STAGES * Cfg::STAGE_BYTES || args.k_splits > 8)
+      return HB_BAD_ARGUMENT;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = Cfg::SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = args.k_splits;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = hb_pdl_enabled() ? 2 : 1;
+    cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, args);
+  } else {
+    hb_launch(kernel, grid, dim3(GEMM_THREADS), Cfg::SMEM, stream, map_a, map_b, args);
+  }
   return hb_check_launch();
+}
+
+// How many clusters of `cluster_size` blocks of this kernel the device keeps resident.
+template <int BN, bool SWAP, int EPI>
+int max_clusters(int cluster_size) {
+  using Cfg = Config<BN, SWAP, EPI>;
+  auto kernel = gemm_bf16_kernel<BN, SWAP, EPI>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM) != cudaSuccess)
+    return -1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1, 1, cluster_size);
+  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.dynamicSmemBytes = Cfg::SMEM;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = cluster_size;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) return -1;
+  return n;
 }
 
 }  // namespace
 
 #ifndef HB_GEMM_BF16_NO_EXPORTS
+// Resident clusters of `cluster_size` blocks for the kernel variant a call would use
+// (-1 if the query fails).
+HB_EXPORT int hb_gemm_bf16_max_clusters(int swap_bn, int glu, int cluster_size) {
+  if (cluster_size < 1 || cluster_size > 8) return -1;
+#define HB_OCC_CASE(BN_, SWAP_) \
+  return glu ? max_clusters<BN_, SWAP_, EPI_GLU>(cluster_size) : max_clusters<BN_, SWAP_, EPI_STORE>(cluster_size)
+  switch (swap_bn) {
+    case 0: HB_OCC_CASE(256, false);
+    case 16: HB_OCC_CASE(16, true);
+    case 32: HB_OCC_CASE(32, true);
+    case 64: HB_OCC_CASE(64, true);
+    case 128: HB_OCC_CASE(128, true);
+    default: return -1;
+  }
+#undef HB_OCC_CASE
+}
+
 // Output tiles of a call (N counts the result's features), and the scratch floats it needs
 // (0 when the K range is not split).  swap_bn = 0: tiles of 128 tokens x 256 features (128
 // result features for SwiGLU); else 128 features x swap_bn tokens.
@@ -499,21 +633,25 @@ HB_EXPORT long long hb_gemm_bf16_scratch_floats(int T, int N, int swap_bn, int g
 // y[T, N] = x[T, K] w[N, K]^T (+ bias), or SwiGLU over w = [gate rows; up rows] with the up
 // rows starting at row glu_offset (then N counts the result's features).
 //   swap_bn = 0: tokens on the M axis (tile 128 x 256).  swap_bn in {16, 32, 64, 128}: swapped,
-//   that many tokens per tile.  With k_splits > 1 scratch and tickets are needed.
+//   that many tokens per tile.  With 1 < k_splits <= 8 and `cluster` set, the slices of a tile
+//   run as one thread-block cluster and add up through distributed shared memory; else the
+//   partial sums go through `scratch` with one ticket per tile.
 HB_EXPORT int hb_gemm_bf16(void* out, const void* x, const void* w, const float* bias, float* scratch,
                            int* tickets, int* error, int T, int N, int K, int ldx, int ldw, int ldo,
                            int w_rows, int glu, int glu_offset, int out_f32, int swap_bn, int k_splits,
-                           cudaStream_t stream) {
+                           int cluster, cudaStream_t stream) {
   if (T <= 0 || N <= 0) return HB_OK;
   if (K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || k_splits < 1) return HB_BAD_ARGUMENT;
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return HB_BAD_ARGUMENT;
-  if (k_splits > 1 && (scratch == nullptr || tickets == nullptr)) return HB_BAD_ARGUMENT;
+  const bool clustered = k_splits > 1 && k_splits <= 8 && cluster != 0;
+  if (k_splits > 1 && !clustered && (scratch == nullptr || tickets == nullptr)) return HB_BAD_ARGUMENT;
   if (k_splits > (K + BK - 1) / BK) return HB_BAD_ARGUMENT;
   if (error == nullptr) return HB_BAD_ARGUMENT;
   GemmArgs a;
   a.out = out; a.bias = bias; a.scratch = scratch; a.tickets = tickets; a.error = error;
   a.T = T; a.N = N; a.K = K; a.ldo = ldo; a.glu_offset = glu_offset; a.out_f32 = out_f32;
   a.k_splits = k_splits;
+  a.cluster_reduce = clustered ? 1 : 0;
 #define HB_GEMM_CASE(BN_, SWAP_)                                                              \
   return glu ? launch<BN_, SWAP_, EPI_GLU>(x, w, a, w_rows, ldx, ldw, stream)                 \
              : launch<BN_, SWAP_, EPI_STORE>(x, w, a, w_rows, ldx, ldw, stream)

@@ -104,6 +104,7 @@ int hb_gemm_bf16_noalloc(void* out, const void* x, const void* w, int T, int N, 
   a.error = error_word;
   a.T = T; a.N = N; a.K = K; a.ldo = N; a.glu_offset = 0; a.out_f32 = 0;
   a.k_splits = k_splits;
+  a.cluster_reduce = 0;
   const int rc = launch<16, true, EPI_STORE>(x, w, a, N, K, K, stream);
   if (rc != HB_OK)
     return fail(HB_NOALLOC_LAUNCH_FAILED, err, err_len, "hb_gemm_bf16_noalloc: the kernel launch failed");

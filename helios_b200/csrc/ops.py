@@ -268,7 +268,21 @@ def linear_f32(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tenso
 # reductions, one ticket per output tile (zero between launches), and an error word
 # that a kernel sets when one of its bounded waits ran out.  Its addresses never
 # change, so captured CUDA graphs stay valid.
+#: add the partial sums of a split reduction inside a thread-block cluster (through
+#: distributed shared memory) where that is possible, instead of through scratch memory
+GEMM_CLUSTER_REDUCE = True
 _GEMM_SCRATCH_FLOATS = 16 * 1024 * 1024
+
+
+def _cluster_fits(bn: int, glu: bool) -> bool:
+    """Whether a block's float32 partial sums fit the stage buffers they reuse."""
+    if bn == 0:
+        stage, budget, cols = 48 * 1024, 196 * 1024, 256
+    else:
+        a_tiles = 2 if glu else 1
+        stage, budget, cols = a_tiles * 16384 + bn * 128, 108 * 1024, bn * a_tiles
+    stages = max(2, min(8, budget // stage))
+    return cols * 128 * 4 <= stages * stage
 _GEMM_TICKETS = 1 << 16
 _gemm_ws = {}
 
@@ -296,10 +310,31 @@ def check_kernel_errors(device=None) -> None:
                               "the results of that launch are not valid")
 
 
+_cluster_capacity = {}
+
+
+def cluster_capacity(bn: int, glu: bool, size: int) -> int:
+    """Clusters of ``size`` blocks of the GEMM variant (bn, glu) the device keeps resident
+    at once.  The CUDA occupancy calculator is asked (it knows how the SMs are spread over
+    the GPCs, which bounds whole clusters); it counts one block per SM where the swapped
+    variants run two, so its figure is doubled for them.  Measured on B200: cluster counts
+    up to that doubled figure run in one round, beyond it a second round shows."""
+    key = (bn, bool(glu), size)
+    if key not in _cluster_capacity:
+        lib = load_library("gemm_bf16")
+        n = int(lib.hb_gemm_bf16_max_clusters(bn, int(glu), size))
+        if n <= 0:
+            n = _SM_COUNT // size
+        _cluster_capacity[key] = n * (2 if bn else 1)
+    return _cluster_capacity[key]
+
+
 def gemm_plan(T: int, N: int, K: int, glu: bool):
     """(swap_bn, k_splits) of the tensor-core product for T tokens, N result features.
-    Up to 128 tokens run swapped (features on the MMA M axis) with the reduction split so
-    that the blocks fill the SMs (two resident per SM, at least 8 k-blocks a slice)."""
+    Up to 128 tokens run swapped (features on the MMA M axis).  When the tiles alone do not
+    fill the SMs, the reduction is split (at least 8 k-blocks a slice): with slices as
+    thread-block clusters, the count that keeps the most blocks resident in ONE round of
+    clusters; else the count that fills the resident blocks."""
     k_blocks = -(-K // 64)
     if T <= 128:
         bn = 16 if T <= 16 else 32 if T <= 32 else 64 if T <= 64 else 128
@@ -313,9 +348,17 @@ def gemm_plan(T: int, N: int, K: int, glu: bool):
         slots = _SM_COUNT
     splits = 1
     if tiles < slots:
-        splits = _wave_splits(tiles, slots, max(1, min(16, k_blocks // 8)))
-        while splits > 1 and tiles * splits * 128 * cols > _GEMM_SCRATCH_FLOATS:
-            splits -= 1
+        most_k = max(1, k_blocks // 8)
+        if GEMM_CLUSTER_REDUCE and _cluster_fits(bn, glu):
+            best = 0
+            for s in range(1, min(8, most_k) + 1):
+                # a few clusters over the figure cost less than a smaller cluster size
+                if tiles * 15 <= cluster_capacity(bn, glu, s) * 16 and tiles * s > best + best // 16:
+                    splits, best = s, tiles * s
+        else:
+            splits = _wave_splits(tiles, slots, min(16, most_k))
+            while splits > 1 and tiles * splits * 128 * cols > _GEMM_SCRATCH_FLOATS:
+                splits -= 1
     return bn, splits
 
 
@@ -328,7 +371,7 @@ def tc_gemm_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
 
 def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
                 glu: bool = False, out_dtype: torch.dtype = torch.bfloat16,
-                plan=None) -> torch.Tensor:
+                plan=None, cluster: Optional[bool] = None) -> torch.Tensor:
     """y = x W^T (+ bias) on tcgen05 tensor cores; bfloat16 operands, float32 accumulate.
 
     With ``glu`` the weight is [gate rows; up rows] ([2 I, K]) and the result is
@@ -357,9 +400,13 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
     if T == 0:
         return out
     bn, splits = plan if plan is not None else gemm_plan(T, N, K, glu)
+    if cluster is None:
+        cluster = GEMM_CLUSTER_REDUCE
+    # slices of a tile as a cluster: at most 8, and the partial sums must fit the stages
+    cluster = bool(cluster) and 1 < splits <= 8 and _cluster_fits(bn, glu)
     scratch, tickets, err = _gemm_workspace(x.device)
     lib = load_library("gemm_bf16")
-    if splits > 1:
+    if splits > 1 and not cluster:
         lib.hb_gemm_bf16_scratch_floats.restype = ctypes.c_longlong
         need = lib.hb_gemm_bf16_scratch_floats(T, N, bn, int(glu), splits)
         tiles = lib.hb_gemm_bf16_tiles(T, N, bn, int(glu))
@@ -368,10 +415,10 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
                               f"the work space holds {scratch.numel()} and {tickets.numel()}")
     f = _fn("gemm_bf16", "hb_gemm_bf16",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
     _run(f(_p(out), _p(x), _p(weight), _p(bias), _p(scratch), _p(tickets), _p(err), T, N, K, K, K, N,
            rows, int(glu), N if glu else 0, 1 if out_dtype == torch.float32 else 0, bn, splits,
-           _stream()), "gemm_bf16")
+           1 if cluster else 0, _stream()), "gemm_bf16")
     return out
 
 

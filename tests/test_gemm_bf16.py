@@ -37,10 +37,13 @@ def test_plain_and_bias(T, N, K):
     ops().check_kernel_errors()
 
 
+@pytest.mark.parametrize("cluster", [False, True])
 @pytest.mark.parametrize("bn", [0, 16, 32, 64, 128])
-@pytest.mark.parametrize("splits", [1, 2, 5])
+@pytest.mark.parametrize("splits", [1, 2, 5, 8])
 @pytest.mark.parametrize("glu", [False, True])
-def test_every_orientation_and_split(bn, splits, glu):
+def test_every_orientation_and_split(bn, splits, glu, cluster):
+    """Split reductions both ways: through scratch memory with a ticket per tile, and
+    inside a thread-block cluster through distributed shared memory."""
     T = {0: 260, 16: 9, 32: 32, 64: 50, 128: 128}[bn]
     N, K = 392, 1024 + 64 * 3
     x, w, b = _case(T, N, K, bn + splits, glu)
@@ -48,10 +51,10 @@ def test_every_orientation_and_split(bn, splits, glu):
     if glu:
         gate, up = xd @ wd[:N].T, xd @ wd[N:].T
         want = gate * torch.sigmoid(gate) * up
-        got = ops().linear_bf16(x.to(DEV), w.to(DEV), glu=True, plan=(bn, splits))
+        got = ops().linear_bf16(x.to(DEV), w.to(DEV), glu=True, plan=(bn, splits), cluster=cluster)
     else:
         want = xd @ wd.T + b.double()
-        got = ops().linear_bf16(x.to(DEV), w.to(DEV), b.to(DEV), plan=(bn, splits))
+        got = ops().linear_bf16(x.to(DEV), w.to(DEV), b.to(DEV), plan=(bn, splits), cluster=cluster)
     _close(got, want)
     ops().check_kernel_errors()
 
@@ -59,9 +62,12 @@ def test_every_orientation_and_split(bn, splits, glu):
 def test_split_sum_is_the_same_every_time_and_tickets_return_to_zero():
     x, w, _ = _case(8, 4096, 14336, 3)
     xd, wd = x.to(DEV), w.to(DEV)
-    first = ops().linear_bf16(xd, wd, plan=(16, 7))
+    first = ops().linear_bf16(xd, wd, plan=(16, 7), cluster=False)
     for _ in range(5):
-        assert torch.equal(ops().linear_bf16(xd, wd, plan=(16, 7)), first)
+        assert torch.equal(ops().linear_bf16(xd, wd, plan=(16, 7), cluster=False), first)
+    # the cluster reduction adds the slices in the same order
+    for _ in range(3):
+        assert torch.equal(ops().linear_bf16(xd, wd, plan=(16, 7), cluster=True), first)
     _, tickets, _ = ops()._gemm_workspace(torch.device(DEV))
     assert int(tickets.abs().sum()) == 0
     _close(first, x.double() @ w.double().T)
