@@ -74,8 +74,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* error, int code) {
   for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (i > 32) {
+    if (mbar_try_wait(bar, parity)) return true;      // suspends in hardware for a while itself
+    if (i > 2048) {
       __nanosleep(64);
       if (*abort_flag) return false;
     }
@@ -391,11 +391,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           float g[16], u[16];
           load_chunk(c, g);
           load_chunk(HALF + c, u);
+          float val[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float val = g[j] / (1.f + __expf(-g[j])) * u[j];
-            if (SWAP) store(tile_b * BN + c + j, tile_a * BM + r, val);
-            else store(tile_a * BM + r, tile_b * HALF + c + j, val);
+          for (int j = 0; j < 16; ++j) val[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
+          if (SWAP) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) store(tile_b * BN + c + j, tile_a * BM + r, val[j]);
+          } else {
+            const int t = tile_a * BM + r, n0 = tile_b * HALF + c;
+            if (!args.out_f32 && t < args.T && n0 + 16 <= args.N && (args.ldo & 7) == 0) {
+              uint32_t packed[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                __nv_bfloat162 p = __floats2bfloat162_rn(val[2 * j], val[2 * j + 1]);
+                packed[j] = *reinterpret_cast<uint32_t*>(&p);
+              }
+              uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(args.out) + (size_t)t * args.ldo + n0);
+              dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+              dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) store(t, n0 + j, val[j]);
+            }
           }
         }
       } else {
@@ -487,6 +504,211 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   }
 }
 
+// ------------------------------------------------------------------ persistent kernel (prefill)
+// Tokens on the M axis, tiles of 128 tokens x 256 weight rows (SwiGLU: 128 gate + 128 up
+// rows -> 128 result features).  One block per SM walks the tiles (token tiles fastest, so
+// blocks that run together share a weight tile in L2).  Tensor memory holds TWO accumulators
+// (2 x 256 columns): while the epilogue warps drain one, the MMA warp fills the other, so
+// the epilogue costs nothing as long as it is shorter than a tile's main loop.
+constexpr int P_BN = 256;
+constexpr int P_STAGES = 4;
+constexpr int P_A_BYTES = BM * BK * 2;
+constexpr int P_B_BYTES = P_BN * BK * 2;
+constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
+constexpr size_t P_SMEM = (size_t)P_STAGES * P_STAGE_BYTES + 1024 + 256;
+
+template <int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                            GemmArgs args, int tiles_m, int tiles_n) {
+  extern __shared__ unsigned char smem_raw[];
+  pdl_launch_dependents();
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* aligned = smem_raw + (base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + (size_t)P_STAGES * P_STAGE_BYTES);
+  // bars[0..S): full, [S..2S): empty, [2S..2S+2): accumulator full, [2S+2..2S+4): accumulator empty
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * P_STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kb_total = (args.K + BK - 1) / BK;
+  const int n_tiles = tiles_m * tiles_n;
+  constexpr int RESULT_COLS = (EPI == EPI_GLU) ? P_BN / 2 : P_BN;
+
+  auto full_bar = [&](int s) { return smem_u32(bars + s); };
+  auto empty_bar = [&](int s) { return smem_u32(bars + P_STAGES + s); };
+  auto acc_full = [&](int b) { return smem_u32(bars + 2 * P_STAGES + b); };
+  auto acc_empty = [&](int b) { return smem_u32(bars + 2 * P_STAGES + 2 + b); };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < P_STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full(b), 1);
+      mbar_init(acc_empty(b), 4);          // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------------------------------------------------- TMA producer
+      // `it` counts k-blocks over all of this block's tiles; stage = it % P_STAGES.
+      const int my_tiles = blockIdx.x < n_tiles ? (n_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+      const long long total = (long long)my_tiles * kb_total;
+      auto coords = [&](long long it, int& k0, int& a_row, int& b_row0, int& b_row1) {
+        const int j = (int)(it / kb_total), kb = (int)(it - (long long)j * kb_total);
+        const int q = blockIdx.x + j * gridDim.x;
+        const int tile_m = q % tiles_m, tile_n = q / tiles_m;
+        k0 = kb * BK;
+        a_row = tile_m * BM;
+        b_row0 = tile_n * RESULT_COLS;
+        b_row1 = args.glu_offset + tile_n * RESULT_COLS;
+      };
+      auto load_weights = [&](long long it, int s) {
+        int k0, a_row, b_row0, b_row1;
+        coords(it, k0, a_row, b_row0, b_row1);
+        const uint32_t sb = base + s * P_STAGE_BYTES + P_A_BYTES;
+        tma_load_2d(sb, &map_b, full_bar(s), k0, b_row0);
+        if (EPI == EPI_GLU) tma_load_2d(sb + P_B_BYTES / 2, &map_b, full_bar(s), k0, b_row1);
+      };
+      auto load_activations = [&](long long it, int s) {
+        int k0, a_row, b_row0, b_row1;
+        coords(it, k0, a_row, b_row0, b_row1);
+        tma_load_2d(base + s * P_STAGE_BYTES, &map_a, full_bar(s), k0, a_row);
+      };
+      // the weight tiles of the first stages do not depend on the kernel before
+      const int pre = total < P_STAGES ? (int)total : P_STAGES;
+      for (int i = 0; i < pre; ++i) {
+        mbar_expect_tx(full_bar(i), P_STAGE_BYTES);
+        load_weights(i, i);
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i) load_activations(i, i);
+      for (long long it = pre; it < total; ++it) {
+        const int s = (int)(it % P_STAGES);
+        const uint32_t ph = (uint32_t)((it / P_STAGES) & 1);
+        if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, args.error, 1)) break;
+        mbar_expect_tx(full_bar(s), P_STAGE_BYTES);
+        load_weights(it, s);
+        load_activations(it, s);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------------------------------------------------- MMA issuer
+      constexpr uint32_t idesc = instr_desc(BM, P_BN);
+      int it = 0, j = 0;
+      bool ok = true;
+      for (int q = blockIdx.x; q < n_tiles && ok; q += gridDim.x, ++j) {
+        const int b = j & 1;
+        const uint32_t use = (uint32_t)(j >> 1);
+        ok = mbar_wait(acc_empty(b), (use & 1) ^ 1, abort_flag, args.error, 4);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t acc_addr = tmem_base + (uint32_t)(b * P_BN);
+        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+          const int s = it % P_STAGES;
+          const uint32_t ph = (it / P_STAGES) & 1;
+          ok = mbar_wait(full_bar(s), ph, abort_flag, args.error, 2);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sa = base + s * P_STAGE_BYTES, sb = sa + P_A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_bf16(acc_addr, smem_desc(sa + k * UMMA_K * 2), smem_desc(sb + k * UMMA_K * 2), idesc,
+                      (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit(empty_bar(s));
+        }
+        if (ok) umma_commit(acc_full(b));
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ epilogue warps
+    pdl_wait();
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    int j = 0;
+    for (int q = blockIdx.x; q < n_tiles; q += gridDim.x, ++j) {
+      const int b = j & 1;
+      const uint32_t use = (uint32_t)(j >> 1);
+      const int tile_m = q % tiles_m, tile_n = q / tiles_m;
+      if (!mbar_wait(acc_full(b), use & 1, abort_flag, args.error, 3)) break;
+      if (*abort_flag) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * P_BN);
+      const int t = tile_m * BM + r;
+      for (int c = 0; c < RESULT_COLS; c += 16) {
+        float val[16];
+        if (EPI == EPI_GLU) {
+          float g[16], u[16];
+          tmem_ld16(taddr + c, g);
+          tmem_ld16(taddr + RESULT_COLS + c, u);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) val[i] = g[i] / (1.f + __expf(-g[i])) * u[i];
+        } else {
+          tmem_ld16(taddr + c, val);
+        }
+        const int n0 = tile_n * RESULT_COLS + c;
+        if (t < args.T) {
+          if (args.bias) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) if (n0 + i < args.N) val[i] += args.bias[n0 + i];
+          }
+          if (!args.out_f32 && n0 + 16 <= args.N && (args.ldo & 7) == 0) {
+            uint32_t packed[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              __nv_bfloat162 p = __floats2bfloat162_rn(val[2 * i], val[2 * i + 1]);
+              packed[i] = *reinterpret_cast<uint32_t*>(&p);
+            }
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(args.out) + (size_t)t * args.ldo + n0);
+            dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              if (n0 + i < args.N) {
+                if (args.out_f32) reinterpret_cast<float*>(args.out)[(size_t)t * args.ldo + n0 + i] = val[i];
+                else reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)t * args.ldo + n0 + i] = __float2bfloat16_rn(val[i]);
+              }
+            }
+          }
+        }
+      }
+      // this warp has read its lanes of the accumulator: hand it back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(b)) : "memory");
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(100);
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
@@ -568,6 +790,32 @@ int launch(const void* x, const void* w, const GemmArgs& args, int w_rows, int l
   } else {
     hb_launch(kernel, grid, dim3(GEMM_THREADS), Cfg::SMEM, stream, map_a, map_b, args);
   }
+  return hb_check_launch();
+}
+
+template <int EPI>
+int launch_persistent(const void* x, const void* w, const GemmArgs& args, int w_rows, int ldx, int ldw,
+                      cudaStream_t stream) {
+  CUtensorMap map_a, map_b;
+  if (!make_map(&map_a, x, args.T, args.K, ldx, BM)) return HB_LAUNCH_FAILED;
+  if (!make_map(&map_b, w, w_rows, args.K, ldw, EPI == EPI_GLU ? P_BN / 2 : P_BN)) return HB_LAUNCH_FAILED;
+  auto kernel = gemm_bf16_persistent_kernel<EPI>;
+  static bool configured = false;
+  static int sm_count = 0;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P_SMEM) != cudaSuccess)
+      return HB_LAUNCH_FAILED;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0)
+      return HB_LAUNCH_FAILED;
+    configured = true;
+  }
+  const int per_tile = (EPI == EPI_GLU) ? P_BN / 2 : P_BN;
+  const int tiles_m = (args.T + BM - 1) / BM, tiles_n = (args.N + per_tile - 1) / per_tile;
+  const int n_tiles = tiles_m * tiles_n;
+  const int blocks = n_tiles < sm_count ? n_tiles : sm_count;
+  hb_launch(kernel, dim3(blocks), dim3(GEMM_THREADS), P_SMEM, stream, map_a, map_b, args, tiles_m, tiles_n);
   return hb_check_launch();
 }
 
@@ -655,6 +903,9 @@ HB_EXPORT int hb_gemm_bf16(void* out, const void* x, const void* w, const float*
 #define HB_GEMM_CASE(BN_, SWAP_)                                                              \
   return glu ? launch<BN_, SWAP_, EPI_GLU>(x, w, a, w_rows, ldx, ldw, stream)                 \
              : launch<BN_, SWAP_, EPI_STORE>(x, w, a, w_rows, ldx, ldw, stream)
+  if (swap_bn == 0 && k_splits == 1)      // prefill: the persistent kernel
+    return glu ? launch_persistent<EPI_GLU>(x, w, a, w_rows, ldx, ldw, stream)
+               : launch_persistent<EPI_STORE>(x, w, a, w_rows, ldx, ldw, stream);
   switch (swap_bn) {
     case 0: HB_GEMM_CASE(256, false);
     case 16: HB_GEMM_CASE(16, true);
