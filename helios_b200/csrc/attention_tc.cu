@@ -1,0 +1,377 @@
+// Prefill / mixed-batch attention over the paged cache on the 5th-generation tensor
+// cores (tcgen05.mma with the score and output tiles in tensor memory), bfloat16,
+// head sizes 64 and 128.
+//
+// A block takes one KV head and 128 query rows = 128/G consecutive tokens of one request
+// times the G query heads that share the KV head, and walks the keys the rows may see in
+// tiles of 128:
+//     TMA        pages of K and V (boxes of page_size x 64 elements, 128-byte swizzle)
+//                -> a two-stage ring in shared memory
+//     MMA 1      S[128 x 128] = Q K^T           (Q staged once, K-major; K tile K-major)
+//     softmax    8 warps, two threads per row: scale, mask by position (causal, window),
+//                running maximum and sum in float32, P = exp2(.) as bfloat16 into shared
+//                memory in the operand layout
+//     MMA 2      O_tile[128 x hd] = P V         (V tile as an MN-major operand)
+//     the same warps add O_tile into the float32 output they keep in registers, rescaled
+//                when the maximum moved.
+// Formulas: python/helios/exec/paged_attn.py:368-408 (scores * scale, key position > query
+// position masked, softmax in float32, times V), head mapping :248-261.
+//
+// Every mbarrier wait is bounded; on a timeout the block raises the error word, frees its
+// tensor memory and returns.
+#include "tcgen05.cuh"
+
+namespace {
+
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr int TILE = 128;            // query rows and keys per tile
+constexpr int TC_THREADS = 320;      // warp 0: TMA, warp 1: MMA, warps 2-9: softmax
+constexpr int SOFTMAX_THREADS = 256;
+
+struct AttnArgs {
+  __nv_bfloat16* out;
+  const __nv_bfloat16* q;
+  int q_stride;
+  const int* block_table;
+  int bt_stride;
+  const int* q_tiles;       // (request, first local token) per tile
+  const int* cu_tokens;
+  const int* start_pos;
+  int nh, nkv, page_size, window;
+  float scale_log2;
+  int* error;
+};
+
+__device__ __forceinline__ void named_barrier(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+// byte offset of 16-byte chunk `c8` (0..7) of row `row` in a [rows x 128 bytes] tile with
+// the 128-byte swizzle (chunk index XOR row mod 8)
+__device__ __forceinline__ uint32_t swz(int row, int c8) {
+  return (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((c8 ^ (row & 7)) << 4));
+}
+
+template <int HD>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                            AttnArgs a) {
+  constexpr int KH = HD / 64;                       // 64-element halves of the head dimension
+  constexpr int HALF_BYTES = TILE * 128;            // one [128 rows x 64 elements] block
+  constexpr int QKV_BYTES = KH * HALF_BYTES;        // a Q, K or V tile
+  constexpr int P_BYTES = 2 * HALF_BYTES;           // 128 rows x 128 keys
+  constexpr uint32_t TMEM_COLS = 256;
+  constexpr uint32_t S_COL = 0, O_COL = 128;
+
+  extern __shared__ unsigned char smem_raw[];
+  pdl_launch_dependents();
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* aligned = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t q_smem = base;
+  const uint32_t k_smem = q_smem + QKV_BYTES;               // 2 stages
+  const uint32_t v_smem = k_smem + 2 * QKV_BYTES;           // 2 stages
+  const uint32_t p_smem = v_smem + 2 * QKV_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + 5 * QKV_BYTES + P_BYTES);
+  // 0,1: kv full; 2,3: kv empty; 4: q ready; 5: s full; 6: p ready; 7: o full
+  float* l_exchange = reinterpret_cast<float*>(bars + 8);   // [128]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(l_exchange + TILE);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  auto bar = [&](int i) { return smem_u32(bars + i); };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = a.nh / a.nkv;
+  const int TQ = TILE / G;                            // tokens per tile
+  const int kvh = blockIdx.y;
+  const int seq = a.q_tiles[2 * blockIdx.x], t0 = a.q_tiles[2 * blockIdx.x + 1];
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar(0), 1); mbar_init(bar(1), 1);
+    mbar_init(bar(2), 1); mbar_init(bar(3), 1);
+    mbar_init(bar(4), SOFTMAX_THREADS);
+    mbar_init(bar(5), 1);
+    mbar_init(bar(6), SOFTMAX_THREADS);
+    mbar_init(bar(7), 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  pdl_wait();     // everything below reads what earlier kernels wrote
+  const int tok0 = a.cu_tokens[seq], n_tok = a.cu_tokens[seq + 1] - tok0;
+  const int sp = a.start_pos[seq];
+  const int p_first = sp + t0;
+  const int p_last = sp + min(n_tok, t0 + TQ) - 1;
+  const int k_min = (a.window > 0 && p_first - a.window + 1 > 0) ? p_first - a.window + 1 : 0;
+  const int kt_begin = k_min / TILE, kt_end = p_last / TILE + 1;
+  const int n_it = kt_end - kt_begin;
+  const int* table = a.block_table + (size_t)seq * a.bt_stride;
+  const int ps = a.page_size;
+  const int pages_per_tile = TILE / ps;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------------------------------------ TMA producer
+      for (int it = 0; it < n_it; ++it) {
+        const int s = it & 1;
+        if (!mbar_wait(bar(2 + s), ((it >> 1) & 1) ^ 1, abort_flag, a.error, 11)) break;
+        const int key_base = (kt_begin + it) * TILE;
+        // pages that hold at least one key some row may see
+        int first = 0, count = 0;
+        for (int i = 0; i < pages_per_tile; ++i) {
+          const int key0 = key_base + i * ps;
+          const bool valid = key0 + ps - 1 >= k_min && key0 <= p_last;
+          if (valid) { if (count == 0) first = i; ++count; }
+        }
+        mbar_expect_tx(bar(s), (uint32_t)(count * ps * 128 * KH * 2));
+        for (int i = first; i < first + count; ++i) {
+          const int page = table[(key_base + i * ps) / ps];
+          const int row = (page * a.nkv + kvh) * ps;
+          const uint32_t off = (uint32_t)(i * ps * 128);
+#pragma unroll
+          for (int hh = 0; hh < KH; ++hh) {
+            tma_load_2d(k_smem + s * QKV_BYTES + hh * HALF_BYTES + off, &map_k, bar(s), hh * 64, row);
+            tma_load_2d(v_smem + s * QKV_BYTES + hh * HALF_BYTES + off, &map_v, bar(s), hh * 64, row);
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ------------------------------------------------------------ MMA issuer
+      constexpr uint32_t idesc_qk = instr_desc(TILE, TILE);
+      constexpr uint32_t idesc_pv = instr_desc_b_mn(TILE, HD);
+      bool ok = mbar_wait(bar(4), 0, abort_flag, a.error, 12);
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int s = it & 1;
+        ok = mbar_wait(bar(s), (it >> 1) & 1, abort_flag, a.error, 13);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t ks = k_smem + s * QKV_BYTES, vs = v_smem + s * QKV_BYTES;
+#pragma unroll
+        for (int hh = 0; hh < KH; ++hh)
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_bf16(tmem_base + S_COL, smem_desc(q_smem + hh * HALF_BYTES + k * 32),
+                      smem_desc(ks + hh * HALF_BYTES + k * 32), idesc_qk, (hh | k) ? 1u : 0u);
+        umma_commit(bar(5));
+        ok = mbar_wait(bar(6), it & 1, abort_flag, a.error, 14);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_bf16(tmem_base + O_COL, smem_desc(p_smem + (kk >> 2) * HALF_BYTES + (kk & 3) * 32),
+                    smem_desc_mn(vs + kk * 2048, HALF_BYTES, 1024), idesc_pv, kk ? 1u : 0u);
+        umma_commit(bar(2 + s));     // K and V of this stage are free
+        umma_commit(bar(7));         // O_tile complete
+      }
+    }
+    __syncwarp();
+  } else {
+    // -------------------------------------------------------------- softmax warps
+    const int sw = warp - 2;                       // 0..7
+    const int quarter = warp & 3;                  // lanes of tensor memory this warp may read
+    const int half = sw >> 2;                      // which 64 keys / which half of hd this thread owns
+    const int m = quarter * 32 + lane;             // row of the tile
+    const int tl = t0 + m / G, g = m % G;
+    const bool row_valid = tl < n_tok;
+    const int pr = sp + tl;                        // the row's position
+    const int tid = threadIdx.x - 64;
+
+    // stage Q: rows = (token, head) pairs, swizzled K-major; invalid rows are zero
+    for (int idx = tid; idx < TILE * (HD / 8); idx += SOFTMAX_THREADS) {
+      const int row = idx / (HD / 8), c = idx - row * (HD / 8);
+      const int rt = t0 + row / G, rg = row % G;
+      uint4 val = make_uint4(0, 0, 0, 0);
+      if (rt < n_tok)
+        val = *reinterpret_cast<const uint4*>(a.q + (size_t)(tok0 + rt) * a.q_stride +
+                                              (size_t)(kvh * G + rg) * HD + c * 8);
+      st_shared_v4(q_smem + (c >> 3) * HALF_BYTES + swz(row, c & 7), val.x, val.y, val.z, val.w);
+    }
+    fence_async_smem();
+    mbar_arrive(bar(4));
+
+    constexpr int OWN = HD / 2;                    // output columns this thread accumulates
+    float o_reg[OWN];
+#pragma unroll
+    for (int i = 0; i < OWN; ++i) o_reg[i] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    bool ok = true;
+
+    for (int it = 0; it < n_it; ++it) {
+      const int key_base = (kt_begin + it) * TILE;
+      if (!mbar_wait(bar(5), it & 1, abort_flag, a.error, 15)) { ok = false; break; }
+      tc_fence_after();
+      const bool masked_tile = key_base + TILE - 1 > p_first || key_base < k_min ||
+                               (a.window > 0 && key_base <= p_last - a.window);
+      auto visible = [&](int key) {
+        return key <= pr && (a.window <= 0 || key > pr - a.window);
+      };
+      // pass 1: the row's maximum over all 128 keys of the tile
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float v[32];
+        tmem_ld32(lane_addr + S_COL + c * 32, v);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          float x = v[j] * a.scale_log2;
+          if (masked_tile && !visible(key_base + c * 32 + j)) x = -INFINITY;
+          mx = fmaxf(mx, x);
+        }
+      }
+      const float m_new = fmaxf(m_run, mx);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float corr = exp2f(m_run - m_use);
+      m_run = m_new;
+      // pass 2: this thread's 64 keys: probabilities, their sum, and P in the operand layout
+      float sum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        float v[32];
+        tmem_ld32(lane_addr + S_COL + half * 64 + c * 32, v);
+        uint32_t packed[16];
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          float x0 = v[j] * a.scale_log2, x1 = v[j + 1] * a.scale_log2;
+          if (masked_tile) {
+            const int key = key_base + half * 64 + c * 32 + j;
+            if (!visible(key)) x0 = -INFINITY;
+            if (!visible(key + 1)) x1 = -INFINITY;
+          }
+          const float p0 = exp2f(x0 - m_use), p1 = exp2f(x1 - m_use);
+          sum += p0 + p1;
+          __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+          packed[j >> 1] = *reinterpret_cast<uint32_t*>(&pk);
+        }
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4)
+          st_shared_v4(p_smem + half * HALF_BYTES + swz(m, c * 4 + q4), packed[4 * q4], packed[4 * q4 + 1],
+                       packed[4 * q4 + 2], packed[4 * q4 + 3]);
+      }
+      l_run = l_run * corr + sum;
+      // V rows of keys past the last position (unwritten slots, pages that were not copied)
+      // must not be NaN or Inf when they meet their zero probabilities
+      {
+        const int s = it & 1;
+        auto zero_rows = [&](int row_begin, int row_end) {
+          for (int idx = tid + row_begin * KH * 8; idx < row_end * KH * 8; idx += SOFTMAX_THREADS) {
+            const int row = idx / (KH * 8), rest = idx - row * (KH * 8);
+            st_shared_v4(v_smem + s * QKV_BYTES + (rest >> 3) * HALF_BYTES + row * 128 + (rest & 7) * 16,
+                         0, 0, 0, 0);
+          }
+        };
+        if (key_base + TILE - 1 > p_last) zero_rows(p_last + 1 - key_base, TILE);
+        // pages wholly before the window of the first row were not copied either
+        if (key_base < k_min) zero_rows(0, ((k_min - key_base) / ps) * ps);
+      }
+      tc_fence_before();
+      fence_async_smem();
+      mbar_arrive(bar(6));
+      // O_tile
+      if (!mbar_wait(bar(7), it & 1, abort_flag, a.error, 16)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < OWN / 32; ++c) {
+        float v[32];
+        tmem_ld32(lane_addr + O_COL + half * OWN + c * 32, v);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) o_reg[c * 32 + j] = o_reg[c * 32 + j] * corr + v[j];
+      }
+      tc_fence_before();
+    }
+
+    // the two threads of a row add their sums
+    if (half == 1) l_exchange[m] = l_run;
+    named_barrier(1, SOFTMAX_THREADS);
+    if (half == 0) {
+      const float other = l_exchange[m];
+      l_exchange[m] = l_run;
+      l_run += other;
+    }
+    named_barrier(1, SOFTMAX_THREADS);
+    if (half == 1) l_run += l_exchange[m];
+    if (ok && row_valid && !*abort_flag) {
+      const float inv = 1.f / l_run;
+      __nv_bfloat16* dst = a.out + ((size_t)(tok0 + tl) * a.nh + (kvh * G + g)) * HD + half * OWN;
+#pragma unroll
+      for (int j = 0; j < OWN; j += 8) {
+        uint32_t w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          __nv_bfloat162 pk = __floats2bfloat162_rn(o_reg[j + 2 * e] * inv, o_reg[j + 2 * e + 1] * inv);
+          w[e] = *reinterpret_cast<uint32_t*>(&pk);
+        }
+        *reinterpret_cast<uint4*>(dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(100);
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int HD>
+int launch_tc(const AttnArgs& a, const void* k_pages, const void* v_pages, long long page_rows, int n_tiles,
+              cudaStream_t stream) {
+  constexpr int KH = HD / 64;
+  constexpr size_t SMEM = 5 * (size_t)KH * TILE * 128 + 2 * TILE * 128 + 1024 + 1024;
+  CUtensorMap map_k, map_v;
+  if (!make_map(&map_k, k_pages, (uint64_t)page_rows, HD, HD, a.page_size)) return HB_LAUNCH_FAILED;
+  if (!make_map(&map_v, v_pages, (uint64_t)page_rows, HD, HD, a.page_size)) return HB_LAUNCH_FAILED;
+  auto kernel = attention_prefill_tc_kernel<HD>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM) != cudaSuccess)
+      return HB_LAUNCH_FAILED;
+    configured = true;
+  }
+  hb_launch(kernel, dim3(n_tiles, a.nkv), dim3(TC_THREADS), SMEM, stream, map_k, map_v, a);
+  return hb_check_launch();
+}
+
+}  // namespace
+
+// q_tiles: (request, first local token) for tiles of 128 / (nh / nkv) tokens.  Needs hd in
+// {64, 128}, a group size that divides 128, and a page size that is a multiple of 8 and
+// divides 128.  num_pages: pages in k_pages / v_pages ([pages, nkv, page_size, hd]).
+HB_EXPORT int hb_attention_prefill_tc(void* out, const void* q, int q_stride, const void* k_pages,
+                                      const void* v_pages, long long num_pages, const int* block_table,
+                                      int bt_stride, const int* q_tiles, int n_tiles, const int* cu_tokens,
+                                      const int* start_pos, int nh, int nkv, int hd, int page_size, int window,
+                                      float scale, int* error, cudaStream_t stream) {
+  if (n_tiles <= 0) return HB_OK;
+  if (nkv <= 0 || nh % nkv != 0 || error == nullptr) return HB_BAD_ARGUMENT;
+  const int G = nh / nkv;
+  if (G > TILE || TILE % G != 0) return HB_BAD_ARGUMENT;
+  if (page_size < 8 || page_size % 8 != 0 || TILE % page_size != 0) return HB_BAD_ARGUMENT;
+  if (((uintptr_t)q & 15) || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15) || (q_stride & 7))
+    return HB_BAD_ARGUMENT;
+  AttnArgs a;
+  a.out = (__nv_bfloat16*)out; a.q = (const __nv_bfloat16*)q; a.q_stride = q_stride;
+  a.block_table = block_table; a.bt_stride = bt_stride; a.q_tiles = q_tiles; a.cu_tokens = cu_tokens;
+  a.start_pos = start_pos; a.nh = nh; a.nkv = nkv; a.page_size = page_size; a.window = window;
+  a.scale_log2 = scale * LOG2E; a.error = error;
+  const long long rows = num_pages * nkv * page_size;
+  if (hd == 128) return launch_tc<128>(a, k_pages, v_pages, rows, n_tiles, stream);
+  if (hd == 64) return launch_tc<64>(a, k_pages, v_pages, rows, n_tiles, stream);
+  return HB_BAD_ARGUMENT;
+}

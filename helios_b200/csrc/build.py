@@ -33,12 +33,13 @@ LIBRARIES: Dict[str, str] = {
     "elementwise": "elementwise.cu",
     "attention_generic": "attention_generic.cu",
     "attention_bf16": "attention_bf16.cu",
+    "attention_tc": "attention_tc.cu",
     "gemm_f32": "gemm_f32.cu",
     "gemm_bf16": "gemm_bf16.cu",
     "gemm_bf16_noalloc": "gemm_bf16_noalloc.cu",
     "sampling": "sampling.cu",
 }
-_HEADERS = ["common.cuh"]
+_HEADERS = ["common.cuh", "tcgen05.cuh"]
 # further files a library's source includes
 _INCLUDES: Dict[str, List[str]] = {"gemm_bf16_noalloc": ["gemm_bf16.cu", "gemm_bf16_noalloc.h"]}
 

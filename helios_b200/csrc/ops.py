@@ -490,6 +490,8 @@ def linear_logits(rows: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
 
 
 TILED_HEAD_DIMS = (32, 64, 96, 128)
+#: use the tcgen05 attention kernel for batches with prompt portions where its sizes fit
+ATTENTION_TCGEN05 = True
 _SM_COUNT = 148
 
 
@@ -594,9 +596,51 @@ def attention_prefill_bf16(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: to
     return out
 
 
-def query_tiles(tokens_per_seq, tile: int, device) -> torch.Tensor:
-    """int32 [tiles, 2] on ``device``: (request, first local token) of every tile."""
+def tc_attention_supported(num_heads: int, num_kv_heads: int, head_dim: int, page_size: int) -> bool:
+    """Sizes the tcgen05 prefill attention kernel takes."""
+    group = num_heads // max(1, num_kv_heads)
+    return (head_dim in (64, 128) and num_heads % num_kv_heads == 0 and group <= 128
+            and 128 % group == 0 and page_size >= 8 and page_size % 8 == 0 and 128 % page_size == 0)
+
+
+def attention_prefill_tc(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                         block_table: torch.Tensor, q_tiles: torch.Tensor, cu_tokens: torch.Tensor,
+                         start_pos: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
+                         page_size: int, window: Optional[int], scale: float) -> torch.Tensor:
+    """Attention of query tiles over the cache on tcgen05 tensor cores; ``q_tiles`` is int32
+    [tiles, 2] = (request, first local token) for tiles of ``128 // (nh // nkv)`` tokens."""
+    _check(qkv, "qkv", torch.bfloat16, 2)
+    _check(k_pages, "k_pages", torch.bfloat16, 4)
+    _check(v_pages, "v_pages", torch.bfloat16, 4)
+    _check(block_table, "block_table", torch.int32, 2)
+    _check(q_tiles, "q_tiles", torch.int32, 2)
+    _check(cu_tokens, "cu_tokens", torch.int32, 1)
+    _check(start_pos, "start_pos", torch.int32, 1)
+    if not tc_attention_supported(num_heads, num_kv_heads, head_dim, page_size):
+        raise KernelError(f"the tcgen05 attention kernel does not take {num_heads} heads on "
+                          f"{num_kv_heads} KV heads, head_dim {head_dim}, page size {page_size}")
+    if tuple(k_pages.shape[1:]) != (num_kv_heads, page_size, head_dim) or k_pages.shape != v_pages.shape:
+        raise KernelError(f"cache pages have shape {tuple(k_pages.shape)}, expected "
+                          f"[pages, {num_kv_heads}, {page_size}, {head_dim}]")
+    T = qkv.shape[0]
+    out = torch.empty((T, num_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
+    _scratch, _tickets, err = _gemm_workspace(qkv.device)
+    f = _fn("attention_tc", "hb_attention_prefill_tc",
+            [c_void_p, c_void_p, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_void_p,
+             c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p])
+    _run(f(_p(out), _p(qkv), qkv.shape[1], _p(k_pages), _p(v_pages), k_pages.shape[0], _p(block_table),
+           block_table.shape[1], _p(q_tiles), q_tiles.shape[0], _p(cu_tokens), _p(start_pos), num_heads,
+           num_kv_heads, head_dim, page_size, int(window or 0), float(scale), _p(err), _stream()),
+         "attention_prefill_tc")
+    return out
+
+
+def query_tiles(tokens_per_seq, tile: int, device, start_positions=None) -> torch.Tensor:
+    """int32 [tiles, 2] on ``device``: (request, first local token) of every tile.  With
+    ``start_positions`` the tiles that see the most keys come first (they run longest)."""
     rows = [(i, t0) for i, n in enumerate(tokens_per_seq) for t0 in range(0, n, tile)]
+    if start_positions is not None:
+        rows.sort(key=lambda r: -(start_positions[r[0]] + r[1]))
     host = torch.tensor(rows, dtype=torch.int32).reshape(-1, 2)
     if torch.device(device).type == "cuda":
         host = host.pin_memory()
@@ -618,6 +662,18 @@ def attention(ctx, qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
             return attention_decode_bf16(qkv, k_pages, v_pages, block_table, ctx.positions,
                                          num_heads, num_kv_heads, head_dim, page_size, window,
                                          scale, splits)
+        if (ATTENTION_TCGEN05 and ctx.max_tokens_per_seq >= 16
+                and tc_attention_supported(num_heads, num_kv_heads, head_dim, page_size)):
+            tile = 128 // (num_heads // num_kv_heads)
+            key = ("q_tiles_tc", tile)
+            tiles = ctx.extras.get(key)
+            if tiles is None:
+                tiles = query_tiles([s.num_tokens for s in ctx.seqs], tile, qkv.device,
+                                    [s.start_pos for s in ctx.seqs])
+                ctx.extras[key] = tiles
+            return attention_prefill_tc(qkv, k_pages, v_pages, block_table, tiles, ctx.cu_tokens,
+                                        ctx.start_pos, num_heads, num_kv_heads, head_dim, page_size,
+                                        window, scale)
         _heads, subtiles = prefill_tiling(num_heads, num_kv_heads)
         key = ("q_tiles", 16 * subtiles)
         tiles = ctx.extras.get(key)

@@ -336,3 +336,30 @@ def test_sampled_frequencies_follow_the_distribution():
     got = _sample(logits.repeat(R, 1), [1.0] * R, [0] * R, [1.0] * R, [5] * R, list(range(R)))
     freq = torch.bincount(torch.tensor(got), minlength=5).double() / R
     assert (freq - torch.softmax(logits[0].double(), -1)).abs().max() < 0.03
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page", [(32, 8, 128, 16), (8, 8, 128, 8), (16, 2, 64, 32), (4, 1, 64, 128),
+                                            (16, 1, 128, 64), (2, 1, 64, 16)])
+@pytest.mark.parametrize("window", [None, 100, 300])
+def test_prefill_attention_tcgen05(nh, nkv, hd, page, window):
+    """The tensor-memory attention kernel: ragged requests, portions that start deep in the
+    cache, single tokens beside them, scattered and poisoned pages."""
+    seqs = CASES + [(0, 300), (190, 70), (1000, 17), (500, 129), (127, 1), (128, 128)]
+    case = make_paged_case(seqs, nh, nkv, hd, page, torch.bfloat16, DEV, seed=nh * hd + page)
+    scale = 1.0 / math.sqrt(hd)
+    tiles = ops().query_tiles([n for _, n in seqs], 128 // (nh // nkv), DEV, [a for a, _ in seqs])
+    out = ops().attention_prefill_tc(case.qkv, case.k_pages, case.v_pages, case.table, tiles,
+                                     case.cu_tokens, case.start_pos, nh, nkv, hd, page, window, scale)
+    ops().check_kernel_errors()
+    torch.testing.assert_close(out.cpu().double(), dense_attention(case, scale, window), atol=2e-2, rtol=2e-2)
+
+
+def test_tcgen05_attention_refuses_sizes_it_does_not_take():
+    assert not ops().tc_attention_supported(28, 4, 128, 16)      # groups of 7 do not fill 128 rows
+    assert not ops().tc_attention_supported(32, 8, 96, 16)
+    assert not ops().tc_attention_supported(32, 8, 128, 5)
+    case = make_paged_case([(0, 20)], 6, 2, 64, 16, torch.bfloat16, DEV)
+    tiles = ops().query_tiles([20], 42, DEV)
+    with pytest.raises(ops().KernelError):
+        ops().attention_prefill_tc(case.qkv, case.k_pages, case.v_pages, case.table, tiles, case.cu_tokens,
+                                   case.start_pos, 6, 2, 64, 16, None, 0.125)
