@@ -20,12 +20,15 @@
 // Every mbarrier wait is bounded; on a timeout the block raises the error word, frees its
 // tensor memory and returns.
 #include "tcgen05.cuh"
+#ifdef HB_ATTN_TIMING
+#include <cstdio>
+#endif
 
 namespace {
 
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr int TILE = 128;            // query rows and keys per tile
-constexpr int TC_THREADS = 320;      // warp 0: TMA, warp 1: MMA, warps 2-9: softmax
+constexpr int TC_THREADS = 352;      // warp 0: TMA of K, warp 1: MMA, warps 2-9: softmax, warp 10: TMA of V
 constexpr int SOFTMAX_THREADS = 256;
 
 struct AttnArgs {
@@ -42,6 +45,11 @@ struct AttnArgs {
   int* error;
 };
 
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ void named_barrier(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
@@ -74,9 +82,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const uint32_t v_smem = k_smem + 2 * QKV_BYTES;           // 2 stages
   const uint32_t p_smem = v_smem + 2 * QKV_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + 5 * QKV_BYTES + P_BYTES);
-  // 0,1: kv full; 2,3: kv empty; 4: q ready; 5: s full; 6: p ready; 7: o full
-  float* l_exchange = reinterpret_cast<float*>(bars + 8);   // [128]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(l_exchange + TILE);
+  // 0,1: K full; 2,3: K empty; 4: q ready; 5: s full; 6: p ready; 7: o full; 8: s free;
+  // 9,10: V full; 11,12: V empty
+  float* l_exchange = reinterpret_cast<float*>(bars + 14);  // [128]
+  float* max_exchange = l_exchange + TILE;                  // [2 tiles][2 halves][128]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(max_exchange + 4 * TILE);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   auto bar = [&](int i) { return smem_u32(bars + i); };
 
@@ -93,6 +103,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     mbar_init(bar(5), 1);
     mbar_init(bar(6), SOFTMAX_THREADS);
     mbar_init(bar(7), 1);
+    mbar_init(bar(8), SOFTMAX_THREADS);
+    mbar_init(bar(9), 1); mbar_init(bar(10), 1);
+    mbar_init(bar(11), 1); mbar_init(bar(12), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -117,30 +130,43 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const int ps = a.page_size;
   const int pages_per_tile = TILE / ps;
 
-  if (warp == 0) {
-    if (lane == 0) {
-      // ------------------------------------------------------------ TMA producer
+  if (warp == 0 || warp == 10) {
+    // ---------------------------------------------------------------- TMA producers
+    // Warp 0 copies the K tiles, warp 10 the V tiles, each through a ring of two stages of
+    // its own: a K stage is free again as soon as the scores of its tile are computed, long
+    // before its V stage, so the next keys arrive while the softmax of this tile still runs.
+    // Lane i looks up and copies page i of the tile (the look-ups of a tile's pages would
+    // otherwise wait for one another); lane 0 waits for the stage and announces the bytes.
+    {
+      const bool is_v = warp == 10;
+      const CUtensorMap* map = is_v ? &map_v : &map_k;
+      const uint32_t ring = is_v ? v_smem : k_smem;
+      const int full0 = is_v ? 9 : 0, empty0 = is_v ? 11 : 2;
       for (int it = 0; it < n_it; ++it) {
         const int s = it & 1;
-        if (!mbar_wait(bar(2 + s), ((it >> 1) & 1) ^ 1, abort_flag, a.error, 11)) break;
         const int key_base = (kt_begin + it) * TILE;
-        // pages that hold at least one key some row may see
+        // pages that hold at least one key some row may see (a contiguous run)
         int first = 0, count = 0;
         for (int i = 0; i < pages_per_tile; ++i) {
           const int key0 = key_base + i * ps;
           const bool valid = key0 + ps - 1 >= k_min && key0 <= p_last;
           if (valid) { if (count == 0) first = i; ++count; }
         }
-        mbar_expect_tx(bar(s), (uint32_t)(count * ps * 128 * KH * 2));
-        for (int i = first; i < first + count; ++i) {
-          const int page = table[(key_base + i * ps) / ps];
-          const int row = (page * a.nkv + kvh) * ps;
-          const uint32_t off = (uint32_t)(i * ps * 128);
+        const bool mine = lane >= first && lane < first + count;
+        int row = 0;
+        if (mine) row = (table[(key_base + lane * ps) / ps] * a.nkv + kvh) * ps;    // before the wait
+        int go = 1;
+        if (lane == 0) {
+          go = mbar_wait(bar(empty0 + s), ((it >> 1) & 1) ^ 1, abort_flag, a.error, 11) ? 1 : 0;
+          if (go) mbar_expect_tx(bar(full0 + s), (uint32_t)(count * ps * 128 * KH));
+        }
+        go = __shfl_sync(0xffffffffu, go, 0);
+        if (!go) break;
+        if (mine) {
+          const uint32_t off = (uint32_t)(lane * ps * 128);
 #pragma unroll
-          for (int hh = 0; hh < KH; ++hh) {
-            tma_load_2d(k_smem + s * QKV_BYTES + hh * HALF_BYTES + off, &map_k, bar(s), hh * 64, row);
-            tma_load_2d(v_smem + s * QKV_BYTES + hh * HALF_BYTES + off, &map_v, bar(s), hh * 64, row);
-          }
+          for (int hh = 0; hh < KH; ++hh)
+            tma_load_2d(ring + s * QKV_BYTES + hh * HALF_BYTES + off, map, bar(full0 + s), hh * 64, row);
         }
       }
     }
@@ -150,35 +176,69 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       // ------------------------------------------------------------ MMA issuer
       constexpr uint32_t idesc_qk = instr_desc(TILE, TILE);
       constexpr uint32_t idesc_pv = instr_desc_b_mn(TILE, HD);
+      // S(i+1) = Q K(i+1)^T is issued as soon as the softmax warps have taken S(i) into
+      // registers, so that it runs under their exponentials; O_tile(i) = P(i) V(i) follows
+      // when P(i) is written.
       bool ok = mbar_wait(bar(4), 0, abort_flag, a.error, 12);
-      for (int it = 0; it < n_it && ok; ++it) {
+      auto issue_qk = [&](int it) {
         const int s = it & 1;
-        ok = mbar_wait(bar(s), (it >> 1) & 1, abort_flag, a.error, 13);
-        if (!ok) break;
+        if (!mbar_wait(bar(s), (it >> 1) & 1, abort_flag, a.error, 13)) return false;
         tc_fence_after();
-        const uint32_t ks = k_smem + s * QKV_BYTES, vs = v_smem + s * QKV_BYTES;
+        const uint32_t ks = k_smem + s * QKV_BYTES;
 #pragma unroll
         for (int hh = 0; hh < KH; ++hh)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
             umma_bf16(tmem_base + S_COL, smem_desc(q_smem + hh * HALF_BYTES + k * 32),
                       smem_desc(ks + hh * HALF_BYTES + k * 32), idesc_qk, (hh | k) ? 1u : 0u);
+        umma_commit(bar(2 + s));      // the K stage is free once the scores are there
         umma_commit(bar(5));
+        return true;
+      };
+      if (ok && n_it > 0) ok = issue_qk(0);
+#ifdef HB_ATTN_TIMING
+      long long mt[4] = {0, 0, 0, 0};
+      long long mprev = clock64();
+#define HB_MTICK(i) { const long long now = clock64(); mt[i] += now - mprev; mprev = now; }
+#else
+#define HB_MTICK(i)
+#endif
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int s = it & 1;
+        if (it + 1 < n_it) {
+          ok = mbar_wait(bar(8), it & 1, abort_flag, a.error, 17);     // S(it) is in registers
+          if (!ok) break;
+          tc_fence_after();
+          HB_MTICK(0)
+          ok = issue_qk(it + 1);
+          if (!ok) break;
+          HB_MTICK(1)
+        }
+        ok = mbar_wait(bar(9 + s), (it >> 1) & 1, abort_flag, a.error, 18);     // V(it) has arrived
+        if (!ok) break;
+        HB_MTICK(2)
         ok = mbar_wait(bar(6), it & 1, abort_flag, a.error, 14);
         if (!ok) break;
+        HB_MTICK(3)
         tc_fence_after();
+        const uint32_t vs = v_smem + s * QKV_BYTES;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
           umma_bf16(tmem_base + O_COL, smem_desc(p_smem + (kk >> 2) * HALF_BYTES + (kk & 3) * 32),
                     smem_desc_mn(vs + kk * 2048, HALF_BYTES, 1024), idesc_pv, kk ? 1u : 0u);
-        umma_commit(bar(2 + s));     // K and V of this stage are free
+        umma_commit(bar(11 + s));    // the V stage is free
         umma_commit(bar(7));         // O_tile complete
       }
+#ifdef HB_ATTN_TIMING
+      if (blockIdx.x == 0 && blockIdx.y == 0)
+        printf("mma thread per tile: wait s_free %lld  issue_qk (wait K) %lld  wait V %lld  wait p_ready %lld\n",
+               mt[0] / n_it, mt[1] / n_it, mt[2] / n_it, mt[3] / n_it);
+#endif
     }
     __syncwarp();
   } else {
     // -------------------------------------------------------------- softmax warps
-    const int sw = warp - 2;                       // 0..7
+    const int sw = warp - 2;                       // 0..7 (warps 2..9)
     const int quarter = warp & 3;                  // lanes of tensor memory this warp may read
     const int half = sw >> 2;                      // which 64 keys / which half of hd this thread owns
     const int m = quarter * 32 + lane;             // row of the tile
@@ -208,57 +268,83 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     bool ok = true;
 
+#ifdef HB_ATTN_TIMING
+    long long tphase[6] = {0, 0, 0, 0, 0, 0};
+    long long tprev = clock64();
+#define HB_TICK(i) { const long long now = clock64(); tphase[i] += now - tprev; tprev = now; }
+#else
+#define HB_TICK(i)
+#endif
     for (int it = 0; it < n_it; ++it) {
       const int key_base = (kt_begin + it) * TILE;
       if (!mbar_wait(bar(5), it & 1, abort_flag, a.error, 15)) { ok = false; break; }
       tc_fence_after();
+      HB_TICK(0)
       const bool masked_tile = key_base + TILE - 1 > p_first || key_base < k_min ||
                                (a.window > 0 && key_base <= p_last - a.window);
-      auto visible = [&](int key) {
-        return key <= pr && (a.window <= 0 || key > pr - a.window);
-      };
-      // pass 1: the row's maximum over all 128 keys of the tile
-      float mx = -INFINITY;
+      // this thread's 64 scores stay in registers; the maximum goes over to the other
+      // thread of the row through shared memory
+      float sv[64];
+      {
+        float v0[32], v1[32];
+        tmem_ld32(lane_addr + S_COL + half * 64, v0);
+        tmem_ld32(lane_addr + S_COL + half * 64 + 32, v1);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        float v[32];
-        tmem_ld32(lane_addr + S_COL + c * 32, v);
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          float x = v[j] * a.scale_log2;
-          if (masked_tile && !visible(key_base + c * 32 + j)) x = -INFINITY;
-          mx = fmaxf(mx, x);
-        }
+        for (int j = 0; j < 32; ++j) { sv[j] = v0[j]; sv[32 + j] = v1[j]; }
       }
+      tc_fence_before();
+      mbar_arrive(bar(8));        // the score tile may be overwritten
+      if (masked_tile) {
+        // columns of this thread's 64 keys the row may see: [lo, hi]
+        const int col0 = key_base + half * 64;
+        const int hi = pr - col0;
+        const int lo = (a.window > 0 ? pr - a.window + 1 : 0) - col0;
+#pragma unroll
+        for (int j = 0; j < 64; ++j)
+          if (j < lo || j > hi) sv[j] = -INFINITY;
+      }
+      float mx = sv[0];
+#pragma unroll
+      for (int j = 1; j < 64; ++j) mx = fmaxf(mx, sv[j]);
+      max_exchange[((it & 1) * 2 + half) * TILE + m] = mx;
+      named_barrier(2 + quarter, 64);
+      mx = fmaxf(mx, max_exchange[((it & 1) * 2 + (half ^ 1)) * TILE + m]) * a.scale_log2;
+      HB_TICK(1)
       const float m_new = fmaxf(m_run, mx);
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float corr = exp2f(m_run - m_use);
+      const float corr = fast_exp2(m_run - m_use);
       m_run = m_new;
-      // pass 2: this thread's 64 keys: probabilities, their sum, and P in the operand layout
+      // O_tile of the tile before was computed under the work above.  The output in
+      // registers lacks it and is relative to the old maximum: add it and rescale, before P,
+      // which that product still read, is overwritten.
+      if (it > 0) {
+        if (!mbar_wait(bar(7), (it - 1) & 1, abort_flag, a.error, 16)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < OWN / 32; ++c) {
+          float v[32];
+          tmem_ld32(lane_addr + O_COL + half * OWN + c * 32, v);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o_reg[c * 32 + j] = (o_reg[c * 32 + j] + v[j]) * corr;
+        }
+        tc_fence_before();
+      }
+      HB_TICK(4)
       float sum = 0.f;
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        float v[32];
-        tmem_ld32(lane_addr + S_COL + half * 64 + c * 32, v);
-        uint32_t packed[16];
+      for (int c8 = 0; c8 < 8; ++c8) {
+        uint32_t packed[4];
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          float x0 = v[j] * a.scale_log2, x1 = v[j + 1] * a.scale_log2;
-          if (masked_tile) {
-            const int key = key_base + half * 64 + c * 32 + j;
-            if (!visible(key)) x0 = -INFINITY;
-            if (!visible(key + 1)) x1 = -INFINITY;
-          }
-          const float p0 = exp2f(x0 - m_use), p1 = exp2f(x1 - m_use);
+        for (int e = 0; e < 4; ++e) {
+          const float p0 = fast_exp2(fmaf(sv[c8 * 8 + 2 * e], a.scale_log2, -m_use));
+          const float p1 = fast_exp2(fmaf(sv[c8 * 8 + 2 * e + 1], a.scale_log2, -m_use));
           sum += p0 + p1;
           __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
-          packed[j >> 1] = *reinterpret_cast<uint32_t*>(&pk);
+          packed[e] = *reinterpret_cast<uint32_t*>(&pk);
         }
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4)
-          st_shared_v4(p_smem + half * HALF_BYTES + swz(m, c * 4 + q4), packed[4 * q4], packed[4 * q4 + 1],
-                       packed[4 * q4 + 2], packed[4 * q4 + 3]);
+        st_shared_v4(p_smem + half * HALF_BYTES + swz(m, c8), packed[0], packed[1], packed[2], packed[3]);
       }
+      HB_TICK(2)
       l_run = l_run * corr + sum;
       // V rows of keys past the last position (unwritten slots, pages that were not copied)
       // must not be NaN or Inf when they meet their zero probabilities
@@ -271,25 +357,41 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                          0, 0, 0, 0);
           }
         };
-        if (key_base + TILE - 1 > p_last) zero_rows(p_last + 1 - key_base, TILE);
-        // pages wholly before the window of the first row were not copied either
-        if (key_base < k_min) zero_rows(0, ((k_min - key_base) / ps) * ps);
+        if (key_base + TILE - 1 > p_last || key_base < k_min) {
+          // the copies of this V tile must have landed first: they bring whole pages
+          if (!mbar_wait(bar(9 + s), (it >> 1) & 1, abort_flag, a.error, 19)) { ok = false; break; }
+          if (key_base + TILE - 1 > p_last) zero_rows(p_last + 1 - key_base, TILE);
+          // pages wholly before the window of the first row were not copied either
+          if (key_base < k_min) zero_rows(0, ((k_min - key_base) / ps) * ps);
+        }
       }
       tc_fence_before();
       fence_async_smem();
       mbar_arrive(bar(6));
-      // O_tile
-      if (!mbar_wait(bar(7), it & 1, abort_flag, a.error, 16)) { ok = false; break; }
-      tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < OWN / 32; ++c) {
-        float v[32];
-        tmem_ld32(lane_addr + O_COL + half * OWN + c * 32, v);
-#pragma unroll
-        for (int j = 0; j < 32; ++j) o_reg[c * 32 + j] = o_reg[c * 32 + j] * corr + v[j];
-      }
-      tc_fence_before();
+      HB_TICK(3)
+      HB_TICK(5)      // O_tile(it) is added at the start of the next tile's work
     }
+    if (ok && n_it > 0) {
+      if (mbar_wait(bar(7), (n_it - 1) & 1, abort_flag, a.error, 16)) {
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < OWN / 32; ++c) {
+          float v[32];
+          tmem_ld32(lane_addr + O_COL + half * OWN + c * 32, v);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o_reg[c * 32 + j] += v[j];
+        }
+        tc_fence_before();
+      } else {
+        ok = false;
+      }
+    }
+#ifdef HB_ATTN_TIMING
+    if (threadIdx.x == 64 && blockIdx.x == 0 && blockIdx.y == 0)
+      printf("tiles %d: wait_s %lld  pass1 %lld  pass2 %lld  zero+arrive %lld  wait_o %lld  acc %lld (cycles per tile)\n",
+             n_it, tphase[0] / n_it, tphase[1] / n_it, tphase[2] / n_it, tphase[3] / n_it, tphase[4] / n_it,
+             tphase[5] / n_it);
+#endif
 
     // the two threads of a row add their sums
     if (half == 1) l_exchange[m] = l_run;
@@ -333,7 +435,7 @@ template <int HD>
 int launch_tc(const AttnArgs& a, const void* k_pages, const void* v_pages, long long page_rows, int n_tiles,
               cudaStream_t stream) {
   constexpr int KH = HD / 64;
-  constexpr size_t SMEM = 5 * (size_t)KH * TILE * 128 + 2 * TILE * 128 + 1024 + 1024;
+  constexpr size_t SMEM = 5 * (size_t)KH * TILE * 128 + 2 * TILE * 128 + 1024 + 4096;
   CUtensorMap map_k, map_v;
   if (!make_map(&map_k, k_pages, (uint64_t)page_rows, HD, HD, a.page_size)) return HB_LAUNCH_FAILED;
   if (!make_map(&map_v, v_pages, (uint64_t)page_rows, HD, HD, a.page_size)) return HB_LAUNCH_FAILED;

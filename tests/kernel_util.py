@@ -80,5 +80,5 @@ def step_ctx(case):
     return SimpleNamespace(
         seq_of_token=case.seq_of_token, positions=case.positions, cu_tokens=case.cu_tokens,
         start_pos=case.start_pos, num_seqs=len(case.seqs), decode_only=(n_max == 1),
-        max_context_len=max(a + n for a, n in case.seqs),
-        seqs=[SimpleNamespace(num_tokens=n) for _, n in case.seqs], extras={})
+        max_tokens_per_seq=n_max, max_context_len=max(a + n for a, n in case.seqs),
+        seqs=[SimpleNamespace(num_tokens=n, start_pos=a) for a, n in case.seqs], extras={})

@@ -184,8 +184,8 @@ def test_one_far_key_among_hundreds_and_the_windows_edge(dtype, hd):
     scale = 1.0 / math.sqrt(hd)
     for far, window, seen in [(3, None, True), (ctx - W, W, True), (ctx - W - 1, W, False),
                               (ctx - 1, W, True), (page * 7 - 1, None, True), (page * 7, None, True)]:
-        for mode in ("decode", "portion"):
-            seqs = [(ctx - 1, 1)] if mode == "decode" else [(ctx - 5, 5)]
+        for mode in ("decode", "portion", "long portion"):
+            seqs = {"decode": [(ctx - 1, 1)], "portion": [(ctx - 5, 5)], "long portion": [(ctx - 40, 40)]}[mode]
             case = make_paged_case(seqs, nh, nkv, hd, page, dtype, DEV, seed=far)
             q, k, v, a = case.dense[0]
             # the last query points along e0, the far key too; its value is a marker
