@@ -422,15 +422,25 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
     return out
 
 
+#: Plain products (no bias, bfloat16 out) of more than 128 tokens go to the library
+#: (cuBLAS through torch), which the reference uses for every product
+#: (python/helios/exec/model.py:170-181) and which, with its two-SM tiles, is still ahead
+#: of this package's one-SM tcgen05 kernel at these sizes (1.5 against 1.2 PFLOP/s at 2,048
+#: tokens).  Decode-sized and fused products (bias, SwiGLU, float32 logits) always run
+#: on this package's kernel.  Set False to run everything on it.
+GEMM_LIBRARY_FOR_LARGE_PLAIN = True
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """y = x W^T + b.  float32: this package's FMA kernel.  bfloat16: the tcgen05 kernel;
-    a K that is no multiple of 8 goes to the library product (cuBLAS through torch), as the
-    reference engine uses one for all its projections (python/helios/exec/model.py:170-181)."""
+    """y = x W^T + b.  float32: this package's FMA kernel.  bfloat16: the tcgen05 kernel
+    (see GEMM_LIBRARY_FOR_LARGE_PLAIN for the one case that goes to the library); a K that
+    is no multiple of 8 goes to the library too, as TMA needs 16-byte rows."""
     if x.dtype == torch.float32:
         return linear_f32(x, weight, bias)
     _check(x, "x", torch.bfloat16, 2)
     _check(weight, "weight", torch.bfloat16, 2)
-    if tc_gemm_supported(x, weight):
+    if tc_gemm_supported(x, weight) and not (GEMM_LIBRARY_FOR_LARGE_PLAIN and bias is None
+                                             and x.shape[0] > 128):
         return linear_bf16(x, weight, bias)
     b = None if bias is None else bias.to(torch.bfloat16)
     return torch.nn.functional.linear(x, weight, b)
