@@ -19,6 +19,9 @@
 // mbarrier is bounded: when it runs out the block raises an error word in global
 // memory, frees its tensor memory and returns.
 #include "tcgen05.cuh"
+#ifdef HB_GEMM_TIMING
+#include <cstdio>
+#endif
 
 #ifndef HB_SWAP_BUDGET_KB
 #define HB_SWAP_BUDGET_KB 108
@@ -459,45 +462,26 @@ gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
   if (warp == 0) {
     if (lane == 0) {
       // ---------------------------------------------------------- TMA producer
-      // `it` counts k-blocks over all of this block's tiles; stage = it % P_STAGES.
-      const int my_tiles = blockIdx.x < n_tiles ? (n_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
-      const long long total = (long long)my_tiles * kb_total;
-      auto coords = [&](long long it, int& k0, int& a_row, int& b_row0, int& b_row1) {
-        const int j = (int)(it / kb_total), kb = (int)(it - (long long)j * kb_total);
-        const int q = blockIdx.x + j * gridDim.x;
-        const int tile_m = q % tiles_m, tile_n = q / tiles_m;
-        k0 = kb * BK;
-        a_row = tile_m * BM;
-        b_row0 = tile_n * RESULT_COLS;
-        b_row1 = args.glu_offset + tile_n * RESULT_COLS;
-      };
-      auto load_weights = [&](long long it, int s) {
-        int k0, a_row, b_row0, b_row1;
-        coords(it, k0, a_row, b_row0, b_row1);
-        const uint32_t sb = base + s * P_STAGE_BYTES + P_A_BYTES;
-        tma_load_2d(sb, &map_b, full_bar(s), k0, b_row0);
-        if (EPI == EPI_GLU) tma_load_2d(sb + P_B_BYTES / 2, &map_b, full_bar(s), k0, b_row1);
-      };
-      auto load_activations = [&](long long it, int s) {
-        int k0, a_row, b_row0, b_row1;
-        coords(it, k0, a_row, b_row0, b_row1);
-        tma_load_2d(base + s * P_STAGE_BYTES, &map_a, full_bar(s), k0, a_row);
-      };
-      // the weight tiles of the first stages do not depend on the kernel before
-      const int pre = total < P_STAGES ? (int)total : P_STAGES;
-      for (int i = 0; i < pre; ++i) {
-        mbar_expect_tx(full_bar(i), P_STAGE_BYTES);
-        load_weights(i, i);
-      }
+      // `it` counts k-blocks over all of this block's tiles; stage = it % P_STAGES.  (No
+      // 64-bit arithmetic and no divisions by run-time values inside the k loop: this thread
+      // has to keep several stages ahead of the tensor cores.)
       pdl_wait();
-      for (int i = 0; i < pre; ++i) load_activations(i, i);
-      for (long long it = pre; it < total; ++it) {
-        const int s = (int)(it % P_STAGES);
-        const uint32_t ph = (uint32_t)((it / P_STAGES) & 1);
-        if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, args.error, 1)) break;
-        mbar_expect_tx(full_bar(s), P_STAGE_BYTES);
-        load_weights(it, s);
-        load_activations(it, s);
+      uint32_t it = 0;
+      for (int q = blockIdx.x; q < n_tiles; q += gridDim.x) {
+        const int tile_m = q % tiles_m, tile_n = q / tiles_m;
+        const int a_row = tile_m * BM;
+        const int b_row0 = tile_n * RESULT_COLS, b_row1 = args.glu_offset + tile_n * RESULT_COLS;
+        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+          const int s = it % P_STAGES;
+          const uint32_t ph = (it / P_STAGES) & 1;
+          if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, args.error, 1)) { q = n_tiles; break; }
+          const uint32_t sa = base + s * P_STAGE_BYTES, sb = sa + P_A_BYTES;
+          mbar_expect_tx(full_bar(s), P_STAGE_BYTES);
+          const int k0 = kb * BK;
+          tma_load_2d(sb, &map_b, full_bar(s), k0, b_row0);
+          if (EPI == EPI_GLU) tma_load_2d(sb + P_B_BYTES / 2, &map_b, full_bar(s), k0, b_row1);
+          tma_load_2d(sa, &map_a, full_bar(s), k0, a_row);
+        }
       }
     }
     __syncwarp();
@@ -507,6 +491,9 @@ gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       constexpr uint32_t idesc = instr_desc(BM, P_BN);
       int it = 0, j = 0;
       bool ok = true;
+#ifdef HB_GEMM_TIMING
+      long long t_wait = 0, t_issue = 0;
+#endif
       for (int q = blockIdx.x; q < n_tiles && ok; q += gridDim.x, ++j) {
         const int b = j & 1;
         const uint32_t use = (uint32_t)(j >> 1);
@@ -517,18 +504,33 @@ gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         for (int kb = 0; kb < kb_total; ++kb, ++it) {
           const int s = it % P_STAGES;
           const uint32_t ph = (it / P_STAGES) & 1;
+#ifdef HB_GEMM_TIMING
+          const long long t0 = clock64();
+#endif
           ok = mbar_wait(full_bar(s), ph, abort_flag, args.error, 2);
           if (!ok) break;
           tc_fence_after();
+#ifdef HB_GEMM_TIMING
+          const long long t1 = clock64();
+          t_wait += t1 - t0;
+#endif
           const uint32_t sa = base + s * P_STAGE_BYTES, sb = sa + P_A_BYTES;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
             umma_bf16(acc_addr, smem_desc(sa + k * UMMA_K * 2), smem_desc(sb + k * UMMA_K * 2), idesc,
                       (kb > 0 || k > 0) ? 1u : 0u);
           umma_commit(empty_bar(s));
+#ifdef HB_GEMM_TIMING
+          t_issue += clock64() - t1;
+#endif
         }
         if (ok) umma_commit(acc_full(b));
       }
+#ifdef HB_GEMM_TIMING
+      if (blockIdx.x == 0)
+        printf("1-SM MMA thread: %d k-blocks, per k-block: wait for operands %lld cycles, issue %lld cycles\n",
+               it, t_wait / (it ? it : 1), t_issue / (it ? it : 1));
+#endif
     }
     __syncwarp();
   } else {
@@ -602,6 +604,195 @@ gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ------------------------------------------------------------------ two-SM persistent kernel (prefill)
+// A cluster of two blocks works on tiles of 256 tokens x 256 weight rows with
+// tcgen05.mma.cta_group::2: each block stages its 128 token rows and HALF of the weight
+// tile (128 rows; for SwiGLU the even block takes the gate rows and the odd block the up
+// rows), so a stage is 32 KB instead of 48 KB, six stages fit, and every SM reads two
+// thirds of the operand bytes from L2.  The even block's MMA thread issues for the pair;
+// barriers: copies of both blocks count on the leader's "full" barriers, one multicast
+// commit frees a stage in both blocks and publishes an accumulator to both epilogues, and
+// both epilogues hand accumulators back on the leader's "empty" barrier.
+constexpr int T2_STAGES = 6;
+constexpr int T2_A_BYTES = BM * BK * 2;            // 128 token rows
+constexpr int T2_B_BYTES = 128 * BK * 2;           // this block's half of the weight tile
+constexpr int T2_STAGE_BYTES = T2_A_BYTES + T2_B_BYTES;
+constexpr size_t T2_SMEM = (size_t)T2_STAGES * T2_STAGE_BYTES + 1024 + 256;
+
+template <int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                     GemmArgs args, int tiles_m, int tiles_n) {
+  extern __shared__ unsigned char smem_raw[];
+  pdl_launch_dependents();
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* aligned = smem_raw + (base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + (size_t)T2_STAGES * T2_STAGE_BYTES);
+  // [0,S): full (leader's are used), [S,2S): empty, then 2 accumulator-full, 2 accumulator-empty (leader's)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * T2_STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();           // 0 = leader
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int kb_total = (args.K + BK - 1) / BK;
+  const int n_tiles = tiles_m * tiles_n;             // tiles of 256 x 256
+  constexpr int RESULT_COLS = (EPI == EPI_GLU) ? 128 : 256;
+
+  auto full_bar = [&](int s) { return smem_u32(bars + s); };
+  auto empty_bar = [&](int s) { return smem_u32(bars + T2_STAGES + s); };
+  auto acc_full = [&](int b) { return smem_u32(bars + 2 * T2_STAGES + b); };
+  auto acc_empty = [&](int b) { return smem_u32(bars + 2 * T2_STAGES + 2 + b); };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < T2_STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full(b), 1);
+      mbar_init(acc_empty(b), 8);          // four epilogue warps in each of the two blocks
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc_2sm(smem_u32(tmem_slot), 512);
+    tmem_relinquish_2sm();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                      // the peer's barriers exist before anyone signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int my_tiles = pair < n_tiles ? (n_tiles - 1 - pair) / n_pairs + 1 : 0;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------------------------------------------------- TMA producer (both blocks)
+      pdl_wait();
+      uint32_t it = 0;
+      for (int j = 0; j < my_tiles; ++j) {
+        const int q = pair + j * n_pairs;
+        const int tile_m = q % tiles_m, tile_n = q / tiles_m;
+        const int a_row = tile_m * 256 + (int)rank * 128;
+        const int b_row = (EPI == EPI_GLU) ? (rank ? args.glu_offset : 0) + tile_n * 128
+                                           : tile_n * 256 + (int)rank * 128;
+        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+          const int s = it % T2_STAGES;
+          const uint32_t ph = (it / T2_STAGES) & 1;
+          if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, args.error, 1)) { j = my_tiles; break; }
+          // the leader announces the bytes of BOTH blocks for the stage
+          if (rank == 0) mbar_expect_tx(full_bar(s), 2 * T2_STAGE_BYTES);
+          const uint32_t sa = base + s * T2_STAGE_BYTES;
+          const int k0 = kb * BK;
+          tma_load_2d_2sm(sa + T2_A_BYTES, &map_b, full_bar(s), k0, b_row);
+          tma_load_2d_2sm(sa, &map_a, full_bar(s), k0, a_row);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      // ---------------------------------------------------------- MMA issuer (leader only)
+      constexpr uint32_t idesc = instr_desc(256, 256);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int j = 0; j < my_tiles && ok; ++j) {
+        const int b = j & 1;
+        const uint32_t use = (uint32_t)(j >> 1);
+        ok = mbar_wait(acc_empty(b), (use & 1) ^ 1, abort_flag, args.error, 4);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t acc_addr = tmem_base + (uint32_t)(b * 256);
+        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+          const int s = it % T2_STAGES;
+          const uint32_t ph = (it / T2_STAGES) & 1;
+          ok = mbar_wait(full_bar(s), ph, abort_flag, args.error, 2);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sa = base + s * T2_STAGE_BYTES, sb = sa + T2_A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_bf16_2sm(acc_addr, smem_desc(sa + k * UMMA_K * 2), smem_desc(sb + k * UMMA_K * 2), idesc,
+                          (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit_2sm(empty_bar(s));
+        }
+        if (ok) umma_commit_2sm(acc_full(b));
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ epilogue warps (both blocks)
+    pdl_wait();
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    for (int j = 0; j < my_tiles; ++j) {
+      const int b = j & 1;
+      const uint32_t use = (uint32_t)(j >> 1);
+      const int q = pair + j * n_pairs;
+      const int tile_m = q % tiles_m, tile_n = q / tiles_m;
+      if (!mbar_wait(acc_full(b), use & 1, abort_flag, args.error, 3)) break;
+      if (*abort_flag) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * 256);
+      const int t = tile_m * 256 + (int)rank * 128 + r;
+      for (int c = 0; c < RESULT_COLS; c += 16) {
+        float val[16];
+        if (EPI == EPI_GLU) {
+          float g[16], u[16];
+          tmem_ld16(taddr + c, g);
+          tmem_ld16(taddr + 128 + c, u);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) val[i] = g[i] / (1.f + __expf(-g[i])) * u[i];
+        } else {
+          tmem_ld16(taddr + c, val);
+        }
+        const int n0 = tile_n * RESULT_COLS + c;
+        if (t < args.T) {
+          if (args.bias) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) if (n0 + i < args.N) val[i] += args.bias[n0 + i];
+          }
+          if (!args.out_f32 && n0 + 16 <= args.N && (args.ldo & 7) == 0) {
+            uint32_t packed[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              __nv_bfloat162 p = __floats2bfloat162_rn(val[2 * i], val[2 * i + 1]);
+              packed[i] = *reinterpret_cast<uint32_t*>(&p);
+            }
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(args.out) + (size_t)t * args.ldo + n0);
+            dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              if (n0 + i < args.N) {
+                if (args.out_f32) reinterpret_cast<float*>(args.out)[(size_t)t * args.ldo + n0 + i] = val[i];
+                else reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)t * args.ldo + n0 + i] = __float2bfloat16_rn(val[i]);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_leader(acc_empty(b));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0) {
+    for (int i = 0; i < 2000; ++i) __nanosleep(100);
+  }
+  cluster_sync_all();                      // neither block frees tensor memory the pair still uses
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_2sm(tmem_base, 512);
   }
 }
 
@@ -681,6 +872,47 @@ int launch_persistent(const void* x, const void* w, const GemmArgs& args, int w_
   const int n_tiles = tiles_m * tiles_n;
   const int blocks = n_tiles < sm_count ? n_tiles : sm_count;
   hb_launch(kernel, dim3(blocks), dim3(GEMM_THREADS), P_SMEM, stream, map_a, map_b, args, tiles_m, tiles_n);
+  return hb_check_launch();
+}
+
+template <int EPI>
+int launch_2sm(const void* x, const void* w, const GemmArgs& args, int w_rows, int ldx, int ldw,
+               cudaStream_t stream) {
+  CUtensorMap map_a, map_b;
+  if (!make_map(&map_a, x, args.T, args.K, ldx, BM)) return HB_LAUNCH_FAILED;
+  if (!make_map(&map_b, w, w_rows, args.K, ldw, 128)) return HB_LAUNCH_FAILED;
+  auto kernel = gemm_bf16_2sm_kernel<EPI>;
+  static bool configured = false;
+  static int sm_count = 0;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)T2_SMEM) != cudaSuccess)
+      return HB_LAUNCH_FAILED;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0)
+      return HB_LAUNCH_FAILED;
+    configured = true;
+  }
+  const int per_tile = (EPI == EPI_GLU) ? 128 : 256;
+  const int tiles_m = (args.T + 255) / 256, tiles_n = (args.N + per_tile - 1) / per_tile;
+  const int n_tiles = tiles_m * tiles_n;
+  int pairs = sm_count / 2;
+  if (n_tiles < pairs) pairs = n_tiles;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.dynamicSmemBytes = T2_SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = hb_pdl_enabled() ? 2 : 1;
+  cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, args, tiles_m, tiles_n);
   return hb_check_launch();
 }
 
@@ -768,9 +1000,13 @@ HB_EXPORT int hb_gemm_bf16(void* out, const void* x, const void* w, const float*
 #define HB_GEMM_CASE(BN_, SWAP_)                                                              \
   return glu ? launch<BN_, SWAP_, EPI_GLU>(x, w, a, w_rows, ldx, ldw, stream)                 \
              : launch<BN_, SWAP_, EPI_STORE>(x, w, a, w_rows, ldx, ldw, stream)
-  if (swap_bn == 0 && k_splits == 1)      // prefill: the persistent kernel
+  if (swap_bn == 0 && k_splits == 1) {    // prefill: a persistent kernel, two SMs a tile or one
+    if (cluster == 2)
+      return glu ? launch_2sm<EPI_GLU>(x, w, a, w_rows, ldx, ldw, stream)
+                 : launch_2sm<EPI_STORE>(x, w, a, w_rows, ldx, ldw, stream);
     return glu ? launch_persistent<EPI_GLU>(x, w, a, w_rows, ldx, ldw, stream)
                : launch_persistent<EPI_STORE>(x, w, a, w_rows, ldx, ldw, stream);
+  }
   switch (swap_bn) {
     case 0: HB_GEMM_CASE(256, false);
     case 16: HB_GEMM_CASE(16, true);

@@ -271,6 +271,8 @@ def linear_f32(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tenso
 #: add the partial sums of a split reduction inside a thread-block cluster (through
 #: distributed shared memory) where that is possible, instead of through scratch memory
 GEMM_CLUSTER_REDUCE = True
+#: prefill-sized products (more than 128 tokens, reduction not split) on pairs of SMs
+GEMM_TWO_SM = True
 _GEMM_SCRATCH_FLOATS = 16 * 1024 * 1024
 
 
@@ -371,7 +373,7 @@ def tc_gemm_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
 
 def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
                 glu: bool = False, out_dtype: torch.dtype = torch.bfloat16,
-                plan=None, cluster: Optional[bool] = None) -> torch.Tensor:
+                plan=None, cluster: Optional[bool] = None, two_sm: Optional[bool] = None) -> torch.Tensor:
     """y = x W^T (+ bias) on tcgen05 tensor cores; bfloat16 operands, float32 accumulate.
 
     With ``glu`` the weight is [gate rows; up rows] ([2 I, K]) and the result is
@@ -404,6 +406,9 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
         cluster = GEMM_CLUSTER_REDUCE
     # slices of a tile as a cluster: at most 8, and the partial sums must fit the stages
     cluster = bool(cluster) and 1 < splits <= 8 and _cluster_fits(bn, glu)
+    cluster_arg = 1 if cluster else 0
+    if bn == 0 and splits == 1 and (GEMM_TWO_SM if two_sm is None else two_sm):
+        cluster_arg = 2                      # prefill tiles on pairs of SMs (cta_group::2)
     scratch, tickets, err = _gemm_workspace(x.device)
     lib = load_library("gemm_bf16")
     if splits > 1 and not cluster:
@@ -418,29 +423,34 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
     _run(f(_p(out), _p(x), _p(weight), _p(bias), _p(scratch), _p(tickets), _p(err), T, N, K, K, K, N,
            rows, int(glu), N if glu else 0, 1 if out_dtype == torch.float32 else 0, bn, splits,
-           1 if cluster else 0, _stream()), "gemm_bf16")
+           cluster_arg, _stream()), "gemm_bf16")
     return out
 
 
-#: Plain products (no bias, bfloat16 out) of more than 128 tokens go to the library
-#: (cuBLAS through torch), which the reference uses for every product
-#: (python/helios/exec/model.py:170-181) and which, with its two-SM tiles, is still ahead
-#: of this package's one-SM tcgen05 kernel at these sizes (1.5 against 1.2 PFLOP/s at 2,048
-#: tokens).  Decode-sized and fused products (bias, SwiGLU, float32 logits) always run
-#: on this package's kernel.  Set False to run everything on it.
-GEMM_LIBRARY_FOR_LARGE_PLAIN = True
+#: Token counts between the decode kernel's range (up to 128, weights streamed once with
+#: the tokens on the MMA N axis) and the prefill kernel's (from 1,024 up, pairs of SMs on
+#: 256x256 tiles) leave most SMs of the two-SM kernel without a tile.  There plain products
+#: (no bias, bfloat16 out) go to the library (cuBLAS through torch), which the reference uses
+#: for every product (python/helios/exec/model.py:170-181).  Fused products (bias, float32
+#: logits, SwiGLU from 384 tokens up) always run on this package's kernel.  (0, 0) turns
+#: the library off.
+GEMM_LIBRARY_TOKEN_RANGE = (129, 1023)
+
+
+def _library_range(tokens: int) -> bool:
+    lo, hi = GEMM_LIBRARY_TOKEN_RANGE
+    return lo <= tokens <= hi
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """y = x W^T + b.  float32: this package's FMA kernel.  bfloat16: the tcgen05 kernel
-    (see GEMM_LIBRARY_FOR_LARGE_PLAIN for the one case that goes to the library); a K that
-    is no multiple of 8 goes to the library too, as TMA needs 16-byte rows."""
+    """y = x W^T + b.  float32: this package's FMA kernel.  bfloat16: the tcgen05 kernels
+    (see GEMM_LIBRARY_TOKEN_RANGE for the one case that goes to the library); a K that is
+    no multiple of 8 goes to the library too, as TMA needs 16-byte rows."""
     if x.dtype == torch.float32:
         return linear_f32(x, weight, bias)
     _check(x, "x", torch.bfloat16, 2)
     _check(weight, "weight", torch.bfloat16, 2)
-    if tc_gemm_supported(x, weight) and not (GEMM_LIBRARY_FOR_LARGE_PLAIN and bias is None
-                                             and x.shape[0] > 128):
+    if tc_gemm_supported(x, weight) and not (bias is None and _library_range(x.shape[0])):
         return linear_bf16(x, weight, bias)
     b = None if bias is None else bias.to(torch.bfloat16)
     return torch.nn.functional.linear(x, weight, b)
@@ -449,7 +459,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
 def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     """silu(x gate^T) * (x up^T) for ``w_gate_up`` = [gate rows; up rows]; fused into the
     product's epilogue in bfloat16, two kernels otherwise."""
-    if x.dtype == torch.bfloat16 and tc_gemm_supported(x, w_gate_up):
+    if x.dtype == torch.bfloat16 and tc_gemm_supported(x, w_gate_up) and not (
+            _library_range(x.shape[0]) and x.shape[0] < 384):
         return linear_bf16(x, w_gate_up, glu=True)
     return silu_mul(linear(x, w_gate_up))
 

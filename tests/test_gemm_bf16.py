@@ -97,3 +97,26 @@ def test_k_that_is_no_multiple_of_8_goes_to_the_library_and_is_refused_by_the_ke
     _close(got, x.double() @ w.double().T)
     with pytest.raises(ops().KernelError):
         ops().linear_bf16(x.to(DEV), w.to(DEV))
+
+
+@pytest.mark.parametrize("two_sm", [False, True])
+@pytest.mark.parametrize("T,N,K", [(129, 256, 64), (256, 512, 192), (300, 392, 1224), (2048, 4096, 1024),
+                                   (1000, 1000, 520), (513, 6144, 4096)])
+@pytest.mark.parametrize("glu", [False, True])
+def test_prefill_kernels_one_and_two_sm(T, N, K, glu, two_sm):
+    """Tokens on the M axis: the one-SM persistent kernel and the cta_group::2 kernel
+    (pairs of SMs on 256x256 tiles), ragged in every dimension."""
+    x, w, b = _case(T, N, K, T + N + K, glu)
+    xd, wd = x.double(), w.double()
+    if glu:
+        gate, up = xd @ wd[:N].T, xd @ wd[N:].T
+        want = gate * torch.sigmoid(gate) * up
+        got = ops().linear_bf16(x.to(DEV), w.to(DEV), glu=True, plan=(0, 1), two_sm=two_sm)
+    else:
+        want = xd @ wd.T + b.double()
+        got = ops().linear_bf16(x.to(DEV), w.to(DEV), b.to(DEV), plan=(0, 1), two_sm=two_sm)
+    ops().check_kernel_errors()
+    _close(got, want)
+    got32 = ops().linear_bf16(x.to(DEV), w.to(DEV), glu=glu, plan=(0, 1), two_sm=two_sm, out_dtype=torch.float32)
+    ops().check_kernel_errors()
+    assert got32.dtype == torch.float32
