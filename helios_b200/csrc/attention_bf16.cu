@@ -141,7 +141,7 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
                         const __nv_bfloat16* __restrict__ v_pages,
                         const int* __restrict__ block_table, int bt_stride,
                         const int* __restrict__ positions, int nh, int nkv, int page_size,
-                        int window, float scale_log2, int n_splits) {
+                        int window, float scale_log2, int n_splits, int cluster_merge) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int RS = HD + 8;
@@ -260,6 +260,8 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
   float* red_o = reinterpret_cast<float*>(smem_raw);                 // [warps][16][HD]
   float* red_m = red_o + DEC_WARPS * 16 * HD;                        // [warps][16]
   float* red_l = red_m + DEC_WARPS * 16;
+  float* cta_o = red_l + DEC_WARPS * 16;                             // [16][HD] this block's merged partial
+  float* cta_ml = cta_o + 16 * HD;                                   // [16][2]
   {
     const int g0 = lane >> 2, c0 = 2 * (lane & 3);
 #pragma unroll
@@ -294,6 +296,14 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     const int h = kvh * G + row;
     if (n_splits == 1) {
       out[((size_t)seq * nh + h) * HD + d] = __float2bfloat16_rn(acc / L);
+    } else if (cluster_merge) {
+      // the slices of this (request, KV head) are one thread-block cluster: park the block's
+      // partial result in its own shared memory for the merge below
+      cta_o[idx] = acc;
+      if (d == 0) {
+        cta_ml[2 * row] = M;
+        cta_ml[2 * row + 1] = L;
+      }
     } else {
       const size_t p = ((size_t)seq * nh + h) * n_splits + split;
       part_o[p * HD + d] = acc;
@@ -302,6 +312,46 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
         part_ml[p * 2 + 1] = L;
       }
     }
+  }
+  if (n_splits > 1 && cluster_merge) {
+    // every block merges its share of the G x HD outputs, reading all slices' partial
+    // results (in slice order) from its peers' shared memory
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    const uint32_t o_addr = (uint32_t)__cvta_generic_to_shared(cta_o);
+    const uint32_t ml_addr = (uint32_t)__cvta_generic_to_shared(cta_ml);
+    auto peer = [](uint32_t addr, uint32_t rank) {
+      uint32_t remote;
+      float v;
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+      asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+      return v;
+    };
+    const int total = G * HD;
+    const int per = (total + n_splits - 1) / n_splits;
+    const int e_end = min(total, (split + 1) * per);
+    for (int idx = split * per + threadIdx.x; idx < e_end; idx += DEC_WARPS * 32) {
+      const int row = idx / HD, d = idx - row * HD;
+      float ms[8], ls[8], os[8];
+#pragma unroll
+      for (int sp = 0; sp < 8; ++sp) {
+        const bool on = sp < n_splits;
+        ms[sp] = on ? peer(ml_addr + (uint32_t)(2 * row) * 4u, sp) : -INFINITY;
+        ls[sp] = on ? peer(ml_addr + (uint32_t)(2 * row + 1) * 4u, sp) : 0.f;
+        os[sp] = on ? peer(o_addr + (uint32_t)idx * 4u, sp) : 0.f;
+      }
+      float M = -INFINITY;
+#pragma unroll
+      for (int sp = 0; sp < 8; ++sp) M = fmaxf(M, ms[sp]);
+      float L = 0.f, acc = 0.f;
+#pragma unroll
+      for (int sp = 0; sp < 8; ++sp) {
+        const float f = exp2f(ms[sp] - M);
+        L += ls[sp] * f;
+        acc += os[sp] * f;
+      }
+      out[((size_t)seq * nh + kvh * G + row) * HD + d] = __float2bfloat16_rn(acc / L);
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
   }
 }
 
@@ -467,7 +517,7 @@ int launch_decode(void* out, float* part_o, float* part_ml, const void* q, int q
                   float scale, int n_splits, cudaStream_t stream) {
   constexpr int RS = HD + 8;
   size_t smem = (size_t)DEC_WARPS * DEC_STAGES * 2 * DEC_TILE * RS * sizeof(__nv_bfloat16);
-  const size_t red = (size_t)DEC_WARPS * 16 * (HD + 2) * sizeof(float);
+  const size_t red = (size_t)(DEC_WARPS * 16 * (HD + 2) + 16 * (HD + 2)) * sizeof(float);
   if (red > smem) smem = red;
   auto kernel = decode_attention_kernel<HD>;
   static bool configured = false;
@@ -477,10 +527,32 @@ int launch_decode(void* out, float* part_o, float* part_ml, const void* q, int q
     configured = true;
   }
   dim3 grid(n_splits, nkv, S);
+  const int cluster_merge = (n_splits > 1 && n_splits <= 8 && part_o == nullptr) ? 1 : 0;
+  if (cluster_merge) {
+    // the slices of one (request, KV head) as a cluster: merged through distributed shared memory
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(DEC_WARPS * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = n_splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = hb_pdl_enabled() ? 2 : 1;
+    cudaLaunchKernelEx(&cfg, kernel, (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, q_stride,
+                       (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, bt_stride,
+                       positions, nh, nkv, page_size, window, scale * LOG2E, n_splits, 1);
+    return hb_check_launch();
+  }
   hb_launch(kernel, dim3(grid), dim3(DEC_WARPS * 32), smem, stream, 
       (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, q_stride,
       (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, bt_stride,
-      positions, nh, nkv, page_size, window, scale * LOG2E, n_splits);
+      positions, nh, nkv, page_size, window, scale * LOG2E, n_splits, 0);
   if (n_splits > 1)
     hb_launch(decode_merge_kernel<HD>, dim3(S * nh), dim3(HD < 128 ? HD : 128), 0, stream, 
         (__nv_bfloat16*)out, part_o, part_ml, n_splits);
@@ -524,7 +596,9 @@ int launch_prefill(void* out, const void* q, int q_stride, const void* k_pages, 
 
 // Decode: S requests, one token each (token i belongs to request i).  Needs the group
 // size nh / nkv <= 16.  part_o: float [S, nh, n_splits, hd], part_ml: float
-// [S, nh, n_splits, 2]; both unused when n_splits == 1.
+// [S, nh, n_splits, 2]; both unused when n_splits == 1.  With 2..8 slices and part_o null
+// the slices run as one thread-block cluster and are merged through distributed shared
+// memory instead of a second kernel.
 HB_EXPORT int hb_attention_decode_bf16(void* out, float* part_o, float* part_ml, const void* q,
                                        int q_stride, const void* k_pages, const void* v_pages,
                                        const int* block_table, int bt_stride, const int* positions,

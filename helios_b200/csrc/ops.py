@@ -84,7 +84,7 @@ def preload(dtype: torch.dtype) -> None:
     from .build import build_all
 
     names = ["elementwise", "attention_generic"]
-    names += ["gemm_f32"] if dtype == torch.float32 else ["attention_bf16", "gemm_bf16"]
+    names += ["gemm_f32"] if dtype == torch.float32 else ["attention_bf16", "attention_tc", "gemm_bf16"]
     build_all(names)
     for n in names:
         load_library(n)
@@ -511,14 +511,16 @@ def linear_logits(rows: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
 
 
 TILED_HEAD_DIMS = (32, 64, 96, 128)
+#: merge the context slices of decode attention inside a thread-block cluster (up to 8 slices)
+ATTENTION_CLUSTER_MERGE = True
 #: use the tcgen05 attention kernel for batches with prompt portions where its sizes fit
 ATTENTION_TCGEN05 = True
 _SM_COUNT = 148
 
 
 def _wave_splits(blocks: int, slots: int, most: int) -> int:
-    """Number of slices per block so that blocks * slices fills ``slots`` resident blocks
-    as evenly as possible: the largest count that still fits one round, or, when even one
+    """Number of slices per block so that blocks * slices fills ``slots`` resident blocks as
+    evenly as possible: the largest count that still fits one round, or, when even one
     slice per block overflows it, the count with the fullest last round."""
     if blocks >= slots:
         best, best_eff = 1, 0.0
@@ -562,7 +564,10 @@ def attention_decode_bf16(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: tor
         raise KernelError("decode attention needs one token per request")
     out = torch.empty((S, num_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
     part_o = part_ml = None
-    if n_splits > 1:
+    # slices as one cluster only while all blocks are resident at once: with several rounds
+    # of blocks, clusters (whose blocks must start together) cost more than the merge kernel
+    one_round = S * num_kv_heads * n_splits <= 2 * _SM_COUNT
+    if n_splits > 8 or (n_splits > 1 and not (ATTENTION_CLUSTER_MERGE and one_round)):
         part_o = torch.empty((S, num_heads, n_splits, head_dim), dtype=torch.float32, device=qkv.device)
         part_ml = torch.empty((S, num_heads, n_splits, 2), dtype=torch.float32, device=qkv.device)
     f = _fn("attention_bf16", "hb_attention_decode_bf16",

@@ -152,8 +152,10 @@ def test_generic_attention(dtype, nh, nkv, hd, page, window):
 @pytest.mark.parametrize("nh,nkv,hd,page", [(32, 8, 128, 16), (28, 4, 128, 16), (14, 2, 64, 8), (6, 6, 96, 64),
                                             (16, 1, 32, 16), (7, 1, 64, 3)])
 @pytest.mark.parametrize("window", [None, 100])
-@pytest.mark.parametrize("splits", [1, 3, 8])
-def test_decode_attention_bf16(nh, nkv, hd, page, window, splits):
+@pytest.mark.parametrize("splits,cluster", [(1, True), (3, True), (8, True), (3, False), (8, False), (13, True)])
+def test_decode_attention_bf16(nh, nkv, hd, page, window, splits, cluster, monkeypatch):
+    """Context slices merged inside a thread-block cluster (up to 8) or by the merge kernel."""
+    monkeypatch.setattr(ops(), "ATTENTION_CLUSTER_MERGE", cluster)
     seqs = [(n, 1) for n in (0, 1, 30, 31, 32, 33, 127, 128, 129, 255, 256, 1000, 2049)]
     case = make_paged_case(seqs, nh, nkv, hd, page, torch.bfloat16, DEV, seed=nh + hd)
     scale = 1.0 / math.sqrt(hd)
