@@ -272,6 +272,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--no-run-ahead", action="store_true",
+                    help="end to end: read every step's tokens before the next step is launched")
     ap.add_argument("--no-graphs", action="store_true",
                     help="run decode steps kernel by kernel (for profilers) instead of as captured graphs")
     ap.add_argument("--ref-layers", type=int, default=FULL_LAYERS,
@@ -392,7 +394,8 @@ def main():
         engine = LLMEngine(EngineConfig(
             model_dir="", dtype="bfloat16", block_size=page, max_num_seqs=args.batch,
             max_num_batched_tokens=PREFILL_TOKENS, max_model_len=args.context + 8,
-            num_blocks=args.batch * (args.context // page + 2) + 8, watermark=0.0), model=model)
+            num_blocks=args.batch * (args.context // page + 2) + 8, watermark=0.0,
+            run_ahead=not args.no_run_ahead), model=model)
         ctx0 = args.context - args.steps - args.warmup
         # every request must still be decoding when the timed steps end, whenever its
         # prompt was finished
@@ -417,7 +420,8 @@ def main():
             print("running:", len(engine.scheduler.running), engine.stats_snapshot(), file=sys.stderr)
         h2d = 4 * (args.batch * 8 + args.batch * (args.context // page + 1)) + args.batch * 28
         e2e = {"value": round(args.batch / wall, 1), "unit": "tokens/s",
-               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch}
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch,
+               "steps_launched_ahead": engine.steps_ahead}
     sampler.stop()
 
     line = {

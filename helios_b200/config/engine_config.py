@@ -22,6 +22,7 @@ class EngineConfig:
     num_blocks: Optional[int] = None         # overrides kv_cache_bytes when given
     seed: int = 0                            # seeds requests that bring no seed
     use_cuda_graphs: bool = True
+    run_ahead: bool = True                   # enqueue the next decode step before reading this one's tokens
 
     def validate(self) -> None:
         if self.block_size <= 0:

@@ -93,15 +93,22 @@ class EngineCore:
             self.cache.release(request_id)
 
     # ------------------------------------------------------------------ the step
-    def step(self, entries: Sequence[StepEntry], manage_cache: bool = True) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], manage_cache: bool = True,
+             token_feed: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Run exactly the given tokens as one batch over the cache earlier steps left.
         Returns float32 logits [sum of len(want), vocab] in the order of the entries and
         of their ``want``.  With ``manage_cache`` requests not seen before are admitted,
         pages for the new tokens are taken and the new length is committed; a scheduler
-        that does this bookkeeping itself passes False."""
+        that does this bookkeeping itself passes False.  ``token_feed`` (int32 on the
+        device, one per entry) replaces the one token of every entry: token ids that an
+        earlier step left on the device and the host has not seen."""
         entries = [e for e in entries]
         if not entries:
             return None
+        if token_feed is not None:
+            if any(len(e.tokens) != 1 for e in entries) or token_feed.numel() != len(entries) \
+                    or token_feed.dtype != torch.int32 or token_feed.device.type != self.model.device.type:
+                raise ValueError("token_feed takes int32 on the model's device, one token per entry")
         seen = set()
         for e in entries:
             if e.request_id in seen:
@@ -136,9 +143,11 @@ class EngineCore:
                                      f"{len(e.tokens)} new tokens")
         logits = None
         if self.use_cuda_graphs and all(len(e.tokens) == 1 for e in entries):
-            logits = self._graph_step(entries)
+            logits = self._graph_step(entries, token_feed)
         if logits is None:
             ctx = build_context(entries, self.cache, self.model.dtype, self.model.device)
+            if token_feed is not None:
+                ctx.token_ids.copy_(token_feed)
             logits = self.model.forward(ctx, self.cache)
         if manage_cache:
             for e in entries:
@@ -148,7 +157,7 @@ class EngineCore:
         return logits
 
     # ------------------------------------------------------------------ captured decode steps
-    def _graph_step(self, entries) -> Optional[torch.Tensor]:
+    def _graph_step(self, entries, token_feed=None) -> Optional[torch.Tensor]:
         S = len(entries)
         bucket = 1
         while bucket < S:
@@ -167,6 +176,8 @@ class EngineCore:
             g.capture(self)
             self._graphs[bucket] = g
         g.fill(entries, self.cache)
+        if token_feed is not None:
+            g.ctx.token_ids[:S].copy_(token_feed)
         logits = g.replay()
         if all(len(e.want) == 1 for e in entries):
             return logits[:S]

@@ -14,31 +14,100 @@ from ..sampling import Sampler
 from .batch import StepEntry
 from .core import EngineCore
 from .model import DecoderModel
-from .scheduler import Scheduler, SchedulerConfig, StepPlan
+from .scheduler import ExecFault, Scheduler, SchedulerConfig, StepPlan
 from .tokenizer import load_tokenizer
 from .types import CompletionOutput, FinishReason, Request, SamplingParams, Sequence as Seq
 
 
+class _TokenMailbox:
+    """Pinned host memory that a step's sampled tokens are copied into, and the event
+    that says the copy is done."""
+
+    def __init__(self, capacity: int) -> None:
+        self.host = torch.empty(capacity, dtype=torch.int32, pin_memory=True)
+        self.event = torch.cuda.Event()
+        self.busy = False
+
+
+class StepHandle:
+    """A step that has been enqueued on the device.  ``device_tokens`` (int32, one per
+    sampled item, in the plan's order) can feed the next step at once; ``result()`` waits
+    for this step alone and gives seq_id -> token."""
+
+    def __init__(self, seq_ids: List[int], device_tokens: Optional[torch.Tensor],
+                 mailbox: Optional[_TokenMailbox]) -> None:
+        self.seq_ids = seq_ids
+        self.device_tokens = device_tokens
+        self._mailbox = mailbox
+
+    def result(self) -> Dict[int, int]:
+        if self._mailbox is None:
+            return {}
+        self._mailbox.event.synchronize()
+        tokens = self._mailbox.host[:len(self.seq_ids)].tolist()
+        self._mailbox.busy = False
+        return dict(zip(self.seq_ids, tokens))
+
+    def discard(self) -> None:
+        """Nobody will read the tokens; the mailbox may be used again once its copy is done."""
+        if self._mailbox is not None:
+            self._mailbox.busy = False
+
+
 class ModelExecutor:
     """Runs a scheduler's plan as ONE batch through ``EngineCore.step`` and samples
-    (python/helios/exec/runner.py:108-153 runs prompts and decodes as two passes)."""
+    (python/helios/exec/runner.py:108-153 runs prompts and decodes as two passes).
+    ``launch`` only enqueues the work: the host is free to prepare the next step while
+    the device runs this one."""
 
-    def __init__(self, core: EngineCore) -> None:
+    def __init__(self, core: EngineCore, max_num_seqs: int = 64) -> None:
         self.core = core
         self.sampler = Sampler()
-        self.launch_steps = 0
+        self._capacity = max(1, max_num_seqs)
+        self._mailboxes: List[_TokenMailbox] = []
 
-    def run(self, plan: StepPlan) -> Dict[int, int]:
+    def _mailbox(self) -> _TokenMailbox:
+        for m in self._mailboxes:
+            if not m.busy:
+                break
+        else:
+            m = _TokenMailbox(self._capacity)
+            self._mailboxes.append(m)
+        m.event.synchronize()         # a copy whose result nobody fetched
+        m.busy = True
+        return m
+
+    def launch(self, plan: StepPlan, feed: Optional[StepHandle] = None) -> StepHandle:
+        """``feed``: the handle of the step before, when the plan's tokens are the ones that
+        step samples (``PlanItem.fed_on_device``): they are taken on the device."""
         entries = [StepEntry(i.seq_id, i.token_ids, [i.num_tokens - 1] if i.sample else [])
                    for i in plan.items]
-        logits = self.core.step(entries, manage_cache=False)
+        on_device = [i.fed_on_device for i in plan.items]
+        token_feed = None
+        if any(on_device):
+            if not all(on_device) or feed is None or feed.seq_ids != [i.seq_id for i in plan.items]:
+                raise ValueError("a step fed on the device needs the handle of the step that "
+                                 "samples exactly its requests, in its order")
+            token_feed = feed.device_tokens
+        logits = self.core.step(entries, manage_cache=False, token_feed=token_feed)
         sampled = [i for i in plan.items if i.sample]
         if not sampled:
-            return {}
-        tokens = self.sampler.sample(logits, [i.params for i in sampled],
-                                     [i.rng_seed for i in sampled],
-                                     [i.rng_offset for i in sampled])
-        return {i.seq_id: t for i, t in zip(sampled, tokens)}
+            return StepHandle([], None, None)
+        if len(sampled) > self._capacity:
+            self._capacity = len(sampled)
+            self._mailboxes = [m for m in self._mailboxes if m.busy]
+        tokens = self.sampler.sample_device(logits, [i.params for i in sampled],
+                                            [i.rng_seed for i in sampled],
+                                            [i.rng_offset for i in sampled])
+        box = self._mailbox()
+        if box.host.numel() < len(sampled):
+            box.host = torch.empty(self._capacity, dtype=torch.int32, pin_memory=True)
+        box.host[:len(sampled)].copy_(tokens, non_blocking=True)
+        box.event.record()
+        return StepHandle([i.seq_id for i in sampled], tokens, box)
+
+    def run(self, plan: StepPlan) -> Dict[int, int]:
+        return self.launch(plan).result()
 
 
 class LLMEngine:
@@ -66,7 +135,10 @@ class LLMEngine:
                             max_model_len=max_len,
                             enable_chunked_prefill=config.enable_chunked_prefill),
             self.core.cache)
-        self.executor = ModelExecutor(self.core)
+        self.executor = ModelExecutor(self.core, config.max_num_seqs)
+        # a decode step that is launched while the one before still runs: (plan, handle)
+        self._in_flight = None
+        self.steps_ahead = 0
         self._rng = random.Random(config.seed)
         self._tokenizer = None
         self._tokenizer_loaded = False
@@ -116,9 +188,48 @@ class LLMEngine:
 
     # ------------------------------------------------------------------ run
     def step(self) -> List[CompletionOutput]:
-        """One scheduler iteration; returns the requests that completed in it."""
-        self.scheduler.step(self.executor)
+        """One scheduler iteration; returns the requests that completed in it.
+
+        With ``run_ahead`` the next decode step is enqueued before this one's tokens are
+        read: its token ids are taken from this step's samples on the device, so the device
+        does not wait while the host reads tokens and prepares the next batch.  A request
+        that stops on the token being read has one more token computed in vain."""
+        sched = self.scheduler
+        if self._in_flight is None:
+            plan = sched.schedule()
+            if plan.is_empty:
+                return self._collect()
+            try:
+                handle = self.executor.launch(plan)
+            except ExecFault as fault:
+                sched.fault(plan, fault)
+                return self._collect()
+            sched.launched(plan)
+        else:
+            plan, handle = self._in_flight
+            self._in_flight = None
+        ahead = ahead_handle = None
+        if self.config.run_ahead:
+            ahead = sched.schedule_ahead(plan)
+            if ahead is not None:
+                try:
+                    ahead_handle = self.executor.launch(ahead, feed=handle)
+                except ExecFault as fault:
+                    sched.fault(ahead, fault)
+                    ahead = None
+                else:
+                    sched.launched(ahead)
+                    self.steps_ahead += 1
+        sched.complete(plan, handle.result(), ahead)
         self._apply_stop_strings()
+        if ahead is not None:
+            if any(not sched.seqs[i.seq_id].is_finished for i in ahead.items):
+                self._in_flight = (ahead, ahead_handle)
+            else:
+                ahead_handle.discard()
+        return self._collect()
+
+    def _collect(self) -> List[CompletionOutput]:
         done = [self._make_output(seq) for seq in self.scheduler.take_finished()]
         self._completed.extend(done)
         return done

@@ -51,6 +51,10 @@ class SchedulerConfig:
             raise ValueError("max_num_seqs, max_num_batched_tokens and max_model_len must be positive")
 
 
+#: stands for a token that is not known on the host yet (``PlanItem.fed_on_device``)
+PLACEHOLDER = 0
+
+
 @dataclass
 class PlanItem:
     """A request's tokens for this step (python/helios/core/execstep.py:24-49: a decode
@@ -62,6 +66,7 @@ class PlanItem:
     params: SamplingParams
     rng_seed: int = 0
     rng_offset: int = 0           # number of tokens this request has sampled so far
+    fed_on_device: bool = False   # the token is the one the step before is sampling
 
     @property
     def num_tokens(self) -> int:
@@ -170,22 +175,102 @@ class Scheduler:
     # ------------------------------------------------------------------ one iteration
     def step(self, executor: Executor) -> Dict[int, int]:
         """python/helios/core/scheduler.py:312-365."""
+        plan = self.schedule()
+        if plan.is_empty:
+            return {}
+        try:
+            tokens = executor.run(plan)
+        except ExecFault as fault:
+            self.fault(plan, fault)
+            return {}
+        self.launched(plan)
+        self.complete(plan, tokens)
+        return tokens
+
+    # The three phases of an iteration, for an executor that works asynchronously:
+    # ``schedule`` decides the step, ``launched`` records that its tokens are in the cache
+    # (true, in the device's order of work, once the step is enqueued), ``complete`` takes
+    # the sampled tokens.  Between ``launched(p)`` and ``complete(p)`` a caller may ask
+    # ``schedule_ahead(p)`` for the step after it and launch that too.
+    def schedule(self) -> StepPlan:
         self.step_t += 1
         self.stats.steps += 1
         self._admit()
         self._ensure_running_can_progress()
         plan = self._build_plan()
         self.last_plan = plan
-        if plan.is_empty:
-            return {}
-        try:
-            tokens = executor.run(plan)
-        except ExecFault as fault:
-            self._handle_fault(plan, fault)
-            return {}
-        self._apply(plan, tokens)
+        return plan
+
+    def launched(self, plan: StepPlan) -> None:
+        for item in plan.items:
+            seq = self.seqs[item.seq_id]
+            self.cache.commit(seq.seq_id, item.num_tokens)
+            seq.num_computed_tokens += item.num_tokens
+            if item.num_tokens > 1 or item.start_pos < seq.prompt_len:
+                self.stats.prefill_tokens += item.num_tokens
+            else:
+                self.stats.decode_tokens += 1
+
+    def complete(self, plan: StepPlan, tokens: Dict[int, int],
+                 ahead: Optional[StepPlan] = None) -> None:
+        """``ahead``: the step that was launched after ``plan`` with ``schedule_ahead``; the
+        places of its tokens are taken already."""
+        reserved = {i.seq_id for i in ahead.items} if ahead is not None else ()
+        for item in plan.items:
+            if not item.sample:
+                continue
+            seq = self.seqs[item.seq_id]
+            if seq.is_finished or seq not in self.running:
+                continue          # finished, aborted or preempted while the step ran
+            if item.seq_id not in tokens:
+                raise RuntimeError(f"the executor returned no token for sequence {item.seq_id}")
+            self._accept(seq, int(tokens[item.seq_id]), reserve=item.seq_id not in reserved)
         self.stats.max_running = max(self.stats.max_running, len(self.running))
-        return tokens
+
+    def fault(self, plan: StepPlan, fault: ExecFault) -> None:
+        self._handle_fault(plan, fault)
+
+    def schedule_ahead(self, prev: StepPlan) -> Optional[StepPlan]:
+        """The step after ``prev`` while ``prev`` still runs: every request of ``prev`` gets
+        as its one token the token ``prev`` is sampling for it (``PLACEHOLDER`` here; the
+        executor feeds it on the device), in the order of ``prev``'s items.  Only when that
+        is certainly the step ``schedule`` would make if no request stops: nothing waits,
+        ``prev`` sampled for every running request, none of them reaches its length with
+        the token in flight, and the places for the new tokens can be had.  Else None, and
+        nothing has changed.  A request that does stop on the token in flight is dropped by
+        ``complete``; what the step ahead computed for it is ignored."""
+        if self.waiting or prev.is_empty or len(prev.items) != len(self.running):
+            return None
+        if len(prev.items) > self.config.max_num_batched_tokens:
+            return None
+        seqs = []
+        for item in prev.items:
+            seq = self.seqs[item.seq_id]
+            if not item.sample or seq.is_finished or seq not in self.running:
+                return None
+            if seq.num_pending_tokens != 0:
+                return None       # ``launched(prev)`` has not been called
+            if seq.num_output_tokens + 1 >= seq.request.params.max_tokens:
+                return None
+            if seq.total_tokens + 1 >= self.config.max_model_len:
+                return None
+            seqs.append(seq)
+        need = [0] * len(self.cache.groups)
+        for seq in seqs:
+            for g, n in enumerate(self.cache.pages_needed(seq.seq_id, 1)):
+                need[g] += n
+        if any(n > pool.num_free for n, pool in zip(need, self.cache.pools)):
+            return None
+        self.step_t += 1
+        self.stats.steps += 1
+        plan = StepPlan(self.step_t)
+        for seq in seqs:
+            self.cache.extend(seq.seq_id, 1)
+            plan.items.append(PlanItem(seq.seq_id, [PLACEHOLDER], seq.num_computed_tokens, sample=True,
+                                       params=seq.request.params, rng_seed=seq.rng_seed,
+                                       rng_offset=seq.num_output_tokens + 1, fed_on_device=True))
+        self.last_plan = plan
+        return plan
 
     # ------------------------------------------------------------------ admission
     def _admit(self) -> None:
@@ -305,26 +390,7 @@ class Scheduler:
                         rng_offset=seq.num_output_tokens)
 
     # ------------------------------------------------------------------ results
-    def _apply(self, plan: StepPlan, tokens: Dict[int, int]) -> None:
-        for item in plan.items:
-            seq = self.seqs[item.seq_id]
-            self.cache.commit(seq.seq_id, item.num_tokens)
-            seq.num_computed_tokens += item.num_tokens
-            if item.num_tokens > 1 or item.start_pos < seq.prompt_len:
-                self.stats.prefill_tokens += item.num_tokens
-            else:
-                self.stats.decode_tokens += 1
-        for item in plan.items:
-            if not item.sample:
-                continue
-            seq = self.seqs[item.seq_id]
-            if seq.is_finished or seq not in self.running:
-                continue
-            if item.seq_id not in tokens:
-                raise RuntimeError(f"the executor returned no token for sequence {item.seq_id}")
-            self._accept(seq, int(tokens[item.seq_id]))
-
-    def _accept(self, seq: Sequence, token: int) -> None:
+    def _accept(self, seq: Sequence, token: int, reserve: bool = True) -> None:
         """python/helios/core/scheduler.py:913-949."""
         params = seq.request.params
         seq.output_token_ids.append(token)
@@ -339,6 +405,8 @@ class Scheduler:
             return
         if seq.total_tokens >= self.config.max_model_len:
             self._finish(seq, FinishReason.LENGTH)
+            return
+        if not reserve:
             return
         try:
             self.cache.extend(seq.seq_id, 1)       # the place of the new token

@@ -107,6 +107,47 @@ def test_staggered_arrivals_and_seeded_sampling_do_not_depend_on_the_batch(model
     assert eng.run_until_complete()[0].token_ids != singles[3]
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("graphs", [True, False])
+def test_running_ahead_of_the_host_changes_no_token(model_folders, dtype, graphs):
+    """The next decode step is launched with token ids that are still on the device; the
+    outputs equal those of an engine that reads every token first.  Requests stop at
+    different steps (stop tokens found one step late, lengths known ahead), and one arrives
+    in the middle."""
+    from helios_b200.engine.types import SamplingParams
+
+    folder = model_folders["tiny_llama"]
+    cfg, _ = read_folder(folder)
+    prompts = [random_tokens(cfg["vocab_size"], n, 40 + n) for n in (7, 33, 64, 18, 5)]
+
+    def run(ahead, stops):
+        eng = _engine(folder, dtype=dtype, run_ahead=ahead, use_cuda_graphs=graphs, max_num_seqs=8)
+        params = [SamplingParams(max_tokens=30 + 9 * i, temperature=0.7 if i % 2 else 0.0, seed=77 + i,
+                                 stop_token_ids=stops[i]) for i in range(5)]
+        done, steps = {}, 0
+        for i in range(4):
+            eng.add_request(f"r{i}", prompts[i], params[i])
+        while eng.scheduler.has_work:
+            if steps == 20:
+                eng.add_request("r4", prompts[4], params[4])
+            for out in eng.step():
+                done[out.request_id] = (out.token_ids, out.finish_reason)
+            steps += 1
+            assert steps < 2000
+        eng.scheduler.check_invariants()
+        assert all(p.num_free == p.num_pages for p in eng.core.cache.pools)
+        return done, eng.steps_ahead
+
+    free, _ = run(False, [[]] * 5)
+    # stop two requests on a token they are known to make in the middle of their output
+    stops = [[free["r0"][0][11]], [], [free["r2"][0][25]], [], []]
+    want, none_ahead = run(False, stops)
+    got, n_ahead = run(True, stops)
+    assert none_ahead == 0 and n_ahead > 40
+    assert got == want
+    assert len(want["r0"][0]) <= 12 and len(want["r2"][0]) <= 26
+
+
 @pytest.mark.parametrize("dtype", ["float32"])
 def test_output_survives_preemption_with_outputs_already_made(model_folders, dtype):
     """The reference's own test only ever preempts sequences without outputs

@@ -278,3 +278,147 @@ def test_scheduler_source_uses_no_clock_or_random():
 
     src = inspect.getsource(mod)
     assert "import time" not in src and "import random" not in src
+
+
+# ---------------------------------------------------------------------- running ahead
+def run_all_ahead(sched, ex, arrivals=None, limit=2000):
+    """Drives the scheduler the way the engine does when it launches the next decode step
+    before it has read the tokens of the running one.  ``arrivals``: {call number: request}."""
+    arrivals = dict(arrivals or {})
+    in_flight, calls, ahead_steps = None, 0, 0
+    while sched.has_work or arrivals:
+        if calls in arrivals:
+            sched.add_request(arrivals.pop(calls))
+        calls += 1
+        assert calls < limit, "the scheduler does not finish"
+        if in_flight is None:
+            plan = sched.schedule()
+            if plan.is_empty:
+                continue
+            tokens = ex.run(plan)
+            sched.launched(plan)
+        else:
+            plan, tokens = in_flight
+            in_flight = None
+        sched.check_invariants()
+        ahead = sched.schedule_ahead(plan)
+        if ahead is not None:
+            assert all(i.fed_on_device and i.num_tokens == 1 and i.sample for i in ahead.items)
+            assert [i.seq_id for i in ahead.items] == [i.seq_id for i in plan.items]
+            ahead_tokens = ex.run(ahead)
+            sched.launched(ahead)
+            sched.check_invariants()
+            ahead_steps += 1
+        sched.complete(plan, tokens, ahead)
+        sched.check_invariants()
+        if ahead is not None and any(not sched.seqs[i.seq_id].is_finished for i in ahead.items):
+            in_flight = (ahead, ahead_tokens)
+    return ahead_steps
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_running_ahead_gives_the_same_outputs_and_loses_no_page(seed):
+    import random
+    rng = random.Random(seed)
+    n_req = rng.randint(2, 7)
+    shapes = [(rng.randint(1, 30), rng.randint(1, 25)) for _ in range(n_req)]
+    eos = {i: rng.randint(0, 20) for i in range(n_req) if rng.random() < 0.5}
+    late = {rng.randint(3, 30): i for i in range(n_req) if i and rng.random() < 0.4}
+    pages, page = rng.choice([(24, 4), (40, 4), (12, 16), (200, 2)])
+    window = rng.choice([None, 8])
+
+    def run(ahead):
+        sched, cache = make(num_pages=pages, page=page, budget=rng_budget, max_seqs=4, window=window)
+        ex = ScriptedExecutor(eos_after=eos)
+        reqs = [Request(f"r{i}", list(range(1, n + 1)), SamplingParams(max_tokens=m, stop_token_ids=[2]))
+                for i, (n, m) in enumerate(shapes)]
+        arrivals = {}
+        for i, r in enumerate(reqs):
+            if i in late.values():
+                arrivals[[k for k, v in late.items() if v == i][0]] = r
+            else:
+                sched.add_request(r)
+        n_ahead = 0
+        if ahead:
+            n_ahead = run_all_ahead(sched, ex, arrivals)
+        else:
+            calls = 0
+            while sched.has_work or arrivals:
+                if calls in arrivals:
+                    sched.add_request(arrivals.pop(calls))
+                calls += 1
+                sched.step(ex)
+                sched.check_invariants()
+        assert all(p.num_free == p.num_pages for p in cache.pools)
+        out = {s.request.request_id: (list(s.output_token_ids), s.finish_reason)
+               for s in sched.take_finished()}
+        return out, n_ahead
+
+    rng_budget = rng.choice([8, 16, 64])
+    plain, _ = run(False)
+    ahead, n_ahead = run(True)
+    assert ahead == plain
+    assert len(plain) == n_req
+    AHEAD_STEPS.append(n_ahead)
+
+
+AHEAD_STEPS = []
+
+
+def test_running_ahead_was_exercised():
+    assert sum(AHEAD_STEPS) > 50
+
+
+def test_running_ahead_is_used_for_plain_decoding_and_stops_for_arrivals_and_lengths():
+    sched, cache = make(num_pages=64, page=4, budget=32, max_seqs=4)
+    for i in range(3):
+        sched.add_request(req(5 + i, max_tokens=10, rid=f"r{i}"))
+    ex = ScriptedExecutor()
+    plan = sched.schedule()
+    ex.run(plan)
+    sched.launched(plan)
+    ahead = sched.schedule_ahead(plan)            # all three sample their first token
+    assert ahead is not None and [i.start_pos for i in ahead.items] == [5, 6, 7]
+    assert [i.rng_offset for i in ahead.items] == [1, 1, 1]
+    # asked twice for the same step: the first answer stands, nothing is taken twice
+    used = [p.num_used for p in cache.pools]
+    sched.launched(ahead)
+    sched.complete(plan, {0: 11, 1: 12, 2: 13}, ahead)
+    assert used == [p.num_used for p in cache.pools]
+    sched.check_invariants()
+    # something waits: the next step must be scheduled in the ordinary way
+    sched.add_request(req(3, rid="late"))
+    assert sched.schedule_ahead(ahead) is None
+    sched.complete(ahead, {0: 21, 1: 22, 2: 23})
+    sched.check_invariants()
+    assert [sched.seqs[i].output_token_ids for i in range(3)] == [[11, 21], [12, 22], [13, 23]]
+    # the token in flight is the last one a request may make: no step ahead
+    sched2, _ = make()
+    sched2.add_request(req(4, max_tokens=2, rid="short"))
+    p1 = sched2.schedule()
+    sched2.launched(p1)
+    p2 = sched2.schedule_ahead(p1)
+    assert p2 is not None
+    sched2.launched(p2)
+    sched2.complete(p1, {0: 7}, p2)
+    assert sched2.schedule_ahead(p2) is None      # output 2 of 2 is in flight
+    sched2.complete(p2, {0: 8})
+    assert sched2.take_finished()[0].output_token_ids == [7, 8]
+
+
+def test_a_request_that_stops_on_the_token_in_flight_is_dropped_from_the_step_ahead():
+    sched, cache = make(num_pages=16, page=4)
+    sched.add_request(Request("a", [1, 2, 3], SamplingParams(max_tokens=9, stop_token_ids=[2])))
+    sched.add_request(Request("b", [1, 2, 3, 4, 5], SamplingParams(max_tokens=9, stop_token_ids=[2])))
+    p1 = sched.schedule()
+    sched.launched(p1)
+    p2 = sched.schedule_ahead(p1)
+    sched.launched(p2)
+    sched.complete(p1, {0: 2, 1: 50}, p2)         # "a" stops
+    sched.check_invariants()
+    assert sched.seqs[0].finish_reason is FinishReason.STOP and sched.seqs[0].output_token_ids == [2]
+    p3 = sched.schedule_ahead(p2)                 # p2 no longer covers exactly the running requests
+    assert p3 is None
+    sched.complete(p2, {0: 99, 1: 51})            # the token computed for "a" is ignored
+    assert sched.seqs[0].output_token_ids == [2] and sched.seqs[1].output_token_ids == [50, 51]
+    sched.check_invariants()
