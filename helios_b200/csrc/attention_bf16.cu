@@ -143,7 +143,6 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
                         const int* __restrict__ positions, int nh, int nkv, int page_size,
                         int window, float scale_log2, int n_splits, int cluster_merge) {
   pdl_launch_dependents();
-  pdl_wait();
   constexpr int RS = HD + 8;
   constexpr int TILE_ELEMS = DEC_TILE * RS;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -162,22 +161,6 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
   const int tile_end = min(tiles_total, tile_begin + tiles_per_split);
   const int k_end = pos + 1;
   const int* table = block_table + (size_t)seq * bt_stride;
-
-  // query fragments: rows = the group's heads (zero beyond G)
-  uint32_t qa[HD / 16][4];
-  {
-    const int g0 = lane >> 2, c0 = 2 * (lane & 3);
-    const __nv_bfloat16* qrow = q + (size_t)seq * q_stride + (size_t)kvh * G * HD;
-#pragma unroll
-    for (int ks = 0; ks < HD / 16; ++ks) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int row = g0 + (e & 1) * 8;
-        const int col = ks * 16 + c0 + (e >> 1) * 8;
-        qa[ks][e] = (row < G) ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)row * HD + col) : 0u;
-      }
-    }
-  }
 
   __nv_bfloat16* my = smem + (size_t)warp * DEC_STAGES * 2 * TILE_ELEMS;   // [stage][k|v][tile]
   // A tile is DEC_TILE rows of HD/8 16-byte chunks.  Lane r first finds the cache row of
@@ -212,13 +195,42 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
   for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
-  // prologue: DEC_STAGES - 1 tiles in flight
+  // prologue: DEC_STAGES - 1 tiles in flight.  Keys of earlier steps do not depend on the
+  // kernel before this one (the block tables and positions were copied before the step's
+  // first kernel): their tiles are fetched while that kernel still runs.  The tile with
+  // the token's own key, which that kernel writes, and the query follow after the wait.
   int tile = tile_begin + warp;
+  bool early[DEC_STAGES - 1];
 #pragma unroll
   for (int p = 0; p < DEC_STAGES - 1; ++p) {
-    if (tile + p * DEC_WARPS < tile_end) load_tile(tile + p * DEC_WARPS, p);
+    const int tp = tile + p * DEC_WARPS;
+    early[p] = tp < tile_end && tp < tiles_total - 1;
+    if (early[p]) load_tile(tp, p);
+  }
+  pdl_wait();
+#pragma unroll
+  for (int p = 0; p < DEC_STAGES - 1; ++p) {
+    const int tp = tile + p * DEC_WARPS;
+    if (tp < tile_end && !early[p]) load_tile(tp, p);
     cp_async_commit();
   }
+
+  // query fragments: rows = the group's heads (zero beyond G)
+  uint32_t qa[HD / 16][4];
+  {
+    const int g0 = lane >> 2, c0 = 2 * (lane & 3);
+    const __nv_bfloat16* qrow = q + (size_t)seq * q_stride + (size_t)kvh * G * HD;
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int row = g0 + (e & 1) * 8;
+        const int col = ks * 16 + c0 + (e >> 1) * 8;
+        qa[ks][e] = (row < G) ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)row * HD + col) : 0u;
+      }
+    }
+  }
+
   int stage = 0;
   for (; tile < tile_end; tile += DEC_WARPS) {
     const int ahead = tile + (DEC_STAGES - 1) * DEC_WARPS;
