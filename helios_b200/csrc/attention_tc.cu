@@ -93,8 +93,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = a.nh / a.nkv;
   const int TQ = TILE / G;                            // tokens per tile
-  const int kvh = blockIdx.y;
-  const int seq = a.q_tiles[2 * blockIdx.x], t0 = a.q_tiles[2 * blockIdx.x + 1];
+  // KV heads fastest: the tiles come longest first, and so do the blocks, whatever the head
+  const int kvh = blockIdx.x % a.nkv, q_tile = blockIdx.x / a.nkv;
+  const int seq = a.q_tiles[2 * q_tile], t0 = a.q_tiles[2 * q_tile + 1];
 
   if (threadIdx.x == 0) {
     mbar_init(bar(0), 1); mbar_init(bar(1), 1);
@@ -446,7 +447,7 @@ int launch_tc(const AttnArgs& a, const void* k_pages, const void* v_pages, long 
       return HB_LAUNCH_FAILED;
     configured = true;
   }
-  hb_launch(kernel, dim3(n_tiles, a.nkv), dim3(TC_THREADS), SMEM, stream, map_k, map_v, a);
+  hb_launch(kernel, dim3(n_tiles * a.nkv), dim3(TC_THREADS), SMEM, stream, map_k, map_v, a);
   return hb_check_launch();
 }
 
