@@ -34,6 +34,7 @@ class ModelPlan:
     head: OutputHead
     schedule: List[Run] = field(default_factory=list)
     embedding_prefix: str = "model.embed_tokens."
+    position_prefix: str = "model.position."
     final_norm_prefix: str = "model.norm."
     head_prefix: str = "lm_head."
     # checkpoint name -> name whose tensor stands in when the first is absent
@@ -61,6 +62,8 @@ class ModelPlan:
     def named_parts(self) -> Iterator[Tuple[str, Part]]:
         """(checkpoint prefix, part) of every part that may own tensors."""
         yield self.embedding_prefix, self.embedding
+        if self.position is not None:
+            yield self.position_prefix, self.position     # tensors only if the encoding is learned
         for prefix, block in zip(self.layer_prefixes, self.layers):
             for sub, part in block.named_parts():
                 yield prefix + sub, part

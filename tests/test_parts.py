@@ -316,3 +316,137 @@ def test_a_toy_mixer_with_state_of_its_own_is_registered_built_and_stepped():
             assert (whole_a[5] - whole_a[4]).abs().max() > 0
     finally:
         unregister_architecture("ToyMeanForCausalLM")
+
+
+# ---------------------------------------------------------------------- a toy feed-forward with routing, another position encoding
+def test_a_toy_routed_feed_forward_and_a_learned_position_encoding_are_registered_built_and_stepped():
+    """Two more parts defined here, not in the package: a feed-forward that sends every
+    token to the one of three small experts its router picks (router logits in float32),
+    and a position encoding that adds a learned row per position to the embedded tokens
+    (attention then runs without rotation).  A toy architecture uses the routed
+    feed-forward in every second layer.  The engine's logits are compared with a plain
+    computation on whole sequences written out below, and must not depend on how the
+    tokens are cut or batched."""
+    from helios_b200.config import DenseDecoderConfig, register_architecture, unregister_architecture
+    from helios_b200.engine.batch import StepEntry
+    from helios_b200.engine.core import EngineCore
+    from helios_b200.engine.model import DecoderModel
+    from helios_b200.parts import (FeedForward, ModelPlan, OutputHead, PositionEncoding, TokenEmbedding,
+                                   WeightSpec, part_class, register_part)
+
+    E, INNER, MAX_POS = 3, 40, 64
+
+    class RoutedFeedForward(FeedForward):
+        graph_safe = False                      # the tokens of an expert are gathered on the host's say
+
+        def __init__(self, width):
+            self.width = width
+
+        def weight_specs(self):
+            specs = {"router.weight": WeightSpec((E, self.width), std=0.3)}
+            for e in range(E):
+                specs[f"experts.{e}.up.weight"] = WeightSpec((INNER, self.width), std=0.3)
+                specs[f"experts.{e}.down.weight"] = WeightSpec((self.width, INNER), std=0.3)
+            return specs
+
+        def bind(self, tensors):
+            self.t = tensors
+
+        def forward(self, ctx, x):
+            choice = (x.float() @ self.t["router.weight"].float().T).argmax(-1)
+            out = torch.zeros_like(x)
+            for e in range(E):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel():
+                    h = torch.relu(x[rows].float() @ self.t[f"experts.{e}.up.weight"].float().T)
+                    out[rows] = (h @ self.t[f"experts.{e}.down.weight"].float().T).to(x.dtype)
+            return out
+
+    class LearnedPositions(PositionEncoding):
+        def __init__(self, width):
+            self.width = width
+
+        def weight_specs(self):
+            return {"weight": WeightSpec((MAX_POS, self.width), std=0.5)}
+
+        def bind(self, tensors):
+            self.table = tensors["weight"]
+
+        def embed(self, ctx, hidden):
+            return hidden + self.table.float().index_select(0, ctx.positions.long())
+
+    register_part("feed_forward", "toy_routed", RoutedFeedForward, replace=True)
+    register_part("position_encoding", "toy_learned", LearnedPositions, replace=True)
+
+    def build(cfg):
+        norm, block = part_class("norm", "rmsnorm"), part_class("block", "pre_norm")
+        attn, dense, routed = (part_class("mixer", "gqa_attention"), part_class("feed_forward", "swiglu"),
+                               part_class("feed_forward", "toy_routed"))
+        layers = [block(norm(cfg.hidden_size, cfg.rms_norm_eps),
+                        attn(cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
+                             cfg.attention_scale, False, rotary=False),
+                        norm(cfg.hidden_size, cfg.rms_norm_eps),
+                        routed(cfg.hidden_size) if i % 2 else dense(cfg.hidden_size, cfg.intermediate_size))
+                  for i in range(cfg.num_hidden_layers)]
+        return ModelPlan(config=cfg, embedding=TokenEmbedding(cfg.vocab_size, cfg.hidden_size),
+                         position=part_class("position_encoding", "toy_learned")(cfg.hidden_size),
+                         layers=layers, layer_prefixes=[f"model.layers.{i}." for i in range(cfg.num_hidden_layers)],
+                         final_norm=norm(cfg.hidden_size, cfg.rms_norm_eps),
+                         head=OutputHead(cfg.vocab_size, cfg.hidden_size))
+
+    experts_used = set()
+
+    def plain(cfg, plan, toks):
+        """float64, whole sequence, from the tensors the parts were given."""
+        f = lambda t: t.double().cpu()
+        n = len(toks)
+        h = f(plan.embedding.table)[toks] + f(plan.position.table)[:n]
+        nh, nkv, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        for block in plan.layers:
+            x = plain_model.rms_norm(h, f(block.mixer_norm.weight), cfg.rms_norm_eps)
+            qkv = x @ f(block.mixer.w_qkv).T
+            q, k, v = qkv.split([nh * hd, nkv * hd, nkv * hd], dim=-1)
+            a = plain_model.causal_attention(q.reshape(n, nh, hd), k.reshape(n, nkv, hd), v.reshape(n, nkv, hd),
+                                             cfg.attention_scale, None)
+            h = h + a.reshape(n, nh * hd) @ f(block.mixer.w_o).T
+            x = plain_model.rms_norm(h, f(block.ffn_norm.weight), cfg.rms_norm_eps)
+            if isinstance(block.ffn, RoutedFeedForward):
+                t = {k_: f(v_) for k_, v_ in block.ffn.t.items()}
+                choice = (x @ t["router.weight"].T).argmax(-1)
+                experts_used.update(choice.tolist())
+                y = torch.zeros_like(x)
+                for i in range(n):
+                    e = int(choice[i])
+                    y[i] = torch.relu(x[i] @ t[f"experts.{e}.up.weight"].T) @ t[f"experts.{e}.down.weight"].T
+                h = h + y
+            else:
+                gu = f(block.ffn.w_gate_up)
+                h = h + plain_model.swiglu(x, gu[: block.ffn.inner], gu[block.ffn.inner:], f(block.ffn.w_down))
+        x = plain_model.rms_norm(h, f(plan.final_norm.weight), cfg.rms_norm_eps)
+        return x @ f(plan.head.weight).T
+
+    register_architecture("ToyRoutedForCausalLM", lambda d: DenseDecoderConfig.from_hf(d, "ToyRoutedForCausalLM"),
+                          build, replace=True)
+    try:
+        cfg_json = dict(TINY_LLAMA, architectures=["ToyRoutedForCausalLM"], num_hidden_layers=4, rope_scaling=None)
+        model = DecoderModel.from_config(cfg_json, seed=11, dtype="float32")
+        assert not model.plan.graph_safe
+        assert any(name.startswith("model.position.") for name in
+                   __import__("helios_b200.weights", fromlist=["expected_tensors"]).expected_tensors(model.plan))
+        core = EngineCore(model, page_size=8, num_pages=32, max_slots=2)
+        a, b = random_tokens(256, 29, 3), random_tokens(256, 12, 4)
+        whole_a = core.step([StepEntry("a", a, list(range(29)))]).clone()
+        core.end("a")
+        want_a = plain(model.config, model.plan, a)
+        assert_logits_close(whole_a, want_a, "float32", "toy routed model, whole")
+        assert experts_used == set(range(E))       # else the test shows nothing of the routing
+        got_a, got_b = [], []
+        for (sa, ea), (sb, eb) in zip([(0, 7), (7, 8), (8, 27), (27, 29)], [(0, 2), (2, 5), (5, 11), (11, 12)]):
+            out = core.step([StepEntry("a", a[sa:ea], list(range(ea - sa))),
+                             StepEntry("b", b[sb:eb], list(range(eb - sb)))])
+            got_a.append(out[: ea - sa].clone())
+            got_b.append(out[ea - sa:].clone())
+        assert_logits_close(torch.cat(got_a), want_a, "float32", "toy routed model, in portions beside another")
+        assert_logits_close(torch.cat(got_b), plain(model.config, model.plan, b), "float32", "toy routed model, b")
+    finally:
+        unregister_architecture("ToyRoutedForCausalLM")
