@@ -1,0 +1,62 @@
+"""One layer with the layer sizes of Llama-3.1-8B (width 4096, 32 query / 8 KV heads of 128,
+feed-forward 14336; small vocabulary) in bfloat16 against the plain implementation: the
+tile shapes, split counts and kernel choices of the real sizes, which the tiny
+configurations never reach.  A prompt long enough for the two-SM products and the tcgen05
+attention, the same prompt in portions, single decoded tokens, and a batch of eight."""
+import pytest
+import torch
+
+import plain_model
+from conftest import assert_logits_close, random_tokens
+from test_parts import _export
+
+pytestmark = pytest.mark.gpu
+
+CONFIG = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "vocab_size": 1024, "hidden_size": 4096, "intermediate_size": 14336, "num_hidden_layers": 1,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128,
+    "max_position_embeddings": 8192, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+    "attention_bias": False, "tie_word_embeddings": False, "hidden_act": "silu",
+}
+
+
+def test_one_layer_of_the_benchmarks_sizes_matches_the_plain_implementation():
+    from helios_b200.engine.batch import StepEntry
+    from helios_b200.engine.core import EngineCore
+    from helios_b200.engine.model import DecoderModel
+
+    model = DecoderModel.from_config(CONFIG, seed=5, dtype="bfloat16")
+    weights = _export(model.plan)
+    core = EngineCore(model, page_size=16, num_pages=400, max_slots=10)
+    n = 1100
+    toks = random_tokens(CONFIG["vocab_size"], n + 3, 77)
+    want = plain_model.forward_logits(CONFIG, weights, toks, dtype=torch.float32)
+    places = [0, 1, 127, 128, 129, 500, 1023, 1024, n - 2, n - 1]
+
+    # whole prompt in one step, then three tokens one by one
+    got = core.step([StepEntry("whole", toks[:n], places)])
+    assert_logits_close(got, want[places], "bfloat16", "1,100 tokens in one step")
+    for i in range(3):
+        got = core.step([StepEntry("whole", [toks[n + i]], [0])])
+        assert_logits_close(got, want[n + i:n + i + 1], "bfloat16", f"decoded token {i}")
+    core.end("whole")
+
+    # the same prompt in portions of 700 and 400 tokens (other kernels for the products)
+    core.step([StepEntry("cut", toks[:700], [])])
+    got = core.step([StepEntry("cut", toks[700:n], [0, n - 701])])
+    assert_logits_close(got, want[[700, n - 1]], "bfloat16", "portions of 700 and 400 tokens")
+    core.end("cut")
+
+    # eight requests decoding together (twice: the second step of a batch size is a captured graph)
+    prompts = [random_tokens(CONFIG["vocab_size"], 20 + 9 * i, 100 + i) for i in range(8)]
+    refs = [plain_model.forward_logits(CONFIG, weights, p, dtype=torch.float32) for p in prompts]
+    core.step([StepEntry(f"b{i}", p[:-3], []) for i, p in enumerate(prompts)])
+    for back in (3, 2, 1):
+        got = core.step([StepEntry(f"b{i}", [p[-back]], [0]) for i, p in enumerate(prompts)])
+        want8 = torch.stack([r[len(p) - back] for r, p in zip(refs, prompts)])
+        assert_logits_close(got, want8, "bfloat16", f"batch of eight, {back} from the end")
+    from helios_b200.csrc import ops
+    ops.check_kernel_errors()
