@@ -74,6 +74,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   constexpr uint32_t S_COL = 0, O_COL = 128;
 
   extern __shared__ unsigned char smem_raw[];
+#ifdef HB_ATTN_TIMING
+  const long long t_entry = clock64();
+#endif
   pdl_launch_dependents();
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* aligned = smem_raw + (base - smem_u32(smem_raw));
@@ -100,11 +103,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   if (threadIdx.x == 0) {
     mbar_init(bar(0), 1); mbar_init(bar(1), 1);
     mbar_init(bar(2), 1); mbar_init(bar(3), 1);
-    mbar_init(bar(4), SOFTMAX_THREADS);
+    mbar_init(bar(4), SOFTMAX_THREADS / 32);     // one arrival per softmax warp
     mbar_init(bar(5), 1);
-    mbar_init(bar(6), SOFTMAX_THREADS);
+    mbar_init(bar(6), SOFTMAX_THREADS / 32);
     mbar_init(bar(7), 1);
-    mbar_init(bar(8), SOFTMAX_THREADS);
+    mbar_init(bar(8), SOFTMAX_THREADS / 32);
     mbar_init(bar(9), 1); mbar_init(bar(10), 1);
     mbar_init(bar(11), 1); mbar_init(bar(12), 1);
     *abort_flag = 0;
@@ -226,7 +229,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
           umma_bf16(tmem_base + O_COL, smem_desc(p_smem + (kk >> 2) * HALF_BYTES + (kk & 3) * 32),
-                    smem_desc_mn(vs + kk * 2048, HALF_BYTES, 1024), idesc_pv, kk ? 1u : 0u);
+                    smem_desc_mn(vs + kk * 2048, HALF_BYTES, 1024), idesc_pv, (it | kk) ? 1u : 0u);
         umma_commit(bar(11 + s));    // the V stage is free
         umma_commit(bar(7));         // O_tile complete
       }
@@ -248,30 +251,46 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     const int pr = sp + tl;                        // the row's position
     const int tid = threadIdx.x - 64;
 
-    // stage Q: rows = (token, head) pairs, swizzled K-major; invalid rows are zero
-    for (int idx = tid; idx < TILE * (HD / 8); idx += SOFTMAX_THREADS) {
-      const int row = idx / (HD / 8), c = idx - row * (HD / 8);
-      const int rt = t0 + row / G, rg = row % G;
-      uint4 val = make_uint4(0, 0, 0, 0);
-      if (rt < n_tok)
-        val = *reinterpret_cast<const uint4*>(a.q + (size_t)(tok0 + rt) * a.q_stride +
-                                              (size_t)(kvh * G + rg) * HD + c * 8);
-      st_shared_v4(q_smem + (c >> 3) * HALF_BYTES + swz(row, c & 7), val.x, val.y, val.z, val.w);
+    // stage Q: rows = (token, head) pairs, swizzled K-major; invalid rows are zero.  All
+    // loads of a thread are issued before the first store (one round trip, not one each).
+    {
+      constexpr int PER_THREAD = TILE * (HD / 8) / SOFTMAX_THREADS;
+      uint4 qv[PER_THREAD];
+#pragma unroll
+      for (int i = 0; i < PER_THREAD; ++i) {
+        const int idx = tid + i * SOFTMAX_THREADS;
+        const int row = idx / (HD / 8), c = idx - row * (HD / 8);
+        const int rt = t0 + row / G, rg = row % G;
+        qv[i] = make_uint4(0, 0, 0, 0);
+        if (rt < n_tok)
+          qv[i] = *reinterpret_cast<const uint4*>(a.q + (size_t)(tok0 + rt) * a.q_stride +
+                                                  (size_t)(kvh * G + rg) * HD + c * 8);
+      }
+#pragma unroll
+      for (int i = 0; i < PER_THREAD; ++i) {
+        const int idx = tid + i * SOFTMAX_THREADS;
+        const int row = idx / (HD / 8), c = idx - row * (HD / 8);
+        st_shared_v4(q_smem + (c >> 3) * HALF_BYTES + swz(row, c & 7), qv[i].x, qv[i].y, qv[i].z, qv[i].w);
+      }
     }
     fence_async_smem();
-    mbar_arrive(bar(4));
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar(4));
 
-    constexpr int OWN = HD / 2;                    // output columns this thread accumulates
-    float o_reg[OWN];
-#pragma unroll
-    for (int i = 0; i < OWN; ++i) o_reg[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
+    constexpr int OWN = HD / 2;                    // output columns this thread rescales and writes
+    // The output accumulates in tensor memory over all key tiles, relative to a reference
+    // maximum m_ref per row that is only moved when the true maximum has run ahead of it by
+    // more than LAG (then the output and the sum are rescaled); exponentials are at most
+    // 2^LAG meanwhile, and the final quotient does not depend on the reference.
+    constexpr float LAG = 8.f;
+    float m_ref = -INFINITY, l_run = 0.f;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     bool ok = true;
 
 #ifdef HB_ATTN_TIMING
     long long tphase[6] = {0, 0, 0, 0, 0, 0};
     long long tprev = clock64();
+    const long long t_loop = tprev;
 #define HB_TICK(i) { const long long now = clock64(); tphase[i] += now - tprev; tprev = now; }
 #else
 #define HB_TICK(i)
@@ -294,7 +313,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         for (int j = 0; j < 32; ++j) { sv[j] = v0[j]; sv[32 + j] = v1[j]; }
       }
       tc_fence_before();
-      mbar_arrive(bar(8));        // the score tile may be overwritten
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(8));        // the score tile may be overwritten
       if (masked_tile) {
         // columns of this thread's 64 keys the row may see: [lo, hi]
         const int col0 = key_base + half * 64;
@@ -304,49 +324,59 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         for (int j = 0; j < 64; ++j)
           if (j < lo || j > hi) sv[j] = -INFINITY;
       }
-      float mx = sv[0];
+      float mx4[4] = {sv[0], sv[1], sv[2], sv[3]};
 #pragma unroll
-      for (int j = 1; j < 64; ++j) mx = fmaxf(mx, sv[j]);
+      for (int j = 4; j < 64; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], sv[j]);
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       max_exchange[((it & 1) * 2 + half) * TILE + m] = mx;
       named_barrier(2 + quarter, 64);
       mx = fmaxf(mx, max_exchange[((it & 1) * 2 + (half ^ 1)) * TILE + m]) * a.scale_log2;
       HB_TICK(1)
-      const float m_new = fmaxf(m_run, mx);
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float corr = fast_exp2(m_run - m_use);
-      m_run = m_new;
-      // O_tile of the tile before was computed under the work above.  The output in
-      // registers lacks it and is relative to the old maximum: add it and rescale, before P,
-      // which that product still read, is overwritten.
+      // move the reference?  Both threads of a row see the same numbers; the rows of a warp
+      // decide together, because tensor memory is read and written by whole warps.
+      const bool move = mx > m_ref + LAG || (m_ref == -INFINITY && mx > -INFINITY);
+      const bool rescale = __any_sync(0xffffffffu, move) && it > 0;
+      float factor = 1.f;
+      if (move) {
+        factor = fast_exp2(m_ref - mx);          // 0 while nothing has been added yet
+        m_ref = mx;
+        l_run *= factor;
+      }
+      const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+      // the exponentials of this tile, packed, wait in registers: the product of the tile
+      // before, which still reads P, finishes under this work
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t packed[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float p0 = fast_exp2(fmaf(sv[2 * j], a.scale_log2, -m_use));
+        const float p1 = fast_exp2(fmaf(sv[2 * j + 1], a.scale_log2, -m_use));
+        sum4[j & 3] += p0 + p1;
+        __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+        packed[j] = *reinterpret_cast<uint32_t*>(&pk);
+      }
+      l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      HB_TICK(2)
       if (it > 0) {
+        // P of the tile before has been read, and its product is in the output
         if (!mbar_wait(bar(7), (it - 1) & 1, abort_flag, a.error, 16)) { ok = false; break; }
         tc_fence_after();
+        if (rescale) {
 #pragma unroll
-        for (int c = 0; c < OWN / 32; ++c) {
-          float v[32];
-          tmem_ld32(lane_addr + O_COL + half * OWN + c * 32, v);
+          for (int c = 0; c < OWN / 32; ++c) {
+            float v[32];
+            tmem_ld32(lane_addr + O_COL + half * OWN + c * 32, v);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) o_reg[c * 32 + j] = (o_reg[c * 32 + j] + v[j]) * corr;
+            for (int j = 0; j < 32; ++j) v[j] *= factor;
+            tmem_st32(lane_addr + O_COL + half * OWN + c * 32, v);
+          }
         }
-        tc_fence_before();
       }
       HB_TICK(4)
-      float sum = 0.f;
 #pragma unroll
-      for (int c8 = 0; c8 < 8; ++c8) {
-        uint32_t packed[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float p0 = fast_exp2(fmaf(sv[c8 * 8 + 2 * e], a.scale_log2, -m_use));
-          const float p1 = fast_exp2(fmaf(sv[c8 * 8 + 2 * e + 1], a.scale_log2, -m_use));
-          sum += p0 + p1;
-          __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
-          packed[e] = *reinterpret_cast<uint32_t*>(&pk);
-        }
-        st_shared_v4(p_smem + half * HALF_BYTES + swz(m, c8), packed[0], packed[1], packed[2], packed[3]);
-      }
-      HB_TICK(2)
-      l_run = l_run * corr + sum;
+      for (int c8 = 0; c8 < 8; ++c8)
+        st_shared_v4(p_smem + half * HALF_BYTES + swz(m, c8), packed[4 * c8], packed[4 * c8 + 1],
+                     packed[4 * c8 + 2], packed[4 * c8 + 3]);
       // V rows of keys past the last position (unwritten slots, pages that were not copied)
       // must not be NaN or Inf when they meet their zero probabilities
       {
@@ -368,10 +398,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       }
       tc_fence_before();
       fence_async_smem();
-      mbar_arrive(bar(6));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(6));
       HB_TICK(3)
-      HB_TICK(5)      // O_tile(it) is added at the start of the next tile's work
+      HB_TICK(5)
     }
+    float o_reg[OWN];
+#pragma unroll
+    for (int i = 0; i < OWN; ++i) o_reg[i] = 0.f;
     if (ok && n_it > 0) {
       if (mbar_wait(bar(7), (n_it - 1) & 1, abort_flag, a.error, 16)) {
         tc_fence_after();
@@ -380,7 +414,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
           float v[32];
           tmem_ld32(lane_addr + O_COL + half * OWN + c * 32, v);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) o_reg[c * 32 + j] += v[j];
+          for (int j = 0; j < 32; ++j) o_reg[c * 32 + j] = v[j];
         }
         tc_fence_before();
       } else {
@@ -388,10 +422,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       }
     }
 #ifdef HB_ATTN_TIMING
+    if (threadIdx.x == 64 && (blockIdx.x == 0 || blockIdx.x == 300))
+      printf("block %d: entry->loop %lld, loop %lld cycles\n", blockIdx.x, t_loop - t_entry, clock64() - t_loop);
     if (threadIdx.x == 64 && blockIdx.x == 0 && blockIdx.y == 0)
-      printf("tiles %d: wait_s %lld  pass1 %lld  pass2 %lld  zero+arrive %lld  wait_o %lld  acc %lld (cycles per tile)\n",
-             n_it, tphase[0] / n_it, tphase[1] / n_it, tphase[2] / n_it, tphase[3] / n_it, tphase[4] / n_it,
-             tphase[5] / n_it);
+      printf("tiles %d: wait_s %lld  pass1 %lld  exps %lld  store+arrive %lld  wait_o+rescale %lld (cycles per tile)\n",
+             n_it, tphase[0] / n_it, tphase[1] / n_it, tphase[2] / n_it, tphase[3] / n_it, tphase[4] / n_it);
 #endif
 
     // the two threads of a row add their sums
