@@ -9,11 +9,13 @@
 //                -> a two-stage ring in shared memory
 //     MMA 1      S[128 x 128] = Q K^T           (Q staged once, K-major; K tile K-major)
 //     softmax    8 warps, two threads per row: scale, mask by position (causal, window),
-//                running maximum and sum in float32, P = exp2(.) as bfloat16 into shared
+//                maximum and sum in float32, P = exp2(.) as bfloat16 into shared
 //                memory in the operand layout
-//     MMA 2      O_tile[128 x hd] = P V         (V tile as an MN-major operand)
-//     the same warps add O_tile into the float32 output they keep in registers, rescaled
-//                when the maximum moved.
+//     MMA 2      O[128 x hd] += P V             (V tile as an MN-major operand); the output
+//                accumulates in tensor memory over all key tiles, relative to a reference
+//                maximum per row that the softmax warps move (rescaling output and sum) only
+//                when the true maximum has run ahead of it by more than 2^8; they read the
+//                output back once, at the end, and divide by the sum.
 // Formulas: python/helios/exec/paged_attn.py:368-408 (scores * scale, key position > query
 // position masked, softmax in float32, times V), head mapping :248-261.
 //
