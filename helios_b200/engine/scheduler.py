@@ -220,7 +220,7 @@ class Scheduler:
             if not item.sample:
                 continue
             seq = self.seqs[item.seq_id]
-            if seq.is_finished or seq not in self.running:
+            if seq.state is not SeqState.RUNNING:
                 continue          # finished, aborted or preempted while the step ran
             if item.seq_id not in tokens:
                 raise RuntimeError(f"the executor returned no token for sequence {item.seq_id}")
@@ -246,7 +246,7 @@ class Scheduler:
         seqs = []
         for item in prev.items:
             seq = self.seqs[item.seq_id]
-            if not item.sample or seq.is_finished or seq not in self.running:
+            if not item.sample or seq.state is not SeqState.RUNNING:
                 return None
             if seq.num_pending_tokens != 0:
                 return None       # ``launched(prev)`` has not been called

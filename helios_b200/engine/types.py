@@ -60,7 +60,7 @@ class Request:
         return len(self.prompt_token_ids)
 
 
-@dataclass
+@dataclass(eq=False)       # an entity: two sequences are equal only if they are the same object
 class Sequence:
     """Scheduler-side state of one request (python/helios/core/types.py:105-195)."""
 

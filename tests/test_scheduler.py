@@ -422,3 +422,14 @@ def test_a_request_that_stops_on_the_token_in_flight_is_dropped_from_the_step_ah
     sched.complete(p2, {0: 99, 1: 51})            # the token computed for "a" is ignored
     assert sched.seqs[0].output_token_ids == [2] and sched.seqs[1].output_token_ids == [50, 51]
     sched.check_invariants()
+
+
+def test_sequences_are_entities_not_values():
+    """Membership tests on the running list must not compare token lists field by field
+    (with hundreds of running requests that made every step quadratic)."""
+    sched, _ = make()
+    a = sched.add_request(req(5, rid="same"))
+    b = sched.add_request(req(5, rid="same"))
+    sa, sb = sched.seqs[a], sched.seqs[b]
+    assert sa is not sb and sa != sb and sa == sa
+    assert sb not in [sa]
