@@ -428,18 +428,33 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
 
 
 #: Token counts between the decode kernel's range (up to 128, weights streamed once with
-#: the tokens on the MMA N axis) and the prefill kernel's (from 1,024 up, pairs of SMs on
-#: 256x256 tiles) leave most SMs of the two-SM kernel without a tile.  There plain products
-#: (no bias, bfloat16 out) go to the library (cuBLAS through torch), which the reference uses
-#: for every product (python/helios/exec/model.py:170-181).  Fused products (bias, float32
-#: logits, SwiGLU from 384 tokens up) always run on this package's kernel.  (0, 0) turns
-#: the library off.
-GEMM_LIBRARY_TOKEN_RANGE = (129, 1023)
+#: the tokens on the MMA N axis) and the prefill kernel's (pairs of SMs on 256x256 tiles;
+#: on a par with the library from 512 tokens) leave most SMs of the two-SM kernel without a
+#: tile.  There plain products (no bias, bfloat16 out) go to the library (cuBLAS through
+#: torch), which the reference uses for every product (python/helios/exec/model.py:170-181).
+#: Fused products (bias, float32 logits, SwiGLU from 384 tokens up) always run on this
+#: package's kernel.  (0, 0) turns the library off.
+GEMM_LIBRARY_TOKEN_RANGE = (129, 511)
+#: The library chooses its kernel per shape, which takes about a millisecond of host time
+#: the first time a shape is seen; token counts are rounded up to a multiple of this (on a
+#: zero-padded copy of the rows) so that a serving run meets a handful of shapes, not hundreds.
+GEMM_LIBRARY_TOKEN_STEP = 64
 
 
 def _library_range(tokens: int) -> bool:
     lo, hi = GEMM_LIBRARY_TOKEN_RANGE
     return lo <= tokens <= hi
+
+
+def _library_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
+    T = x.shape[0]
+    step = GEMM_LIBRARY_TOKEN_STEP
+    padded = -(-T // step) * step if step > 1 else T
+    if padded == T:
+        return torch.nn.functional.linear(x, weight, bias)
+    rows = x.new_zeros((padded, x.shape[1]))
+    rows[:T].copy_(x)
+    return torch.nn.functional.linear(rows, weight, bias)[:T]
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -453,7 +468,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     if tc_gemm_supported(x, weight) and not (bias is None and _library_range(x.shape[0])):
         return linear_bf16(x, weight, bias)
     b = None if bias is None else bias.to(torch.bfloat16)
-    return torch.nn.functional.linear(x, weight, b)
+    return _library_linear(x, weight, b)
 
 
 def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
