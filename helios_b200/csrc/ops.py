@@ -45,7 +45,9 @@ def _check(t: torch.Tensor, name: str, dtype=None, ndim=None) -> None:
 
 
 def _stream() -> c_void_p:
-    return c_void_p(torch.cuda.current_stream().cuda_stream)
+    # the raw handle of torch's current stream on the current device (capture streams
+    # included); the Python-level Stream object costs several microseconds a launch
+    return c_void_p(torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice()))
 
 
 def _p(t: Optional[torch.Tensor]) -> c_void_p:
