@@ -336,7 +336,8 @@ def cluster_capacity(bn: int, glu: bool, size: int) -> int:
 def gemm_plan(T: int, N: int, K: int, glu: bool):
     """(swap_bn, k_splits) of the tensor-core product for T tokens, N result features.
     Up to 128 tokens run swapped (features on the MMA M axis).  When the tiles alone do not
-    fill the SMs, the reduction is split (at least 8 k-blocks a slice): with slices as
+    fill the SMs, the reduction is split (at least 2 k-blocks a slice; short reductions of
+    small models are bound by latency, and more blocks shorten them): with slices as
     thread-block clusters, the count that keeps the most blocks resident in ONE round of
     clusters; else the count that fills the resident blocks."""
     k_blocks = -(-K // 64)
@@ -352,7 +353,7 @@ def gemm_plan(T: int, N: int, K: int, glu: bool):
         slots = _SM_COUNT
     splits = 1
     if tiles < slots:
-        most_k = max(1, k_blocks // 8)
+        most_k = max(1, k_blocks // 2)
         if GEMM_CLUSTER_REDUCE and _cluster_fits(bn, glu):
             best = 0
             for s in range(1, min(8, most_k) + 1):
