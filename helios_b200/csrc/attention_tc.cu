@@ -2,8 +2,9 @@
 // cores (tcgen05.mma with the score and output tiles in tensor memory), bfloat16,
 // head sizes 64 and 128.
 //
-// A block takes one KV head and 128 query rows = 128/G consecutive tokens of one request
-// times the G query heads that share the KV head, and walks the keys the rows may see in
+// A block takes one KV head and up to 128 query rows = floor(128/G) consecutive tokens of one
+// request times the G query heads that share the KV head (the last rows idle when G does
+// not divide 128), and walks the keys the rows may see in
 // tiles of 128:
 //     TMA        pages of K and V (boxes of page_size x 64 elements, 128-byte swizzle)
 //                -> a two-stage ring in shared memory
@@ -249,7 +250,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     const int half = sw >> 2;                      // which 64 keys / which half of hd this thread owns
     const int m = quarter * 32 + lane;             // row of the tile
     const int tl = t0 + m / G, g = m % G;
-    const bool row_valid = tl < n_tok;
+    const bool row_valid = m < TQ * G && tl < n_tok;       // rows beyond TQ * G idle when G does not divide 128
     const int pr = sp + tl;                        // the row's position
     const int tid = threadIdx.x - 64;
 
@@ -264,7 +265,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         const int row = idx / (HD / 8), c = idx - row * (HD / 8);
         const int rt = t0 + row / G, rg = row % G;
         qv[i] = make_uint4(0, 0, 0, 0);
-        if (rt < n_tok)
+        if (row < TQ * G && rt < n_tok)
           qv[i] = *reinterpret_cast<const uint4*>(a.q + (size_t)(tok0 + rt) * a.q_stride +
                                                   (size_t)(kvh * G + rg) * HD + c * 8);
       }
@@ -501,7 +502,7 @@ HB_EXPORT int hb_attention_prefill_tc(void* out, const void* q, int q_stride, co
   if (n_tiles <= 0) return HB_OK;
   if (nkv <= 0 || nh % nkv != 0 || error == nullptr) return HB_BAD_ARGUMENT;
   const int G = nh / nkv;
-  if (G > TILE || TILE % G != 0) return HB_BAD_ARGUMENT;
+  if (G > TILE) return HB_BAD_ARGUMENT;
   if (page_size < 8 || page_size % 8 != 0 || TILE % page_size != 0) return HB_BAD_ARGUMENT;
   if (((uintptr_t)q & 15) || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15) || (q_stride & 7))
     return HB_BAD_ARGUMENT;

@@ -644,7 +644,7 @@ def tc_attention_supported(num_heads: int, num_kv_heads: int, head_dim: int, pag
     """Sizes the tcgen05 prefill attention kernel takes."""
     group = num_heads // max(1, num_kv_heads)
     return (head_dim in (64, 128) and num_heads % num_kv_heads == 0 and group <= 128
-            and 128 % group == 0 and page_size >= 8 and page_size % 8 == 0 and 128 % page_size == 0)
+            and page_size >= 8 and page_size % 8 == 0 and 128 % page_size == 0)
 
 
 def attention_prefill_tc(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,

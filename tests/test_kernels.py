@@ -341,7 +341,8 @@ def test_sampled_frequencies_follow_the_distribution():
 
 
 @pytest.mark.parametrize("nh,nkv,hd,page", [(32, 8, 128, 16), (8, 8, 128, 8), (16, 2, 64, 32), (4, 1, 64, 128),
-                                            (16, 1, 128, 64), (2, 1, 64, 16)])
+                                            (16, 1, 128, 64), (2, 1, 64, 16), (28, 4, 128, 16), (14, 2, 64, 16),
+                                            (5, 1, 128, 32), (6, 2, 64, 8)])
 @pytest.mark.parametrize("window", [None, 100, 300])
 def test_prefill_attention_tcgen05(nh, nkv, hd, page, window):
     """The tensor-memory attention kernel: ragged requests, portions that start deep in the
@@ -357,11 +358,11 @@ def test_prefill_attention_tcgen05(nh, nkv, hd, page, window):
 
 
 def test_tcgen05_attention_refuses_sizes_it_does_not_take():
-    assert not ops().tc_attention_supported(28, 4, 128, 16)      # groups of 7 do not fill 128 rows
+    assert ops().tc_attention_supported(28, 4, 128, 16)          # groups of 7: 18 tokens a tile, two rows idle
     assert not ops().tc_attention_supported(32, 8, 96, 16)
     assert not ops().tc_attention_supported(32, 8, 128, 5)
-    case = make_paged_case([(0, 20)], 6, 2, 64, 16, torch.bfloat16, DEV)
+    case = make_paged_case([(0, 20)], 6, 2, 96, 16, torch.bfloat16, DEV)
     tiles = ops().query_tiles([20], 42, DEV)
     with pytest.raises(ops().KernelError):
         ops().attention_prefill_tc(case.qkv, case.k_pages, case.v_pages, case.table, tiles, case.cu_tokens,
-                                   case.start_pos, 6, 2, 64, 16, None, 0.125)
+                                   case.start_pos, 6, 2, 96, 16, None, 0.125)
