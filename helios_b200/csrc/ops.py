@@ -440,7 +440,7 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
 GEMM_LIBRARY_TOKEN_RANGE = (129, 511)
 #: The library chooses its kernel per shape, which takes about a millisecond of host time
 #: the first time a shape is seen; token counts are rounded up to a multiple of this (on a
-#: zero-padded copy of the rows) so that a serving run meets a handful of shapes, not hundreds.
+#: padded copy of the rows) so that a serving run meets a handful of shapes, not hundreds.
 GEMM_LIBRARY_TOKEN_STEP = 64
 
 
@@ -455,7 +455,7 @@ def _library_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.
     padded = -(-T // step) * step if step > 1 else T
     if padded == T:
         return torch.nn.functional.linear(x, weight, bias)
-    rows = x.new_zeros((padded, x.shape[1]))
+    rows = x.new_empty((padded, x.shape[1]))      # what the spare rows hold reaches no result row
     rows[:T].copy_(x)
     return torch.nn.functional.linear(rows, weight, bias)[:T]
 
