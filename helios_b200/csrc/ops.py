@@ -44,14 +44,16 @@ def _check(t: torch.Tensor, name: str, dtype=None, ndim=None) -> None:
         raise KernelError(f"{name} must have {ndim} dimensions, got shape {tuple(t.shape)}")
 
 
-def _stream() -> c_void_p:
+def _stream() -> int:
     # the raw handle of torch's current stream on the current device (capture streams
     # included); the Python-level Stream object costs several microseconds a launch
-    return c_void_p(torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice()))
+    return torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice())
 
 
-def _p(t: Optional[torch.Tensor]) -> c_void_p:
-    return c_void_p(0 if t is None else t.data_ptr())
+def _p(t: Optional[torch.Tensor]) -> int:
+    # plain integers: ctypes converts them by the declared argument types, which costs less
+    # than building a c_void_p object per argument
+    return 0 if t is None else t.data_ptr()
 
 
 #: launches of this package's own kernels since import (library products are not counted)
@@ -196,8 +198,8 @@ def rope_kv_write(qkv: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[
             [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
     _run(f(_p(qkv), _p(cos), _p(sin), _p(positions), _p(seq_of_token), _p(block_table),
-           block_table.shape[1], _p(k_pages) if write_cache else c_void_p(0),
-           _p(v_pages) if write_cache else c_void_p(0), T, num_heads, num_kv_heads, head_dim,
+           block_table.shape[1], _p(k_pages) if write_cache else 0,
+           _p(v_pages) if write_cache else 0, T, num_heads, num_kv_heads, head_dim,
            rot, page_size, 1 if write_cache else 0, _dt(qkv.dtype), _stream()), "rope_kv_write")
 
 
@@ -333,7 +335,19 @@ def cluster_capacity(bn: int, glu: bool, size: int) -> int:
     return _cluster_capacity[key]
 
 
+_gemm_plans = {}
+
+
 def gemm_plan(T: int, N: int, K: int, glu: bool):
+    """Cached ``_gemm_plan``."""
+    key = (T, N, K, bool(glu), GEMM_CLUSTER_REDUCE)
+    plan = _gemm_plans.get(key)
+    if plan is None:
+        plan = _gemm_plans[key] = _gemm_plan(T, N, K, glu)
+    return plan
+
+
+def _gemm_plan(T: int, N: int, K: int, glu: bool):
     """(swap_bn, k_splits) of the tensor-core product for T tokens, N result features.
     Up to 128 tokens run swapped (features on the MMA M axis).  When the tiles alone do not
     fill the SMs, the reduction is split (at least 2 k-blocks a slice; short reductions of
