@@ -422,6 +422,7 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
   const int kvh = blockIdx.y / head_blocks, hb = blockIdx.y - kvh * head_blocks;
   const int seq = q_tiles[2 * blockIdx.x], t0 = q_tiles[2 * blockIdx.x + 1];
   const int tok0 = cu_tokens[seq], n_tok = cu_tokens[seq + 1] - tok0;
+  if (t0 >= n_tok) return;      // padding of a captured step's tile list
   const int sp = start_pos[seq];
   const int BQ = 16 * token_subtiles;
   const int p_first = sp + t0;

@@ -132,7 +132,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const int p_last = sp + min(n_tok, t0 + TQ) - 1;
   const int k_min = (a.window > 0 && p_first - a.window + 1 > 0) ? p_first - a.window + 1 : 0;
   const int kt_begin = k_min / TILE, kt_end = p_last / TILE + 1;
-  const int n_it = kt_end - kt_begin;
+  // a tile beyond the request's tokens (padding of a captured step's tile list) has no work
+  const int n_it = t0 < n_tok ? kt_end - kt_begin : 0;
   const int* table = a.block_table + (size_t)seq * a.bt_stride;
   const int ps = a.page_size;
   const int pages_per_tile = TILE / ps;

@@ -699,16 +699,42 @@ def attention_prefill_tc(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
     return out
 
 
-def query_tiles(tokens_per_seq, tile: int, device, start_positions=None) -> torch.Tensor:
-    """int32 [tiles, 2] on ``device``: (request, first local token) of every tile.  With
+#: first local token of a tile that holds no work (padding of a captured step's tile list)
+EMPTY_TILE_TOKEN = 1 << 30
+
+
+def query_tile_rows(tokens_per_seq, tile: int, start_positions=None):
+    """(request, first local token) of every tile of ``tile`` tokens, as a list.  With
     ``start_positions`` the tiles that see the most keys come first (they run longest)."""
     rows = [(i, t0) for i, n in enumerate(tokens_per_seq) for t0 in range(0, n, tile)]
     if start_positions is not None:
         rows.sort(key=lambda r: -(start_positions[r[0]] + r[1]))
-    host = torch.tensor(rows, dtype=torch.int32).reshape(-1, 2)
+    return rows
+
+
+def query_tiles(tokens_per_seq, tile: int, device, start_positions=None) -> torch.Tensor:
+    """int32 [tiles, 2] on ``device``: ``query_tile_rows`` copied over."""
+    host = torch.tensor(query_tile_rows(tokens_per_seq, tile, start_positions), dtype=torch.int32).reshape(-1, 2)
     if torch.device(device).type == "cuda":
         host = host.pin_memory()
     return host.to(device, non_blocking=True)
+
+
+def _step_tiles(ctx, tile: int, longest_first: bool, device) -> torch.Tensor:
+    """The step's query tiles of ``tile`` tokens: made once per step and tile size; a step
+    that runs as a captured graph hands out buffers that it refills itself
+    (``ctx.extras["tile_provider"]``)."""
+    key = ("q_tiles", tile, longest_first)
+    tiles = ctx.extras.get(key)
+    if tiles is None:
+        provider = ctx.extras.get("tile_provider")
+        if provider is not None:
+            tiles = provider(tile, longest_first)
+        else:
+            tiles = query_tiles([s.num_tokens for s in ctx.seqs], tile, device,
+                                [s.start_pos for s in ctx.seqs] if longest_first else None)
+        ctx.extras[key] = tiles
+    return tiles
 
 
 def attention(ctx, qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
@@ -728,22 +754,12 @@ def attention(ctx, qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
                                          scale, splits)
         if (ATTENTION_TCGEN05 and ctx.max_tokens_per_seq >= 16
                 and tc_attention_supported(num_heads, num_kv_heads, head_dim, page_size)):
-            tile = 128 // (num_heads // num_kv_heads)
-            key = ("q_tiles_tc", tile)
-            tiles = ctx.extras.get(key)
-            if tiles is None:
-                tiles = query_tiles([s.num_tokens for s in ctx.seqs], tile, qkv.device,
-                                    [s.start_pos for s in ctx.seqs])
-                ctx.extras[key] = tiles
+            tiles = _step_tiles(ctx, 128 // (num_heads // num_kv_heads), True, qkv.device)
             return attention_prefill_tc(qkv, k_pages, v_pages, block_table, tiles, ctx.cu_tokens,
                                         ctx.start_pos, num_heads, num_kv_heads, head_dim, page_size,
                                         window, scale)
         _heads, subtiles = prefill_tiling(num_heads, num_kv_heads)
-        key = ("q_tiles", 16 * subtiles)
-        tiles = ctx.extras.get(key)
-        if tiles is None:
-            tiles = query_tiles([s.num_tokens for s in ctx.seqs], 16 * subtiles, qkv.device)
-            ctx.extras[key] = tiles
+        tiles = _step_tiles(ctx, 16 * subtiles, False, qkv.device)
         return attention_prefill_bf16(qkv, k_pages, v_pages, block_table, tiles, ctx.cu_tokens,
                                       ctx.start_pos, num_heads, num_kv_heads, head_dim, page_size,
                                       window, scale)

@@ -91,10 +91,11 @@ class MetaLayout:
 
 
 def fill_meta(layout: MetaLayout, host: np.ndarray, entries: Sequence[StepEntry], cache,
-              pad_page: Optional[List[int]] = None) -> List[SeqSlice]:
+              pad_page: Optional[List[int]] = None, page_size: int = 1) -> List[SeqSlice]:
     """Write the step's arrays into ``host`` (int32, ``layout.total`` long).  Requests
-    beyond ``len(entries)`` up to ``layout.S`` are padding: one token at position 0 whose
-    keys and values go to the spare page ``pad_page[group]`` that no request ever gets."""
+    beyond ``len(entries)`` up to ``layout.S`` are padding whose keys and values go to the
+    spare page ``pad_page[group]`` that no request ever gets; an entry without a wanted place
+    gets its last token as one when the layout has a row for every request."""
     v = layout.host_views(host)
     token_ids, positions, seq_of_token, cu, start, ctx_len, slots, want = v[:8]
     tables = [t.reshape(layout.S, w) for t, w in zip(v[8:], layout.widths)]
@@ -114,20 +115,34 @@ def fill_meta(layout: MetaLayout, host: np.ndarray, entries: Sequence[StepEntry]
         for w in e.want:
             want[nw] = off + int(w)
             nw += 1
+        if not e.want and pad_page is not None:
+            want[nw] = off + n - 1           # a row nobody reads keeps the row count fixed
+            nw += 1
         off += n
         cu[i + 1] = off
         for g, t in enumerate(tables):
             row = cache.table(e.request_id, g)
             t[i, :len(row)] = row
-    for i in range(len(entries), layout.S):          # padding requests (captured graphs)
-        token_ids[off], positions[off], seq_of_token[off] = 0, 0, i
-        start[i], ctx_len[i], slots[i] = 0, 1, 0
+    # Padding requests (captured graphs): one token each at position 0; the last of them
+    # also takes the tokens that fill the step up to ``layout.T``, at positions 0, 1, ...
+    # Their keys and values all go to the spare page, whatever their position.
+    n_pad = layout.S - len(entries)
+    spare = layout.T - off - n_pad
+    if spare < 0 or (spare > 0 and n_pad == 0):
+        raise ValueError(f"{off} tokens of {len(entries)} requests do not fit a step of "
+                         f"{layout.T} tokens and {layout.S} requests")
+    for i in range(len(entries), layout.S):
+        n = 1 + (spare if i == layout.S - 1 else 0)
+        token_ids[off:off + n] = 0
+        positions[off:off + n] = np.arange(n, dtype=np.int32)
+        seq_of_token[off:off + n] = i
+        start[i], ctx_len[i], slots[i] = 0, n, 0
         want[nw] = off
         nw += 1
-        off += 1
+        off += n
         cu[i + 1] = off
         for g, t in enumerate(tables):
-            t[i, 0] = pad_page[g]
+            t[i, :-(-n // page_size)] = pad_page[g]
     return seqs
 
 

@@ -8,35 +8,82 @@ from typing import Hashable, List, Optional, Sequence
 import torch
 
 from ..cache.manager import KVCacheManager, bytes_per_page
-from .batch import MetaLayout, StepEntry, build_context, context_from_views, fill_meta
+from .batch import MetaLayout, SeqSlice, StepEntry, build_context, context_from_views, fill_meta
 from .model import DecoderModel
 
 
-class _DecodeGraph:
-    """A captured decode step for a fixed number of requests (padded) and fixed block-table
-    widths: static inputs, one CUDA graph, static logits."""
+class _StepGraph:
+    """A captured step for a fixed number of requests and tokens (both padded) and fixed
+    block-table widths: static inputs, one CUDA graph, static logits (one row a request).
+    Decode steps have one token a request; mixed steps (prompt portions beside decoded
+    tokens) are padded to a token count from ``EngineCore.GRAPH_TOKEN_BUCKETS``."""
 
-    def __init__(self, core: "EngineCore", bucket: int) -> None:
+    def __init__(self, core: "EngineCore", num_seqs: int, num_tokens: int) -> None:
         cache, model = core.cache, core.model
-        self.bucket = bucket
-        self.layout = MetaLayout(bucket, bucket, bucket, core.graph_table_widths)
+        self.num_seqs, self.num_tokens = num_seqs, num_tokens
+        self.decode = num_seqs == num_tokens
+        self.layout = MetaLayout(num_seqs, num_tokens, num_seqs, core.graph_table_widths)
         self.host = torch.empty(self.layout.total, dtype=torch.int32, pin_memory=True)
         self.dev = torch.zeros(self.layout.total, dtype=torch.int32, device=model.device)
-        self.ctx = context_from_views(self.layout, self.dev, [], model.dtype, model.device, 1,
-                                      core.graph_max_context)
+        # what kernels are chosen by must not change from step to step: a mixed step always
+        # counts as one with long portions
+        self.ctx = context_from_views(self.layout, self.dev, [], model.dtype, model.device,
+                                      1 if self.decode else num_tokens, core.graph_max_context)
         from ..csrc import ops
-        self.ctx.extras["decode_splits"] = ops.decode_splits(
-            bucket, max(s.num_kv_heads for s in cache.specs) if cache.specs else 1,
-            core.graph_max_context)
+        if self.decode:
+            self.ctx.extras["decode_splits"] = ops.decode_splits(
+                num_seqs, max(s.num_kv_heads for s in cache.specs) if cache.specs else 1,
+                core.graph_max_context)
+        self.ctx.extras["tile_provider"] = self._tiles
+        self._tile_buffers = {}          # (tile, longest first) -> (pinned rows, device rows)
+        self._page_size = cache.page_size
         self.graph = None
+        self.warmed = False
         self.logits = None
         self.launches = 0
         self.copied = torch.cuda.Event()
 
+    # query tiles of the prefill attention kernels: buffers of a fixed size, refilled with
+    # every step's tiles and padded with tiles that hold no work
+    def _tiles(self, tile: int, longest_first: bool) -> torch.Tensor:
+        key = (tile, longest_first)
+        if key not in self._tile_buffers:
+            if self.graph is not None or torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("a captured step met a tile size its warm-up run did not")
+            rows = self.num_tokens // tile + self.num_seqs
+            host = torch.empty((rows, 2), dtype=torch.int32, pin_memory=True)
+            dev = torch.zeros((rows, 2), dtype=torch.int32, device=self.dev.device)
+            self._tile_buffers[key] = (host, dev)
+            self._fill_tiles(key)
+        return self._tile_buffers[key][1]
+
+    def _fill_tiles(self, key) -> None:
+        from ..csrc import ops
+        tile, longest_first = key
+        host, dev = self._tile_buffers[key]
+        seqs = self.ctx.seqs
+        rows = ops.query_tile_rows([s.num_tokens for s in seqs], tile,
+                                   [s.start_pos for s in seqs] if longest_first else None)
+        view = host.numpy()
+        view[:, 0] = 0
+        view[:, 1] = ops.EMPTY_TILE_TOKEN
+        if rows:
+            view[:len(rows)] = rows
+        dev.copy_(host, non_blocking=True)
+
     def fill(self, entries, cache) -> None:
-        self.copied.synchronize()        # the staging buffer is free again
-        self.ctx.seqs = fill_meta(self.layout, self.host.numpy(), entries, cache, cache.pad_pages)
+        self.copied.synchronize()        # the staging buffers are free again
+        self.ctx.seqs = fill_meta(self.layout, self.host.numpy(), entries, cache, cache.pad_pages,
+                                  self._page_size)
+        # the padding requests count as requests of the step (the tile lists cover them)
+        off = sum(s.num_tokens for s in self.ctx.seqs)
+        for i in range(len(entries), self.num_seqs):
+            n = 1 + (self.num_tokens - off - (self.num_seqs - i) if i == self.num_seqs - 1 else 0)
+            self.ctx.seqs.append(SeqSlice(None, 0, 0, n, off))
+            off += n
         self.dev.copy_(self.host, non_blocking=True)
+        for key in self._tile_buffers:
+            self._fill_tiles(key)
         self.copied.record()
 
     def capture(self, core: "EngineCore") -> None:
@@ -57,6 +104,10 @@ class _DecodeGraph:
 
 
 class EngineCore:
+    #: token counts that mixed steps are padded to when they run as captured graphs; larger
+    #: steps keep the device busy longer than the host needs to launch them kernel by kernel
+    GRAPH_TOKEN_BUCKETS = (16, 32, 64, 128, 256, 512)
+
     def __init__(self, model: DecoderModel, page_size: int, num_pages, max_slots: int,
                  watermark: float = 0.0, max_model_len: Optional[int] = None,
                  poison_cache: Optional[float] = None, use_cuda_graphs: bool = True) -> None:
@@ -75,6 +126,7 @@ class EngineCore:
         self.graph_table_widths = [-(-self.graph_max_context // page_size)] * len(self.cache.groups)
         self._graphs = {}
         self._bucket_seen = {}
+        self.graph_max_tokens = max(self.GRAPH_TOKEN_BUCKETS)
 
     @staticmethod
     def pages_for_bytes(model: DecoderModel, page_size: int, kv_cache_bytes: int) -> int:
@@ -141,10 +193,8 @@ class EngineCore:
                 if any(self.cache.pages_needed(e.request_id, len(e.tokens))):
                     raise ValueError(f"request {e.request_id!r} has no pages for its "
                                      f"{len(e.tokens)} new tokens")
-        logits = None
-        if self.use_cuda_graphs and all(len(e.tokens) == 1 for e in entries):
-            logits = self._graph_step(entries, token_feed)
-        if logits is None:
+        ran, logits = self._graph_step(entries, token_feed) if self.use_cuda_graphs else (False, None)
+        if not ran:
             ctx = build_context(entries, self.cache, self.model.dtype, self.model.device)
             if token_feed is not None:
                 ctx.token_ids.copy_(token_feed)
@@ -156,32 +206,54 @@ class EngineCore:
         self.tokens_run += sum(len(e.tokens) for e in entries)
         return logits
 
-    # ------------------------------------------------------------------ captured decode steps
-    def _graph_step(self, entries, token_feed=None) -> Optional[torch.Tensor]:
+    # ------------------------------------------------------------------ captured steps
+    def _graph_step(self, entries, token_feed=None):
+        """(ran, logits).  A step runs as a captured graph when it fits a shape that has been
+        seen before: decode steps by their padded number of requests, mixed steps by their
+        padded numbers of requests and tokens.  The first step of a shape runs kernel by
+        kernel; the second runs kernel by kernel on the graph's static buffers (which fixes
+        what the graph will need); from the third on the graph is replayed."""
         S = len(entries)
-        bucket = 1
-        while bucket < S:
-            bucket *= 2
-        if any(self.cache.length(e.request_id) + 1 > self.graph_max_context for e in entries):
-            return None
-        g = self._graphs.get(bucket)
+        T = sum(len(e.tokens) for e in entries)
+        if any(len(e.want) > 1 for e in entries):
+            return False, None
+        if any(self.cache.length(e.request_id) + len(e.tokens) > self.graph_max_context for e in entries):
+            return False, None
+        if T == S:
+            num_seqs = 1
+            while num_seqs < S:
+                num_seqs *= 2
+            num_tokens = num_seqs
+        else:
+            num_seqs = 2                 # at least one padding request takes the spare tokens
+            while num_seqs < S + 1:
+                num_seqs *= 2
+            fits = [b for b in self.GRAPH_TOKEN_BUCKETS if b >= T + (num_seqs - S)]
+            if not fits or fits[0] > self.graph_max_context or token_feed is not None:
+                return False, None
+            num_tokens = fits[0]
+        key = (num_seqs, num_tokens)
+        g = self._graphs.get(key)
         if g is None:
-            seen = self._bucket_seen.get(bucket, 0)
-            self._bucket_seen[bucket] = seen + 1
+            seen = self._bucket_seen.get(key, 0)
+            self._bucket_seen[key] = seen + 1
             if seen == 0:
-                return None                    # first time: run eagerly (also warms everything up)
-            g = _DecodeGraph(self, bucket)
-            g.fill(entries, self.cache)
-            torch.cuda.synchronize(self.model.device)
-            g.capture(self)
-            self._graphs[bucket] = g
+                return False, None             # first time: run eagerly (also warms everything up)
+            g = self._graphs[key] = _StepGraph(self, num_seqs, num_tokens)
         g.fill(entries, self.cache)
         if token_feed is not None:
             g.ctx.token_ids[:S].copy_(token_feed)
-        logits = g.replay()
-        if all(len(e.want) == 1 for e in entries):
-            return logits[:S]
+        if g.graph is None and not g.warmed:
+            g.warmed = True
+            logits = self.model.forward(g.ctx, self.cache)          # on the static buffers, not captured
+        else:
+            if g.graph is None:
+                torch.cuda.synchronize(self.model.device)
+                g.capture(self)
+            logits = g.replay()
         rows = [i for i, e in enumerate(entries) if e.want]
         if not rows:
-            return None
-        return logits.index_select(0, torch.tensor(rows, device=logits.device))
+            return True, None
+        if len(rows) == S:
+            return True, logits[:S]
+        return True, logits.index_select(0, torch.tensor(rows, device=logits.device))

@@ -1,0 +1,85 @@
+"""Steps that mix prompt portions with decoded tokens run as captured CUDA graphs once their
+padded shape (requests, tokens) has been seen twice.  The same steps through an engine
+without graphs must give the same logits, and both must agree with the plain implementation."""
+import pytest
+import torch
+
+import plain_model
+from conftest import assert_logits_close, random_tokens, read_folder
+
+pytestmark = pytest.mark.gpu
+
+
+def _cores(folder, dtype):
+    from helios_b200.engine.core import EngineCore
+    from helios_b200.engine.model import DecoderModel
+
+    model = DecoderModel.from_folder(folder, dtype=dtype)
+    make = lambda graphs: EngineCore(model, page_size=8, num_pages=120, max_slots=8, max_model_len=400,
+                                     poison_cache=float("nan"), use_cuda_graphs=graphs)
+    return make(True), make(False)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["tiny_llama", "tiny_tiled", "tiny_window"])
+def test_mixed_steps_as_graphs_equal_steps_kernel_by_kernel(model_folders, name, dtype):
+    from helios_b200.engine.batch import StepEntry
+
+    folder = model_folders[name]
+    cfg, weights = read_folder(folder)
+    with_graphs, without = _cores(folder, dtype)
+    V = cfg["vocab_size"]
+    seqs = {r: random_tokens(V, 160, 7 + i) for i, r in enumerate("abcd")}
+    done = {r: 0 for r in seqs}
+    got = {r: [] for r in seqs}          # (position, logits row) from the engine with graphs
+
+    def step(parts):
+        """parts: list of (request, tokens to feed, want the last?)"""
+        entries = []
+        for r, n, want in parts:
+            toks = seqs[r][done[r]:done[r] + n]
+            entries.append(StepEntry(r, toks, [n - 1] if want else []))
+        a = with_graphs.step(entries)
+        b = without.step(entries)
+        wanted = [(r, done[r] + n - 1) for r, n, want in parts if want]
+        if wanted:
+            tol = dict(atol=1e-5, rtol=0) if dtype == "float32" else dict(atol=6e-2, rtol=6e-2)
+            torch.testing.assert_close(a, b, **tol)
+            for row, (r, pos) in enumerate(wanted):
+                got[r].append((pos, a[row].clone()))
+        else:
+            assert a is None and b is None
+        for r, n, _ in parts:
+            done[r] += n
+
+    # the same shapes come back again and again: 3 requests / 15 tokens (no spare token),
+    # 2 requests / 20 tokens (ten spare tokens in the padding request), decode steps between
+    for _ in range(6):
+        step([("a", 5, True), ("b", 1, True), ("c", 9, False)])
+        step([("a", 13, False), ("d", 7, True)])
+        step([("a", 1, True), ("b", 1, False), ("c", 1, True), ("d", 1, True)])
+    captured = [key for key, g in with_graphs._graphs.items() if g.graph is not None]
+    assert any(s != t for s, t in captured), f"no mixed step was captured: {captured}"
+    assert any(s == t for s, t in captured), f"no decode step was captured: {captured}"
+    for r, rows in got.items():
+        want = plain_model.forward_logits(cfg, weights, seqs[r][:done[r]])
+        for pos, row in rows:
+            assert_logits_close(row[None], want[pos:pos + 1], dtype, f"{name} request {r} position {pos}")
+
+
+def test_a_decode_token_without_a_wanted_place_keeps_the_rows_in_order(model_folders):
+    from helios_b200.engine.batch import StepEntry
+
+    folder = model_folders["tiny_llama"]
+    cfg, _ = read_folder(folder)
+    with_graphs, without = _cores(folder, "float32")
+    toks = {r: random_tokens(cfg["vocab_size"], 40, i) for i, r in enumerate("xyz")}
+    for core in (with_graphs, without):
+        core.step([StepEntry(r, t[:20], []) for r, t in toks.items()])
+    for k in range(20, 28):
+        entries = [StepEntry("x", [toks["x"][k]], [0]), StepEntry("y", [toks["y"][k]], []),
+                   StepEntry("z", [toks["z"][k]], [0])]
+        a, b = with_graphs.step(entries), without.step(entries)
+        assert a.shape[0] == 2
+        torch.testing.assert_close(a, b, atol=1e-5, rtol=0)
+    assert any(g.graph is not None for g in with_graphs._graphs.values())
