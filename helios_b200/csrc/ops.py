@@ -340,7 +340,7 @@ _gemm_plans = {}
 
 def gemm_plan(T: int, N: int, K: int, glu: bool):
     """Cached ``_gemm_plan``."""
-    key = (T, N, K, bool(glu), GEMM_CLUSTER_REDUCE)
+    key = (T, N, K, bool(glu), GEMM_CLUSTER_REDUCE, GEMM_TWO_SM)
     plan = _gemm_plans.get(key)
     if plan is None:
         plan = _gemm_plans[key] = _gemm_plan(T, N, K, glu)
@@ -365,6 +365,11 @@ def _gemm_plan(T: int, N: int, K: int, glu: bool):
         tiles = -(-T // 128) * -(-N // (128 if glu else 256))
         cols = 256
         slots = _SM_COUNT
+        if GEMM_TWO_SM:
+            # the two-SM kernel takes whole reductions only; even with part of the pairs idle
+            # it beats the one-SM kernel with a split reduction (20 against 85 microseconds
+            # for 512 tokens x 4096 x 4096)
+            return bn, 1
     splits = 1
     if tiles < slots:
         most_k = max(1, k_blocks // 2)
@@ -446,12 +451,12 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
 
 #: Token counts between the decode kernel's range (up to 128, weights streamed once with
 #: the tokens on the MMA N axis) and the prefill kernel's (pairs of SMs on 256x256 tiles;
-#: on a par with the library from 512 tokens) leave most SMs of the two-SM kernel without a
+#: on a par with the library above 512 tokens) leave most SMs of the two-SM kernel without a
 #: tile.  There plain products (no bias, bfloat16 out) go to the library (cuBLAS through
 #: torch), which the reference uses for every product (python/helios/exec/model.py:170-181).
 #: Fused products (bias, float32 logits, SwiGLU from 384 tokens up) always run on this
 #: package's kernel.  (0, 0) turns the library off.
-GEMM_LIBRARY_TOKEN_RANGE = (129, 511)
+GEMM_LIBRARY_TOKEN_RANGE = (129, 512)
 #: The library chooses its kernel per shape, which takes about a millisecond of host time
 #: the first time a shape is seen; token counts are rounded up to a multiple of this (on a
 #: padded copy of the rows) so that a serving run meets a handful of shapes, not hundreds.

@@ -106,7 +106,7 @@ class _StepGraph:
 class EngineCore:
     #: token counts that mixed steps are padded to when they run as captured graphs; larger
     #: steps keep the device busy longer than the host needs to launch them kernel by kernel
-    GRAPH_TOKEN_BUCKETS = (16, 32, 64, 128, 256, 512)
+    GRAPH_TOKEN_BUCKETS = (16, 32, 64, 128, 192, 256, 384, 512)
 
     def __init__(self, model: DecoderModel, page_size: int, num_pages, max_slots: int,
                  watermark: float = 0.0, max_model_len: Optional[int] = None,
@@ -219,17 +219,18 @@ class EngineCore:
             return False, None
         if any(self.cache.length(e.request_id) + len(e.tokens) > self.graph_max_context for e in entries):
             return False, None
+        num_seqs = 1
+        while num_seqs < S:
+            num_seqs *= 2
         if T == S:
-            num_seqs = 1
-            while num_seqs < S:
-                num_seqs *= 2
             num_tokens = num_seqs
         else:
-            num_seqs = 2                 # at least one padding request takes the spare tokens
-            while num_seqs < S + 1:
-                num_seqs *= 2
+            if token_feed is not None:
+                return False, None
+            if num_seqs == S and T not in self.GRAPH_TOKEN_BUCKETS:
+                num_seqs *= 2            # a padding request has to take the spare tokens
             fits = [b for b in self.GRAPH_TOKEN_BUCKETS if b >= T + (num_seqs - S)]
-            if not fits or fits[0] > self.graph_max_context or token_feed is not None:
+            if not fits or fits[0] > self.graph_max_context:
                 return False, None
             num_tokens = fits[0]
         key = (num_seqs, num_tokens)
