@@ -83,3 +83,50 @@ def test_a_decode_token_without_a_wanted_place_keeps_the_rows_in_order(model_fol
         assert a.shape[0] == 2
         torch.testing.assert_close(a, b, atol=1e-5, rtol=0)
     assert any(g.graph is not None for g in with_graphs._graphs.values())
+
+
+@pytest.mark.parametrize("name", ["tiny_window", "tiny_tiled"])
+def test_generation_with_and_without_graphs_gives_the_same_tokens(model_folders, name):
+    """Requests that arrive at different steps, stop at different lengths and squeeze a
+    small cache (preemptions) through the scheduler: captured steps, launching ahead, both
+    or neither, the tokens are the same (float32: the kernels are deterministic per row)."""
+    import random
+
+    from helios_b200.config import EngineConfig
+    from helios_b200.engine.llm import LLMEngine
+    from helios_b200.engine.types import SamplingParams
+
+    folder = model_folders[name]
+    cfg, _ = read_folder(folder)
+    V = cfg["vocab_size"]
+
+    def run(graphs, ahead):
+        rng = random.Random(5)
+        eng = LLMEngine(EngineConfig(model_dir=str(folder), dtype="float32", block_size=8, num_blocks=36,
+                                     max_num_seqs=6, max_num_batched_tokens=48, run_ahead=ahead,
+                                     use_cuda_graphs=graphs, watermark=0.0))
+        arrivals = []
+        for i in range(16):
+            prompt = [rng.randrange(V) for _ in range(rng.randint(1, 50))]
+            params = SamplingParams(max_tokens=rng.randint(1, 30), temperature=rng.choice([0.0, 0.9]), seed=50 + i)
+            arrivals.append((rng.randint(0, 60), f"r{i}", prompt, params))
+        arrivals.sort(key=lambda a: a[0])
+        done, step = {}, 0
+        while arrivals or eng.scheduler.has_work:
+            while arrivals and arrivals[0][0] <= step:
+                _, rid, prompt, params = arrivals.pop(0)
+                eng.add_request(rid, prompt, params)
+            for out in eng.step():
+                done[out.request_id] = out.token_ids
+            step += 1
+            assert step < 5000
+        captured = [k for k, g in eng.core._graphs.items() if g.graph is not None]
+        return done, captured, eng.scheduler.stats.preemptions
+
+    plain, none, _ = run(False, False)
+    assert none == [] and len(plain) == 16
+    for graphs, ahead in ((True, False), (True, True), (False, True)):
+        got, captured, preemptions = run(graphs, ahead)
+        assert got == plain, f"graphs={graphs} ahead={ahead}"
+        if graphs:
+            assert any(s != t for s, t in captured) and any(s == t for s, t in captured)
