@@ -274,6 +274,13 @@ class Scheduler:
 
     # ------------------------------------------------------------------ admission
     def _admit(self) -> None:
+        if not self.waiting:
+            self._skipped_head_steps = 0
+            return
+        if len(self.running) >= self.config.max_num_seqs or \
+                self.config.max_num_batched_tokens - len(self.running) <= 0:
+            self._skipped_head_steps += 1      # nobody can be admitted: the head is passed once more
+            return
         # preempted requests were put to the front and stay there; the rest in arrival order
         pending = sorted(self.waiting, key=lambda s: (0 if s.state is SeqState.PREEMPTED else 1,
                                                       s.request.arrival_step, s.seq_id))
