@@ -116,6 +116,7 @@ class CompletionOutput:
     text: str = ""
     finish_reason: Optional[FinishReason] = None
     prompt_tokens: int = 0
+    cached_tokens: int = 0        # always 0: there is no prefix cache (python/helios/core/types.py:207)
 
     @property
     def completion_tokens(self) -> int:
