@@ -22,8 +22,8 @@ class FinishReason(Enum):
 
 @dataclass
 class SamplingParams:
-    """Decoding controls with the reference's names and meanings
-    (python/helios/core/types.py:58-85)."""
+    """How a request's tokens are chosen and when it stops.  Names, defaults and limits are
+    the reference's (python/helios/core/types.py:58-85), so that its callers need no change."""
 
     max_tokens: int = 128
     temperature: float = 0.0      # 0 = greedy
@@ -38,14 +38,15 @@ class SamplingParams:
         return self.temperature == 0.0
 
     def validate(self) -> None:
-        if self.max_tokens <= 0:
-            raise ValueError("max_tokens must be positive")
-        if self.temperature < 0.0:
-            raise ValueError("temperature must be >= 0")
-        if not 0.0 < self.top_p <= 1.0:
-            raise ValueError("top_p must be in (0, 1]")
-        if self.top_k < 0:
-            raise ValueError("top_k must be >= 0")
+        limits = (
+            (self.max_tokens > 0, "max_tokens must be positive"),
+            (self.temperature >= 0.0, "temperature must be >= 0"),
+            (0.0 < self.top_p <= 1.0, "top_p must be in (0, 1]"),
+            (self.top_k >= 0, "top_k must be >= 0"),
+        )
+        for ok, message in limits:
+            if not ok:
+                raise ValueError(message)
 
 
 @dataclass
