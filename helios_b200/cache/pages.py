@@ -95,6 +95,8 @@ class RequestPages:
     length: int = 0                                  # tokens written and committed
     tables: List[List[int]] = field(default_factory=list)   # per group: logical page -> id, -1 once given back
     first_held: List[int] = field(default_factory=list)     # per group: first logical page still held
+    version: int = 0                                 # counts the changes of ``tables``
+    arrays: dict = field(default_factory=dict)       # group -> (version, tables[group] as int32 array)
 
 
 class CacheLayout:
@@ -142,6 +144,18 @@ class CacheLayout:
     def table(self, request_id: Hashable, group: int) -> List[int]:
         return self.requests[request_id].tables[group]
 
+    def table_array(self, request_id: Hashable, group: int):
+        """``table`` as an int32 array, rebuilt only when the table has changed (a step's
+        metadata copies every live request's table; with long contexts the conversion
+        from a list every step costs more than the step's kernels)."""
+        import numpy as np
+        req = self.requests[request_id]
+        hit = req.arrays.get(group)
+        if hit is None or hit[0] != req.version:
+            hit = (req.version, np.asarray(req.tables[group], dtype=np.int32))
+            req.arrays[group] = hit
+        return hit[1]
+
     @property
     def num_free_slots(self) -> int:
         return len(self._free_slots)
@@ -176,7 +190,9 @@ class CacheLayout:
                 raise OutOfPages(f"request {request_id!r} needs {n} pages of group {g}, "
                                  f"{self.pools[g].num_free} free")
         for g, n in enumerate(need):
-            req.tables[g].extend(self.pools[g].take(n, request_id))
+            if n:
+                req.tables[g].extend(self.pools[g].take(n, request_id))
+                req.version += 1
 
     def commit(self, request_id: Hashable, n_new: int) -> None:
         """``n_new`` tokens were written.  In a group with a window W the next token, at
@@ -200,6 +216,7 @@ class CacheLayout:
                 req.first_held[g] += 1
             if dead:
                 self.pools[g].give_back(dead, request_id)
+                req.version += 1
 
     def release(self, request_id: Hashable) -> None:
         """The request is over (or preempted): all pages and the slot go back."""

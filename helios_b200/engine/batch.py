@@ -121,7 +121,7 @@ def fill_meta(layout: MetaLayout, host: np.ndarray, entries: Sequence[StepEntry]
         off += n
         cu[i + 1] = off
         for g, t in enumerate(tables):
-            row = cache.table(e.request_id, g)
+            row = cache.table_array(e.request_id, g)
             t[i, :len(row)] = row
     # Padding requests (captured graphs): one token each at position 0; the last of them
     # also takes the tokens that fill the step up to ``layout.T``, at positions 0, 1, ...

@@ -3,6 +3,7 @@ logits at the wanted places out.  Generation, the scheduler and trace replay all
 go through ``EngineCore.step``."""
 from __future__ import annotations
 
+import gc
 from typing import Hashable, List, Optional, Sequence
 
 import torch
@@ -90,8 +91,17 @@ class _StepGraph:
         from ..csrc import ops
         before = ops.launch_count
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            self.logits = core.model.forward(self.ctx, core.cache)
+        # A CUDA graph that the garbage collector frees while this capture runs (an engine
+        # that is no longer used) would invalidate the capture: collect now, not meanwhile.
+        gc.collect()
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph):
+                self.logits = core.model.forward(self.ctx, core.cache)
+        finally:
+            if collecting:
+                gc.enable()
         self.launches = ops.launch_count - before
         ops.launch_count = before
         self.graph = graph

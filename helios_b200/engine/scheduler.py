@@ -391,7 +391,7 @@ class Scheduler:
 
     def _item(self, seq: Sequence, n: int) -> PlanItem:
         start = seq.num_computed_tokens
-        toks = seq.all_token_ids()[start:start + n]
+        toks = seq.token_slice(start, n)
         return PlanItem(seq.seq_id, toks, start, sample=(start + n >= seq.total_tokens),
                         params=seq.request.params, rng_seed=seq.rng_seed,
                         rng_offset=seq.num_output_tokens)

@@ -102,6 +102,17 @@ class Sequence:
     def all_token_ids(self) -> List[int]:
         return self.request.prompt_token_ids + self.output_token_ids
 
+    def token_slice(self, start: int, n: int) -> List[int]:
+        """``all_token_ids()[start:start + n]`` without building the whole list (a decoding
+        request with a long prompt would copy it every step)."""
+        prompt, outputs = self.request.prompt_token_ids, self.output_token_ids
+        split = len(prompt)
+        if start + n <= split:
+            return prompt[start:start + n]
+        if start >= split:
+            return outputs[start - split:start - split + n]
+        return prompt[start:] + outputs[:start + n - split]
+
     def reset_for_recompute(self) -> None:
         """Its cache is gone; the outputs made so far are kept and are run again with
         the prompt (python/helios/core/types.py:181-191)."""

@@ -433,3 +433,14 @@ def test_sequences_are_entities_not_values():
     sa, sb = sched.seqs[a], sched.seqs[b]
     assert sa is not sb and sa != sb and sa == sa
     assert sb not in [sa]
+
+
+def test_token_slice_equals_slicing_the_whole_list():
+    sched, _ = make()
+    sid = sched.add_request(req(7, rid="s"))
+    seq = sched.seqs[sid]
+    seq.output_token_ids.extend([101, 102, 103, 104])
+    whole = seq.all_token_ids()
+    for start in range(0, 12):
+        for n in range(0, 13 - start):
+            assert seq.token_slice(start, n) == whole[start:start + n], (start, n)
