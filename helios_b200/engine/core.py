@@ -92,8 +92,7 @@ class _StepGraph:
         before = ops.launch_count
         graph = torch.cuda.CUDAGraph()
         # A CUDA graph that the garbage collector frees while this capture runs (an engine
-        # that is no longer used) would invalidate the capture: collect now, not meanwhile.
-        gc.collect()
+        # that is no longer used) would invalidate the capture: no collection meanwhile.
         collecting = gc.isenabled()
         gc.disable()
         try:
