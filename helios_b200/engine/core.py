@@ -162,7 +162,8 @@ class EngineCore:
         pages for the new tokens are taken and the new length is committed; a scheduler
         that does this bookkeeping itself passes False.  ``token_feed`` (int32 on the
         device, one per entry) replaces the one token of every entry: token ids that an
-        earlier step left on the device and the host has not seen."""
+        earlier step left on the device and the host has not seen.  The logits may lie in a
+        captured graph's own buffer: they hold until the next step; keep a copy for longer."""
         entries = [e for e in entries]
         if not entries:
             return None
