@@ -56,6 +56,7 @@ class _StepGraph:
             dev = torch.zeros((rows, 2), dtype=torch.int32, device=self.dev.device)
             self._tile_buffers[key] = (host, dev)
             self._fill_tiles(key)
+            self.copied.record()         # the next fill waits for this copy too
         return self._tile_buffers[key][1]
 
     def _fill_tiles(self, key) -> None:
