@@ -136,7 +136,6 @@ class EngineCore:
         self.graph_table_widths = [-(-self.graph_max_context // page_size)] * len(self.cache.groups)
         self._graphs = {}
         self._bucket_seen = {}
-        self.graph_max_tokens = max(self.GRAPH_TOKEN_BUCKETS)
 
     @staticmethod
     def pages_for_bytes(model: DecoderModel, page_size: int, kv_cache_bytes: int) -> int:
