@@ -96,12 +96,22 @@ class _StepGraph:
         # that is no longer used) would invalidate the capture: no collection meanwhile.
         collecting = gc.isenabled()
         gc.disable()
+        # Captured by hand on a side stream: torch's ``cuda.graph`` context first gives all
+        # cached device memory back to the driver, which stalls a serving loop for 0.2 s and
+        # makes the following steps allocate anew.
+        stream = core.capture_stream
+        stream.wait_stream(torch.cuda.current_stream())
         try:
-            with torch.cuda.graph(graph):
-                self.logits = core.model.forward(self.ctx, core.cache)
+            with torch.cuda.stream(stream):
+                graph.capture_begin(pool=core.graph_pool)
+                try:
+                    self.logits = core.model.forward(self.ctx, core.cache)
+                finally:
+                    graph.capture_end()
         finally:
             if collecting:
                 gc.enable()
+        torch.cuda.current_stream().wait_stream(stream)
         self.launches = ops.launch_count - before
         ops.launch_count = before
         self.graph = graph
@@ -131,6 +141,12 @@ class EngineCore:
         # decode steps (one token per request) run as captured CUDA graphs, one per
         # padded batch size; a size is captured the second time it is seen
         self.use_cuda_graphs = bool(use_cuda_graphs) and model.plan.graph_safe
+        # all graphs of the engine draw their intermediate tensors from one pool: they replay
+        # one after the other on one stream, and a step's logits hold until the next step only
+        self.capture_stream = self.graph_pool = None
+        if self.use_cuda_graphs and model.device.type == "cuda":
+            self.capture_stream = torch.cuda.Stream(model.device)
+            self.graph_pool = torch.cuda.graph_pool_handle()
         pool_tokens = max(p.num_pages for p in self.cache.pools) * page_size if self.cache.pools else 0
         self.graph_max_context = min(max_model_len or pool_tokens, pool_tokens) or 1
         self.graph_table_widths = [-(-self.graph_max_context // page_size)] * len(self.cache.groups)

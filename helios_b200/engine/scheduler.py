@@ -234,15 +234,18 @@ class Scheduler:
         """The step after ``prev`` while ``prev`` still runs: every request of ``prev`` gets
         as its one token the token ``prev`` is sampling for it (``PLACEHOLDER`` here; the
         executor feeds it on the device), in the order of ``prev``'s items.  Only when that
-        is certainly the step ``schedule`` would make if no request stops: nothing waits,
+        is certainly the step ``schedule`` would make if no request stops: nothing waits (or
+        nothing that waits could be admitted: all slots are taken),
         ``prev`` sampled for every running request, none of them reaches its length with
         the token in flight, and the places for the new tokens can be had.  Else None, and
         nothing has changed.  A request that does stop on the token in flight is dropped by
         ``complete``; what the step ahead computed for it is ignored."""
-        if self.waiting or prev.is_empty or len(prev.items) != len(self.running):
+        if prev.is_empty or len(prev.items) != len(self.running):
             return None
         if len(prev.items) > self.config.max_num_batched_tokens:
             return None
+        if self.waiting and not self._admission_closed():
+            return None           # a waiting request might join the next step
         seqs = []
         for item in prev.items:
             seq = self.seqs[item.seq_id]
@@ -263,6 +266,8 @@ class Scheduler:
             return None
         self.step_t += 1
         self.stats.steps += 1
+        if self.waiting:
+            self._skipped_head_steps += 1      # as ``_admit`` counts a step without admission
         plan = StepPlan(self.step_t)
         for seq in seqs:
             self.cache.extend(seq.seq_id, 1)
@@ -273,12 +278,17 @@ class Scheduler:
         return plan
 
     # ------------------------------------------------------------------ admission
+    def _admission_closed(self) -> bool:
+        """No waiting request can be admitted whatever its size: every slot is taken, or the
+        running requests use up the token budget."""
+        return len(self.running) >= self.config.max_num_seqs or \
+            self.config.max_num_batched_tokens - len(self.running) <= 0
+
     def _admit(self) -> None:
         if not self.waiting:
             self._skipped_head_steps = 0
             return
-        if len(self.running) >= self.config.max_num_seqs or \
-                self.config.max_num_batched_tokens - len(self.running) <= 0:
+        if self._admission_closed():
             self._skipped_head_steps += 1      # nobody can be admitted: the head is passed once more
             return
         # preempted requests were put to the front and stay there; the rest in arrival order

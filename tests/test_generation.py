@@ -109,11 +109,12 @@ def test_staggered_arrivals_and_seeded_sampling_do_not_depend_on_the_batch(model
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("graphs", [True, False])
-def test_running_ahead_of_the_host_changes_no_token(model_folders, dtype, graphs):
+@pytest.mark.parametrize("slots", [8, 3])
+def test_running_ahead_of_the_host_changes_no_token(model_folders, dtype, graphs, slots):
     """The next decode step is launched with token ids that are still on the device; the
     outputs equal those of an engine that reads every token first.  Requests stop at
     different steps (stop tokens found one step late, lengths known ahead), and one arrives
-    in the middle."""
+    in the middle.  With three slots some requests wait while the others decode ahead."""
     from helios_b200.engine.types import SamplingParams
 
     folder = model_folders["tiny_llama"]
@@ -121,7 +122,7 @@ def test_running_ahead_of_the_host_changes_no_token(model_folders, dtype, graphs
     prompts = [random_tokens(cfg["vocab_size"], n, 40 + n) for n in (7, 33, 64, 18, 5)]
 
     def run(ahead, stops):
-        eng = _engine(folder, dtype=dtype, run_ahead=ahead, use_cuda_graphs=graphs, max_num_seqs=8)
+        eng = _engine(folder, dtype=dtype, run_ahead=ahead, use_cuda_graphs=graphs, max_num_seqs=slots)
         params = [SamplingParams(max_tokens=30 + 9 * i, temperature=0.7 if i % 2 else 0.0, seed=77 + i,
                                  stop_token_ids=stops[i]) for i in range(5)]
         done, steps = {}, 0

@@ -406,6 +406,34 @@ def test_running_ahead_is_used_for_plain_decoding_and_stops_for_arrivals_and_len
     assert sched2.take_finished()[0].output_token_ids == [7, 8]
 
 
+def test_running_ahead_goes_on_while_those_that_wait_cannot_be_admitted():
+    """With every slot taken a waiting request changes nothing about the next step, so the
+    step ahead may be made; once a slot is free it may not."""
+    sched, cache = make(num_pages=64, page=4, budget=32, max_seqs=2)
+    sched.add_request(Request("a", [1, 2, 3], SamplingParams(max_tokens=9, stop_token_ids=[2])))
+    sched.add_request(Request("b", [1, 2, 3, 4], SamplingParams(max_tokens=9, stop_token_ids=[2])))
+    sched.add_request(Request("c", [1, 2], SamplingParams(max_tokens=3, stop_token_ids=[2])))
+    p1 = sched.schedule()
+    assert [i.seq_id for i in p1.items] == [0, 1] and len(sched.waiting) == 1
+    sched.launched(p1)
+    p2 = sched.schedule_ahead(p1)
+    assert p2 is not None and [i.seq_id for i in p2.items] == [0, 1]
+    sched.launched(p2)
+    sched.complete(p1, {0: 40, 1: 2}, p2)         # "b" stops: a slot is free, "c" can come in
+    sched.check_invariants()
+    assert sched.schedule_ahead(p2) is None
+    sched.complete(p2, {0: 41, 1: 99})
+    p3 = sched.schedule()
+    assert sorted(i.seq_id for i in p3.items) == [0, 2]
+    ex = ScriptedExecutor()
+    sched.launched(p3)
+    sched.complete(p3, ex.run(p3))
+    run_all_ahead(sched, ex)
+    out = {s.request.request_id: s.output_token_ids for s in sched.take_finished()}
+    assert out["b"] == [2] and out["a"][:2] == [40, 41] and len(out["c"]) == 3
+    assert all(p.num_free == p.num_pages for p in cache.pools)
+
+
 def test_a_request_that_stops_on_the_token_in_flight_is_dropped_from_the_step_ahead():
     sched, cache = make(num_pages=16, page=4)
     sched.add_request(Request("a", [1, 2, 3], SamplingParams(max_tokens=9, stop_token_ids=[2])))
