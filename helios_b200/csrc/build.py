@@ -34,6 +34,7 @@ LIBRARIES: Dict[str, str] = {
     "attention_generic": "attention_generic.cu",
     "attention_bf16": "attention_bf16.cu",
     "attention_tc": "attention_tc.cu",
+    "attention_pair": "attention_pair.cu",
     "gemm_f32": "gemm_f32.cu",
     "gemm_bf16": "gemm_bf16.cu",
     "gemm_bf16_noalloc": "gemm_bf16_noalloc.cu",

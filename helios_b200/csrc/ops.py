@@ -88,7 +88,7 @@ def preload(dtype: torch.dtype) -> None:
     from .build import build_all
 
     names = ["elementwise", "attention_generic"]
-    names += ["gemm_f32"] if dtype == torch.float32 else ["attention_bf16", "attention_tc", "gemm_bf16"]
+    names += ["gemm_f32"] if dtype == torch.float32 else ["attention_bf16", "attention_tc", "attention_pair", "gemm_bf16"]
     build_all(names)
     for n in names:
         load_library(n)
@@ -558,6 +558,8 @@ TILED_HEAD_DIMS = (32, 64, 96, 128)
 ATTENTION_CLUSTER_MERGE = True
 #: use the tcgen05 attention kernel for batches with prompt portions where its sizes fit
 ATTENTION_TCGEN05 = True
+#: ... with two tiles of query rows per block when a request brings more than one tile of tokens
+ATTENTION_TILE_PAIRS = True
 _SM_COUNT = 148
 
 
@@ -675,9 +677,11 @@ def tc_attention_supported(num_heads: int, num_kv_heads: int, head_dim: int, pag
 def attention_prefill_tc(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                          block_table: torch.Tensor, q_tiles: torch.Tensor, cu_tokens: torch.Tensor,
                          start_pos: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
-                         page_size: int, window: Optional[int], scale: float) -> torch.Tensor:
+                         page_size: int, window: Optional[int], scale: float, pairs: bool = False) -> torch.Tensor:
     """Attention of query tiles over the cache on tcgen05 tensor cores; ``q_tiles`` is int32
-    [tiles, 2] = (request, first local token) for tiles of ``128 // (nh // nkv)`` tokens."""
+    [tiles, 2] = (request, first local token) for tiles of ``128 // (nh // nkv)`` tokens, or
+    with ``pairs`` of twice as many: then a block works on two tiles of query rows at a time
+    (the softmax of one under the products of the other)."""
     _check(qkv, "qkv", torch.bfloat16, 2)
     _check(k_pages, "k_pages", torch.bfloat16, 4)
     _check(v_pages, "v_pages", torch.bfloat16, 4)
@@ -694,13 +698,14 @@ def attention_prefill_tc(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
     T = qkv.shape[0]
     out = torch.empty((T, num_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
     _scratch, _tickets, err = _gemm_workspace(qkv.device)
-    f = _fn("attention_tc", "hb_attention_prefill_tc",
+    f = _fn(*(("attention_pair", "hb_attention_prefill_pair") if pairs else
+              ("attention_tc", "hb_attention_prefill_tc")),
             [c_void_p, c_void_p, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_int, c_void_p,
              c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p])
     _run(f(_p(out), _p(qkv), qkv.shape[1], _p(k_pages), _p(v_pages), k_pages.shape[0], _p(block_table),
            block_table.shape[1], _p(q_tiles), q_tiles.shape[0], _p(cu_tokens), _p(start_pos), num_heads,
            num_kv_heads, head_dim, page_size, int(window or 0), float(scale), _p(err), _stream()),
-         "attention_prefill_tc")
+         "attention_prefill_pair" if pairs else "attention_prefill_tc")
     return out
 
 
@@ -759,10 +764,13 @@ def attention(ctx, qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
                                          scale, splits)
         if (ATTENTION_TCGEN05 and ctx.max_tokens_per_seq >= 16
                 and tc_attention_supported(num_heads, num_kv_heads, head_dim, page_size)):
-            tiles = _step_tiles(ctx, 128 // (num_heads // num_kv_heads), True, qkv.device)
+            tile = 128 // (num_heads // num_kv_heads)
+            # two tiles of query rows per block when some request brings that many tokens
+            pairs = ATTENTION_TILE_PAIRS and ctx.max_tokens_per_seq > tile
+            tiles = _step_tiles(ctx, 2 * tile if pairs else tile, True, qkv.device)
             return attention_prefill_tc(qkv, k_pages, v_pages, block_table, tiles, ctx.cu_tokens,
                                         ctx.start_pos, num_heads, num_kv_heads, head_dim, page_size,
-                                        window, scale)
+                                        window, scale, pairs)
         _heads, subtiles = prefill_tiling(num_heads, num_kv_heads)
         tiles = _step_tiles(ctx, 16 * subtiles, False, qkv.device)
         return attention_prefill_bf16(qkv, k_pages, v_pages, block_table, tiles, ctx.cu_tokens,

@@ -357,6 +357,23 @@ def test_prefill_attention_tcgen05(nh, nkv, hd, page, window):
     torch.testing.assert_close(out.cpu().double(), dense_attention(case, scale, window), atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("nh,nkv,hd,page", [(32, 8, 128, 16), (8, 8, 128, 8), (16, 2, 64, 32), (4, 1, 64, 128),
+                                            (16, 1, 128, 64), (2, 1, 64, 16), (28, 4, 128, 16), (14, 2, 64, 16),
+                                            (5, 1, 128, 32), (6, 2, 64, 8)])
+@pytest.mark.parametrize("window", [None, 100, 300])
+def test_prefill_attention_tcgen05_two_tiles_a_block(nh, nkv, hd, page, window):
+    """The same with two tiles of query rows per block (probabilities kept in tensor memory):
+    requests that fill both tiles, the first only, or part of each."""
+    seqs = CASES + [(0, 300), (190, 70), (1000, 17), (500, 129), (127, 1), (128, 128), (60, 257), (3, 33)]
+    case = make_paged_case(seqs, nh, nkv, hd, page, torch.bfloat16, DEV, seed=nh * hd + page + 1)
+    scale = 1.0 / math.sqrt(hd)
+    tiles = ops().query_tiles([n for _, n in seqs], 2 * (128 // (nh // nkv)), DEV, [a for a, _ in seqs])
+    out = ops().attention_prefill_tc(case.qkv, case.k_pages, case.v_pages, case.table, tiles,
+                                     case.cu_tokens, case.start_pos, nh, nkv, hd, page, window, scale, pairs=True)
+    ops().check_kernel_errors()
+    torch.testing.assert_close(out.cpu().double(), dense_attention(case, scale, window), atol=2e-2, rtol=2e-2)
+
+
 def test_tcgen05_attention_refuses_sizes_it_does_not_take():
     assert ops().tc_attention_supported(28, 4, 128, 16)          # groups of 7: 18 tokens a tile, two rows idle
     assert not ops().tc_attention_supported(32, 8, 96, 16)
