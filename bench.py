@@ -271,6 +271,8 @@ def main():
     ap.add_argument("--points", default="1,64", help="further decode batch sizes")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--prefill-start", type=int, default=0,
+                    help="tokens of the prompt already in the cache when the timed 2,048-token prefill step runs")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-run-ahead", action="store_true",
                     help="end to end: read every step's tokens before the next step is launched")
@@ -325,17 +327,25 @@ def main():
     prefill = None
     if not args.no_prefill:
         times = []
+        start = args.prefill_start
+        if start + PREFILL_TOKENS > args.context:
+            raise SystemExit(f"--prefill-start {start} needs --context >= {start + PREFILL_TOKENS}")
         for i in range(4):
+            # the prompt's first ``start`` tokens go into the cache untimed, in portions
+            for p0 in range(0, start, PREFILL_TOKENS):
+                core.step([StepEntry("p", tokens(min(PREFILL_TOKENS, start - p0)), [])])
             toks = tokens(PREFILL_TOKENS)
             ms = timed(lambda: core.step([StepEntry("p", toks, [PREFILL_TOKENS - 1])]), 1)
             core.end("p")
             if i >= 1:
                 times.append(ms)
         ms = statistics.median(times)
-        flops = step_flops(cfg, args.layers, PREFILL_TOKENS, 0)
+        flops = step_flops(cfg, args.layers, PREFILL_TOKENS, start)
         prefill = {"value": round(PREFILL_TOKENS / ms * 1e3, 1), "tokens": PREFILL_TOKENS,
                    "ms": round(ms, 3),
                    "frac": round(flops / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
+        if start:
+            prefill["start"] = start
 
     # ---------------------------------------------------------------- decode
     def fill(batch, ctx0):

@@ -560,6 +560,7 @@ ATTENTION_CLUSTER_MERGE = True
 ATTENTION_TCGEN05 = True
 #: ... with two tiles of query rows per block when a request brings more than one tile of tokens
 ATTENTION_TILE_PAIRS = True
+ATTENTION_PAIR_MIN_BLOCKS = 120
 _SM_COUNT = 148
 
 
@@ -765,8 +766,10 @@ def attention(ctx, qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
         if (ATTENTION_TCGEN05 and ctx.max_tokens_per_seq >= 16
                 and tc_attention_supported(num_heads, num_kv_heads, head_dim, page_size)):
             tile = 128 // (num_heads // num_kv_heads)
-            # two tiles of query rows per block when some request brings that many tokens
-            pairs = ATTENTION_TILE_PAIRS and ctx.max_tokens_per_seq > tile
+            # two tiles of query rows per block when that still gives most SMs a block: a
+            # block of two tiles takes about 1.5 times as long as a block of one
+            pairs = (ATTENTION_TILE_PAIRS and ctx.max_tokens_per_seq > tile
+                     and -(-ctx.num_tokens // (2 * tile)) * num_kv_heads >= ATTENTION_PAIR_MIN_BLOCKS)
             tiles = _step_tiles(ctx, 2 * tile if pairs else tile, True, qkv.device)
             return attention_prefill_tc(qkv, k_pages, v_pages, block_table, tiles, ctx.cu_tokens,
                                         ctx.start_pos, num_heads, num_kv_heads, head_dim, page_size,
