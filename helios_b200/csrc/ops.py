@@ -560,7 +560,9 @@ ATTENTION_CLUSTER_MERGE = True
 ATTENTION_TCGEN05 = True
 #: ... with two tiles of query rows per block when a request brings more than one tile of tokens
 ATTENTION_TILE_PAIRS = True
-ATTENTION_PAIR_MIN_BLOCKS = 120
+#: ... and the step gives at least this many blocks of two tiles: with fewer, the blocks of one
+#: tile (twice as many, each about 1/1.5 as long) still fit the 148 SMs in one round
+ATTENTION_PAIR_MIN_BLOCKS = 75
 _SM_COUNT = 148
 
 
