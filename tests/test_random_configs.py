@@ -14,9 +14,9 @@ import trace_util as tu
 pytestmark = pytest.mark.gpu
 
 
-def draw_config(seed, scale):
+def draw_config(seed, scale, head_dims=(16, 32, 48, 64, 80, 96, 112, 128, 144, 160, 192, 256)):
     rng = random.Random(seed)
-    head_dim = rng.choice([16, 32, 48, 64, 80, 96, 112, 128, 144, 160, 192, 256])
+    head_dim = rng.choice(list(head_dims))
     kv_heads = rng.choice([1, 2, 3, 4, 5])
     heads = kv_heads * rng.choice([1, 2, 3, 4, 6, 7, 8])
     layers = rng.randint(1, 4 if scale == 1 else 2)
@@ -47,11 +47,29 @@ def draw_config(seed, scale):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("seed,scale", [(s, 1) for s in range(10)] + [(2000 + s, 8) for s in range(4)])
 def test_a_random_configuration_matches_the_plain_implementation(tmp_path, seed, scale, dtype):
+    cfg, rng = draw_config(seed, scale)
+    _compare(tmp_path, cfg, rng, seed, scale, dtype)
+
+
+@pytest.mark.parametrize("seed", range(3000, 3008))
+def test_random_configurations_on_the_tensor_memory_attention_kernels(tmp_path, seed, monkeypatch):
+    """Head sizes 64 and 128 in bfloat16 run their prompt portions on the tcgen05 attention
+    kernels; here also the kernel with two query tiles per block, which otherwise waits for
+    steps of many blocks."""
+    from helios_b200.csrc import ops
+
+    monkeypatch.setattr(ops, "ATTENTION_PAIR_MIN_BLOCKS", 1 if seed % 2 == 0 else 10 ** 6)
+    before = ops.launch_count
+    cfg, rng = draw_config(seed, 1, head_dims=(64, 128))
+    _compare(tmp_path, cfg, rng, seed, 1, "bfloat16", page_sizes=(8, 16, 32))
+    assert ops.launch_count > before
+
+
+def _compare(tmp_path, cfg, rng, seed, scale, dtype, page_sizes=(8, 16, 32)):
     from helios_b200.engine.core import EngineCore
     from helios_b200.engine.model import DecoderModel
     from helios_b200.weights import write_model_folder
 
-    cfg, rng = draw_config(seed, scale)
     folder = write_model_folder(tmp_path / "model", cfg, seed)
     cfg, weights = read_folder(folder)
     lengths = [rng.randint(2, 150 if scale == 1 else 300) for _ in range(6)]
@@ -69,7 +87,7 @@ def test_a_random_configuration_matches_the_plain_implementation(tmp_path, seed,
         else:
             for rid, toks in list(reqs.items())[3:]:
                 tu.portions(tb, rid, toks, [rng.choice([2, 3, 7, 16, 31]) for _ in range(4)])
-        page = rng.choice([8, 16, 32])
+        page = rng.choice(list(page_sizes))
         core = EngineCore(model, page_size=page, num_pages=-(-tb.live_tokens_peak // page), max_slots=4,
                           poison_cache=float("nan"))
         tu.check(tb, tu.run_in_process(core, tb), plain, dtype, f"{cfg} {kind}")
