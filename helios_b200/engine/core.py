@@ -127,6 +127,10 @@ class EngineCore:
     #: token counts that mixed steps are padded to when they run as captured graphs; larger
     #: steps keep the device busy longer than the host needs to launch them kernel by kernel
     GRAPH_TOKEN_BUCKETS = (16, 32, 64, 128, 192, 256, 384, 512)
+    #: ... except steps that fill one of these counts to seven eighths or more: the full
+    #: portions of a long prompt under the usual token budgets, which come many times in a row
+    GRAPH_FULL_TOKEN_BUCKETS = (1024, 2048, 4096, 8192)
+    MAX_FULL_GRAPHS = 8
 
     def __init__(self, model: DecoderModel, page_size: int, num_pages, max_slots: int,
                  watermark: float = 0.0, max_model_len: Optional[int] = None,
@@ -256,6 +260,16 @@ class EngineCore:
             if num_seqs == S and T not in self.GRAPH_TOKEN_BUCKETS:
                 num_seqs *= 2            # a padding request has to take the spare tokens
             fits = [b for b in self.GRAPH_TOKEN_BUCKETS if b >= T + (num_seqs - S)]
+            if not fits:
+                # a full portion: the requests as they are, and one padding request only if
+                # tokens are to spare (such steps come with the same number of requests many
+                # times in a row, so the number is not rounded up)
+                fits = [b for b in self.GRAPH_FULL_TOKEN_BUCKETS if b >= T and 8 * T >= 7 * b]
+                if fits:
+                    num_seqs = S if fits[0] == T else S + 1
+                    if (num_seqs, fits[0]) not in self._graphs and \
+                            sum(t > self.GRAPH_TOKEN_BUCKETS[-1] for _s, t in self._graphs) >= self.MAX_FULL_GRAPHS:
+                        return False, None
             if not fits or fits[0] > self.graph_max_context:
                 return False, None
             num_tokens = fits[0]

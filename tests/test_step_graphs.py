@@ -10,12 +10,12 @@ from conftest import assert_logits_close, random_tokens, read_folder
 pytestmark = pytest.mark.gpu
 
 
-def _cores(folder, dtype):
+def _cores(folder, dtype, pages=120, max_len=400):
     from helios_b200.engine.core import EngineCore
     from helios_b200.engine.model import DecoderModel
 
     model = DecoderModel.from_folder(folder, dtype=dtype)
-    make = lambda graphs: EngineCore(model, page_size=8, num_pages=120, max_slots=8, max_model_len=400,
+    make = lambda graphs: EngineCore(model, page_size=8, num_pages=pages, max_slots=8, max_model_len=max_len,
                                      poison_cache=float("nan"), use_cuda_graphs=graphs)
     return make(True), make(False)
 
@@ -65,6 +65,49 @@ def test_mixed_steps_as_graphs_equal_steps_kernel_by_kernel(model_folders, name,
         want = plain_model.forward_logits(cfg, weights, seqs[r][:done[r]])
         for pos, row in rows:
             assert_logits_close(row[None], want[pos:pos + 1], dtype, f"{name} request {r} position {pos}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_full_portions_of_a_long_prompt_run_as_graphs(model_folders, dtype):
+    """Steps of 1,024 tokens (a full portion alone, or a portion beside decoded tokens that
+    together fill the count) are captured too; a step that fills less than seven eighths of
+    the count is not."""
+    from helios_b200.engine.batch import StepEntry
+
+    folder = model_folders["tiny_window"]
+    cfg, weights = read_folder(folder)
+    with_graphs, without = _cores(folder, dtype, pages=800, max_len=6200)
+    V = cfg["vocab_size"]
+    long = random_tokens(V, 1024 * 5 + 600, 3)
+    short = {r: random_tokens(V, 40, 50 + i) for i, r in enumerate("uv")}
+    for r, toks in short.items():
+        for core in (with_graphs, without):
+            core.step([StepEntry(r, toks[:30], [])])
+    rows = []
+    pos = 0
+    for k in range(5):
+        if k % 2 == 0:
+            entries = [StepEntry("long", long[pos:pos + 1024], [1023])]
+            n = 1024
+        else:       # 1,022 tokens of the prompt beside two decoded tokens
+            entries = [StepEntry("u", short["u"][30 + k // 2:31 + k // 2], [0]),
+                       StepEntry("long", long[pos:pos + 1022], [1021]),
+                       StepEntry("v", short["v"][30 + k // 2:31 + k // 2], [])]
+            n = 1022
+        a, b = with_graphs.step(entries), without.step(entries)
+        tol = dict(atol=1e-5, rtol=0) if dtype == "float32" else dict(atol=6e-2, rtol=6e-2)
+        torch.testing.assert_close(a, b, **tol)
+        rows.append((pos + n - 1, a[0 if k % 2 == 0 else 1].clone()))
+        pos += n
+    a, b = (c.step([StepEntry("long", long[pos:pos + 600], [599])]) for c in (with_graphs, without))
+    torch.testing.assert_close(a, b, **tol)
+    captured = sorted(key for key, g in with_graphs._graphs.items() if g.graph is not None)
+    assert (1, 1024) in captured, captured           # three full portions alone
+    assert (3, 1024) in with_graphs._graphs          # 1,022 + 2 tokens of three requests, seen twice
+    assert not any(t > 1024 or 512 < t < 1024 for _s, t in with_graphs._graphs), sorted(with_graphs._graphs)
+    want = plain_model.forward_logits(cfg, weights, long[:pos])
+    for p, row in rows:
+        assert_logits_close(row[None], want[p:p + 1], dtype, f"position {p}")
 
 
 def test_a_decode_token_without_a_wanted_place_keeps_the_rows_in_order(model_folders):
