@@ -330,16 +330,17 @@ def main():
         start = args.prefill_start
         if start + PREFILL_TOKENS > args.context:
             raise SystemExit(f"--prefill-start {start} needs --context >= {start + PREFILL_TOKENS}")
-        # the first run of the shape goes kernel by kernel, the second on the graph's buffers,
-        # the third captures the graph: the last three of seven are replays
-        for i in range(7):
+        # the first runs of the shape go kernel by kernel, one more on the graph's buffers, the
+        # next captures the graph (EngineCore.FULL_GRAPH_EAGER_RUNS): the last three are replays
+        runs = EngineCore.FULL_GRAPH_EAGER_RUNS + 5
+        for i in range(runs):
             # the prompt's first ``start`` tokens go into the cache untimed, in portions
             for p0 in range(0, start, PREFILL_TOKENS):
                 core.step([StepEntry("p", tokens(min(PREFILL_TOKENS, start - p0)), [])])
             toks = tokens(PREFILL_TOKENS)
             ms = timed(lambda: core.step([StepEntry("p", toks, [PREFILL_TOKENS - 1])]), 1)
             core.end("p")
-            if i >= 4:
+            if i >= runs - 3:
                 times.append(ms)
         ms = statistics.median(times)
         flops = step_flops(cfg, args.layers, PREFILL_TOKENS, start)

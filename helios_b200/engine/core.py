@@ -131,6 +131,7 @@ class EngineCore:
     #: portions of a long prompt under the usual token budgets, which come many times in a row
     GRAPH_FULL_TOKEN_BUCKETS = (1024, 2048, 4096, 8192)
     MAX_FULL_GRAPHS = 8
+    FULL_GRAPH_EAGER_RUNS = 6
 
     def __init__(self, model: DecoderModel, page_size: int, num_pages, max_slots: int,
                  watermark: float = 0.0, max_model_len: Optional[int] = None,
@@ -278,8 +279,12 @@ class EngineCore:
         if g is None:
             seen = self._bucket_seen.get(key, 0)
             self._bucket_seen[key] = seen + 1
-            if seen == 0:
-                return False, None             # first time: run eagerly (also warms everything up)
+            # first time: run eagerly (also warms everything up).  Capturing a step of
+            # thousands of tokens costs as much as it saves in a hundred replays: only a
+            # shape that keeps coming is worth it.
+            eager_runs = 1 if num_tokens <= self.GRAPH_TOKEN_BUCKETS[-1] else self.FULL_GRAPH_EAGER_RUNS
+            if seen < eager_runs:
+                return False, None
             g = self._graphs[key] = _StepGraph(self, num_seqs, num_tokens)
         g.fill(entries, self.cache)
         if token_feed is not None:

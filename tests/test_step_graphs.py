@@ -77,6 +77,7 @@ def test_full_portions_of_a_long_prompt_run_as_graphs(model_folders, dtype):
     folder = model_folders["tiny_window"]
     cfg, weights = read_folder(folder)
     with_graphs, without = _cores(folder, dtype, pages=800, max_len=6200)
+    with_graphs.FULL_GRAPH_EAGER_RUNS = 1        # capture at the third step of a shape, as for small steps
     V = cfg["vocab_size"]
     long = random_tokens(V, 1024 * 5 + 600, 3)
     short = {r: random_tokens(V, 40, 50 + i) for i, r in enumerate("uv")}
