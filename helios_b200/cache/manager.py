@@ -50,6 +50,37 @@ def bytes_per_page(plan: ModelPlan, page_size: int, dtype_bytes: int) -> List[in
             for g, s in enumerate(specs)]
 
 
+def pool_sizes_for_bytes(plan: ModelPlan, page_size: int, dtype_bytes: int, kv_cache_bytes: int,
+                         max_slots: Optional[int] = None,
+                         largest_portion: Optional[int] = None) -> List[int]:
+    """Pages of every cache group that a byte budget pays for
+    (python/helios/engine.py:147-155 has one kind of layer and one number).  The groups
+    that keep every key get the same number of pages each, since a request needs as many
+    in one as in another.  A group with a window W never holds more than W + a portion
+    (+ a page at either end) per request, so with ``max_slots`` and ``largest_portion``
+    given it gets no more than all slots together can use, and the bytes it leaves go
+    to the others."""
+    per_page = bytes_per_page(plan, page_size, dtype_bytes)
+    specs, _ = cache_groups_of(plan)
+    if not specs:
+        return []
+    share = max(8, kv_cache_bytes // max(1, sum(per_page)))
+    sizes: List[Optional[int]] = [None] * len(specs)
+    left = kv_cache_bytes
+    for g, spec in enumerate(specs):
+        if spec.window is not None:
+            sizes[g] = share
+            if max_slots is not None and largest_portion is not None:
+                per_request = -(-(spec.window + largest_portion) // page_size) + 2
+                sizes[g] = max(8, min(share, max_slots * per_request))
+            left -= sizes[g] * per_page[g]
+    full_bytes = sum(per_page[g] for g in range(len(specs)) if sizes[g] is None)
+    for g in range(len(specs)):
+        if sizes[g] is None:
+            sizes[g] = max(8, left // max(1, full_bytes))
+    return [int(n) for n in sizes]
+
+
 class KVCacheManager(CacheLayout):
     """Bookkeeping (``CacheLayout``) plus the tensors."""
 
@@ -86,6 +117,15 @@ class KVCacheManager(CacheLayout):
             if spec is not None and plan.cache_id(entry) == entry:
                 self.states[entry] = torch.zeros((max_slots,) + tuple(spec.shape),
                                                  dtype=spec.dtype, device=self.device)
+        # ... and for the other parts of a block that keep one (a feed-forward, say):
+        # cache id -> {id(part): [slots, *shape]}
+        self.other_states: Dict[int, Dict[int, torch.Tensor]] = {}
+        for entry, run in enumerate(plan.schedule):
+            if plan.cache_id(entry) != entry:
+                continue
+            for part, spec in plan.layers[run.layer].state_specs():
+                self.other_states.setdefault(entry, {})[id(part)] = torch.zeros(
+                    (max_slots,) + tuple(spec.shape), dtype=spec.dtype, device=self.device)
         self._views: Dict[int, LayerCache] = {}
         #: per group, the id of the spare page no request ever gets
         self.pad_pages: List[int] = list(num_pages)
@@ -107,11 +147,18 @@ class KVCacheManager(CacheLayout):
     def layer_state(self, entry: int) -> Optional[torch.Tensor]:
         return self.states.get(self.plan.cache_id(entry))
 
+    def part_states(self, entry: int) -> Dict[int, torch.Tensor]:
+        """id(part) -> state tensor of the parts of schedule entry ``entry`` other than its mixer."""
+        return self.other_states.get(self.plan.cache_id(entry), {})
+
     # ------------------------------------------------------------------ requests
     def admit(self, request_id: Hashable) -> int:
         slot = super().admit(request_id)
         for state in self.states.values():
             state[slot].zero_()
+        for states in self.other_states.values():
+            for state in states.values():
+                state[slot].zero_()
         return slot
 
     def nbytes(self) -> int:

@@ -181,6 +181,22 @@ class CacheLayout:
         need = self.pages_needed(request_id, n_new)
         return all(n + keep_free <= pool.num_free for n, pool in zip(need, self.pools))
 
+    def pages_held(self, request_id: Hashable) -> List[int]:
+        """Pages per group the request holds now (the ones a window has passed are gone)."""
+        req = self.requests[request_id]
+        return [len(t) - first for t, first in zip(req.tables, req.first_held)]
+
+    def tokens_that_fit(self, request_id: Hashable, keep_free: Optional[Sequence[int]] = None) -> int:
+        """How many more tokens the request can take pages for right now, leaving
+        ``keep_free[group]`` pages of every group to others."""
+        req = self.requests[request_id]
+        fit = None
+        for g, (table, pool) in enumerate(zip(req.tables, self.pools)):
+            spare = pool.num_free - (keep_free[g] if keep_free is not None else 0)
+            n = (len(table) + max(0, spare)) * self.page_size - req.length
+            fit = n if fit is None else min(fit, n)
+        return max(0, fit) if fit is not None else 1 << 30
+
     def extend(self, request_id: Hashable, n_new: int) -> None:
         """Take the pages for ``n_new`` more tokens in every group, or none at all."""
         req = self.requests[request_id]

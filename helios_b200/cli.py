@@ -40,69 +40,69 @@ def cmd_generate(args: argparse.Namespace) -> int:
 
 
 def cmd_info(args: argparse.Namespace) -> int:
-    """Sizes of the model and what a cache budget pays for (python/helios/cli.py:182-207)."""
+    """What the model folder holds and what a cache budget pays for, read off the model's
+    plan: any registered architecture gets this report (python/helios/cli.py:182-207 prints
+    the reference's one architecture from its configuration)."""
+    from math import prod
+
+    from .cache.manager import bytes_per_page, cache_groups_of, pool_sizes_for_bytes
     from .config.model_config import read_config_json
     from .config.registry import resolve_architecture
-    from .parts import PagedCacheSpec
+    from .weights.loader import expected_tensors
 
     cfg_json = read_config_json(Path(args.model))
     arch = resolve_architecture(cfg_json)
-    cfg = arch.parse_config(cfg_json)
-    plan = arch.build_plan(cfg)
+    plan = arch.build_plan(arch.parse_config(cfg_json))
+    stored = {n: spec for n, (_p, _l, spec) in expected_tensors(plan).items() if n not in plan.tied}
+    params = sum(prod(spec.shape) for spec in stored.values())
+    print(f"{args.model}: {arch.name}")
+    print(f"  {len(plan.layers)} layers, {len(plan.schedule)} runs a step; vocabulary {plan.vocab_size:,}; "
+          f"{params:,} parameters in {len(stored)} tensors"
+          + (f" ({len(plan.tied)} tied to another)" if plan.tied else ""))
+    kinds = {}
+    for block in plan.layers:
+        key = f"{type(block).__name__}(" + ", ".join(type(p).__name__ for _n, p in block.named_parts()) + ")"
+        kinds[key] = kinds.get(key, 0) + 1
+    for key, n in kinds.items():
+        print(f"  {n} x {key}")
+    if plan.position is not None:
+        print(f"  positions: {type(plan.position).__name__}")
     dtype_bytes = 4 if args.dtype == "float32" else 2
-    per_page = 0
-    groups = {}
-    for entry, run in enumerate(plan.schedule):
-        mixer = plan.layers[run.layer].mixer
-        spec = mixer.cache_spec() if mixer is not None and plan.cache_id(entry) == entry else None
-        if isinstance(spec, PagedCacheSpec):
-            per_page += 2 * args.block_size * spec.num_kv_heads * spec.head_dim * dtype_bytes
-            groups[spec] = groups.get(spec, 0) + 1
+    specs, where = cache_groups_of(plan)
+    per_page = bytes_per_page(plan, args.block_size, dtype_bytes)
     budget = args.kv_mb * 1024 * 1024
-    pages = budget // max(1, per_page)
-    print(f"model: {args.model} ({arch.name})")
-    print(f"  layers={cfg.num_hidden_layers} hidden={cfg.hidden_size} intermediate={cfg.intermediate_size}")
-    print(f"  q_heads={cfg.num_attention_heads} kv_heads={cfg.num_key_value_heads}"
-          f" head_dim={cfg.head_dim} (GQA group={cfg.group_size})")
-    print(f"  vocab={cfg.vocab_size} max_pos={cfg.max_position_embeddings}"
-          f" parameters={cfg.num_parameters():,}")
-    for spec, n in groups.items():
-        kind = "all keys" if spec.window is None else f"window {spec.window}"
-        print(f"  cache group: {n} layers, {spec.num_kv_heads} kv heads x {spec.head_dim}, {kind}")
-    print(f"KV cache ({args.dtype}, block_size={args.block_size}):")
-    print(f"  bytes/block = {per_page:,}")
-    print(f"  budget {args.kv_mb} MiB -> {pages:,} blocks -> {pages * args.block_size:,} tokens of KV")
+    pages = pool_sizes_for_bytes(plan, args.block_size, dtype_bytes, budget, args.max_seqs,
+                                 args.max_batched_tokens)
+    print(f"cache of {args.kv_mb} MiB in {args.dtype}, pages of {args.block_size} tokens, "
+          f"{args.max_seqs} request slots:")
+    for g, spec in enumerate(specs):
+        n_ids = sum(1 for gg, _ in where.values() if gg == g)
+        keeps = "every key" if spec.window is None else f"the last {spec.window} keys"
+        print(f"  group {g}: {n_ids} caches of {spec.num_kv_heads} KV heads x {spec.head_dim}, keeps {keeps}: "
+              f"{per_page[g]:,} bytes a page, {pages[g]:,} pages = {pages[g] * args.block_size:,} tokens")
+    full = [n for n, s in zip(pages, specs) if s.window is None]
+    if full:
+        print(f"  longest context: {min(full) * args.block_size:,} tokens (all requests together)")
+    elif specs:
+        print("  every cache has a window: the pools bound no request's length")
     return 0
 
 
 def cmd_make_toy_model(args: argparse.Namespace) -> int:
-    """A small model folder with random weights (python/helios/cli.py:161-179)."""
+    """A small model folder with random weights of any registered architecture that offers a
+    toy configuration (python/helios/cli.py:161-179)."""
+    from .config.registry import find_architecture
     from .weights import write_model_folder
 
-    arch = {"llama": ("LlamaForCausalLM", "llama"), "qwen2": ("Qwen2ForCausalLM", "qwen2")}[args.arch]
-    cfg = {
-        "architectures": [arch[0]], "model_type": arch[1],
-        "vocab_size": args.vocab_size, "hidden_size": args.hidden_size,
-        "intermediate_size": args.intermediate_size or 2 * args.hidden_size,
-        "num_hidden_layers": args.layers, "num_attention_heads": args.heads,
-        "num_key_value_heads": args.kv_heads, "max_position_embeddings": args.max_pos,
-        "rms_norm_eps": args.rms_eps, "rope_theta": args.rope_theta,
-        "tie_word_embeddings": bool(args.tie), "hidden_act": "silu", "torch_dtype": "float32",
-        "attention_bias": args.arch == "qwen2", "bos_token_id": 1, "eos_token_id": 2,
-    }
-    if args.head_dim:
-        cfg["head_dim"] = args.head_dim
-    if args.rope_scaling:
-        f, lo, hi, orig = args.rope_scaling
-        cfg["rope_scaling"] = {"rope_type": "llama3", "factor": f, "low_freq_factor": lo,
-                               "high_freq_factor": hi, "original_max_position_embeddings": int(orig)}
-    if args.sliding_window:
-        cfg.update(sliding_window=args.sliding_window, use_sliding_window=True,
-                   max_window_layers=args.max_window_layers)
-    path = write_model_folder(args.out, cfg, seed=args.seed)
-    print(f"wrote toy model to {path}")
-    print("  NOTE: random weights -- the output means nothing, but every engine")
-    print("  code path (paging, batching, sampling) is real.")
+    arch = find_architecture(args.arch)
+    if arch.toy_config is None:
+        raise ValueError(f"architecture {arch.name} registers no toy configuration")
+    sizes = {k: getattr(args, k) for k in (
+        "vocab_size", "hidden_size", "intermediate_size", "layers", "heads", "kv_heads", "head_dim",
+        "max_pos", "rope_theta", "rope_scaling", "rms_eps", "sliding_window", "max_window_layers", "tie")}
+    path = write_model_folder(args.out, arch.toy_config(sizes), seed=args.seed)
+    print(f"{arch.name} with random weights (seed {args.seed}) written to {path}")
+    print("  its text is noise; pages, batches, portions and sampling work as with any model")
     return 0
 
 
@@ -135,7 +135,8 @@ def build_parser() -> argparse.ArgumentParser:
 
     p = sub.add_parser("make-toy-model", help="write a small random-weight model")
     p.add_argument("--out", required=True)
-    p.add_argument("--arch", choices=["llama", "qwen2"], default="llama")
+    p.add_argument("--arch", default="llama",
+                   help="a registered architecture, or the start of its name (llama, qwen2)")
     p.add_argument("--vocab-size", type=int, default=259)
     p.add_argument("--hidden-size", type=int, default=64)
     p.add_argument("--intermediate-size", type=int, default=None)
@@ -156,6 +157,8 @@ def build_parser() -> argparse.ArgumentParser:
 
     p = sub.add_parser("info", help="report derived KV capacity for a model")
     add_engine_args(p)
+    p.add_argument("--max-seqs", type=int, default=64)
+    p.add_argument("--max-batched-tokens", type=int, default=2048)
     p.set_defaults(func=cmd_info)
     return ap
 

@@ -154,6 +154,11 @@ class DenseDecoderConfig:
             wins = [window if i >= first else None for i in range(L)]
         else:
             wins = [None] * L
+        if any(w is not None for w in wins) and architecture == "LlamaForCausalLM":
+            # Llama checkpoints have no layers with a window; serving the file with one would
+            # silently run another model than the one it names
+            raise ConfigError("'layer_types' / 'use_sliding_window' ask for sliding-window layers, "
+                              "which LlamaForCausalLM does not have (Qwen2ForCausalLM does)")
 
         eos = cfg.get("eos_token_id")
         if eos is None:

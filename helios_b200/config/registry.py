@@ -9,7 +9,7 @@ the known ones, and a test can register an architecture of its own.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Callable, Dict
+from typing import Any, Callable, Dict, Optional
 
 from .model_config import ConfigError, read_config_json
 
@@ -19,15 +19,20 @@ class Architecture:
     name: str
     parse_config: Callable[[Dict[str, Any]], Any]   # config.json dict -> typed config
     build_plan: Callable[[Any], Any]                # typed config -> parts.ModelPlan
+    # sizes asked for on the command line (``make-toy-model``: vocab_size, hidden_size,
+    # intermediate_size, layers, heads, kv_heads, head_dim, max_pos, rope_theta, rope_scaling,
+    # rms_eps, sliding_window, max_window_layers, tie; None where not given) -> config.json
+    toy_config: Optional[Callable[[Dict[str, Any]], Dict[str, Any]]] = None
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
 
 
-def register_architecture(name: str, parse_config, build_plan, *, replace: bool = False) -> None:
+def register_architecture(name: str, parse_config, build_plan, *, toy_config=None,
+                          replace: bool = False) -> None:
     if name in _ARCHITECTURES and not replace:
         raise ValueError(f"architecture {name!r} is already registered")
-    _ARCHITECTURES[name] = Architecture(name, parse_config, build_plan)
+    _ARCHITECTURES[name] = Architecture(name, parse_config, build_plan, toy_config)
 
 
 def unregister_architecture(name: str) -> None:
@@ -42,6 +47,19 @@ def _builtin() -> None:
 def known_architectures():
     _builtin()
     return sorted(_ARCHITECTURES)
+
+
+def find_architecture(name: str) -> Architecture:
+    """By its registered name, or by a shorter name that only one registered name begins
+    with, whatever the case (``llama`` finds ``LlamaForCausalLM``)."""
+    _builtin()
+    if name in _ARCHITECTURES:
+        return _ARCHITECTURES[name]
+    hits = [a for n, a in sorted(_ARCHITECTURES.items()) if n.lower().startswith(name.lower())]
+    if len(hits) == 1:
+        return hits[0]
+    raise ConfigError(f"architecture {name!r} " + ("is ambiguous" if hits else "is not supported")
+                      + "; known: " + ", ".join(known_architectures()))
 
 
 def resolve_architecture(cfg: Dict[str, Any]) -> Architecture:

@@ -55,10 +55,20 @@ class StepContext:
     decode_only: bool = False
     max_tokens_per_seq: int = 0
     max_context_len: int = 0
-    # left by the position encoding for the mixers
+    # left by the plan's position encoding for the mixers that were given none of their own
     rotary_cos: Optional[torch.Tensor] = None
     rotary_sin: Optional[torch.Tensor] = None
+    # what the parts make once per step (a position encoding's tables under its identity);
+    # emptied when a forward pass begins
+    step_tables: dict = field(default_factory=dict)
+    # per-request state of the parts of the block that runs now: id(part) -> [slots, ...]
+    block_states: dict = field(default_factory=dict)
     extras: dict = field(default_factory=dict)
+
+    def part_state(self, part) -> Optional[torch.Tensor]:
+        """The [slots, *shape] tensor of a part that declared a ``state_spec`` (not the
+        mixer: that one gets its state as an argument); a request's row is its slot."""
+        return self.block_states.get(id(part))
 
 
 def _align4(n: int) -> int:

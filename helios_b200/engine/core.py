@@ -8,7 +8,7 @@ from typing import Hashable, List, Optional, Sequence
 
 import torch
 
-from ..cache.manager import KVCacheManager, bytes_per_page
+from ..cache.manager import KVCacheManager, pool_sizes_for_bytes
 from .batch import MetaLayout, SeqSlice, StepEntry, build_context, context_from_views, fill_meta
 from .model import DecoderModel
 
@@ -140,7 +140,7 @@ class EngineCore:
         self.cache = KVCacheManager(model.plan, page_size, num_pages, max_slots, model.dtype,
                                     model.device, watermark=watermark, poison=poison_cache)
         self.max_model_len = max_model_len
-        self.vocab_size = model.plan.embedding.vocab
+        self.vocab_size = model.plan.vocab_size
         self.steps_run = 0
         self.tokens_run = 0
         # decode steps (one token per request) run as captured CUDA graphs, one per
@@ -152,19 +152,38 @@ class EngineCore:
         if self.use_cuda_graphs and model.device.type == "cuda":
             self.capture_stream = torch.cuda.Stream(model.device)
             self.graph_pool = torch.cuda.graph_pool_handle()
-        pool_tokens = max(p.num_pages for p in self.cache.pools) * page_size if self.cache.pools else 0
+        # the longest context a request can reach: the smallest pool among the groups that
+        # keep every key (a group with a window holds window + portion, whatever the length)
+        pool_tokens = self.context_limit(self.cache.groups, page_size)
+        if pool_tokens is None:
+            pool_tokens = max_model_len or \
+                (max(p.num_pages for p in self.cache.pools) * page_size if self.cache.pools else 0)
         self.graph_max_context = min(max_model_len or pool_tokens, pool_tokens) or 1
         self.graph_table_widths = [-(-self.graph_max_context // page_size)] * len(self.cache.groups)
         self._graphs = {}
         self._bucket_seen = {}
 
     @staticmethod
-    def pages_for_bytes(model: DecoderModel, page_size: int, kv_cache_bytes: int) -> int:
-        """Pages per group a byte budget pays for; every group gets the same number
-        (python/helios/engine.py:147-155)."""
-        per_page = sum(bytes_per_page(model.plan, page_size,
-                                      torch.empty((), dtype=model.dtype).element_size()))
-        return max(8, kv_cache_bytes // max(1, per_page))
+    def context_limit(groups, page_size: int) -> Optional[int]:
+        """Tokens the smallest pool among the groups that keep every key holds; None when
+        every group has a window (then the pools bound no request's length)."""
+        full = [g.num_pages for g in groups if g.window is None]
+        return min(full) * page_size if full else None
+
+    @staticmethod
+    def pages_for_bytes(model: DecoderModel, page_size: int, kv_cache_bytes: int,
+                        max_slots: Optional[int] = None,
+                        largest_portion: Optional[int] = None) -> List[int]:
+        """Pages of every cache group that a byte budget pays for
+        (python/helios/engine.py:147-155 has one kind of layer and one number).  The groups
+        that keep every key get the same number of pages each, since a request needs as many
+        in one as in another.  A group with a window W never holds more than W + a portion
+        (+ a page at either end) per request, so with ``max_slots`` and ``largest_portion``
+        given it gets no more than all slots together can use, and the bytes it leaves go
+        to the others."""
+        elt = torch.empty((), dtype=model.dtype).element_size()
+        return pool_sizes_for_bytes(model.plan, page_size, elt, kv_cache_bytes, max_slots,
+                                    largest_portion)
 
     # ------------------------------------------------------------------ requests
     def begin(self, request_id: Hashable) -> int:

@@ -117,13 +117,23 @@ class LLMEngine:
         self.model = model or DecoderModel.from_folder(config.model_dir, dtype=config.dtype,
                                                        device=config.device)
         mcfg = self.model.config
-        num_pages = config.num_blocks or EngineCore.pages_for_bytes(
-            self.model, config.block_size, config.kv_cache_bytes)
-        max_len = config.max_model_len or getattr(mcfg, "max_position_embeddings", None) \
-            or num_pages * config.block_size
+        from ..cache.manager import cache_groups_of
+        specs, _ = cache_groups_of(self.model.plan)
+        if config.num_blocks:
+            num_pages = [config.num_blocks] * len(specs)
+        else:
+            num_pages = EngineCore.pages_for_bytes(
+                self.model, config.block_size, config.kv_cache_bytes, config.max_num_seqs,
+                config.max_num_batched_tokens)
         # a context longer than the pool is a promise that cannot be kept
-        # (python/helios/engine.py:157-160)
-        max_len = min(max_len, num_pages * config.block_size)
+        # (python/helios/engine.py:157-160); only the groups that keep every key bound it:
+        # where every layer has a window, the window buys any length
+        keeps_all = [n for n, s in zip(num_pages, specs) if s.window is None]
+        pool_tokens = min(keeps_all) * config.block_size if keeps_all else None
+        max_len = config.max_model_len or getattr(mcfg, "max_position_embeddings", None) \
+            or pool_tokens or max(num_pages, default=8) * config.block_size
+        if pool_tokens is not None:
+            max_len = min(max_len, pool_tokens)
         self.max_model_len = max_len
         self.num_blocks = num_pages
         self.core = EngineCore(self.model, config.block_size, num_pages, config.max_num_seqs,

@@ -71,6 +71,7 @@ class DecoderModel:
         """Run the step's tokens through every scheduled layer (writing the cache) and
         return float32 logits [wanted, vocab] (None if nothing is wanted)."""
         plan = self.plan
+        ctx.step_tables = {}
         if plan.position is not None:
             plan.position.prepare(ctx)
         residual = plan.embedding.forward(ctx)
@@ -78,9 +79,10 @@ class DecoderModel:
             residual = plan.position.embed(ctx, residual)
         delta = None
         for entry, run in enumerate(plan.schedule):
+            ctx.block_states = cache.part_states(entry)
             residual, delta = plan.layers[run.layer].forward(
                 ctx, residual, delta, cache.layer_cache(entry), cache.layer_state(entry))
+        ctx.block_states = {}
         if ctx.num_wanted == 0:
             return None
-        rows = plan.final_norm.add_forward(residual, delta, ctx.act_dtype, rows=ctx.want_rows)
-        return plan.head.forward(ctx, rows)
+        return plan.output.forward(ctx, residual, delta)

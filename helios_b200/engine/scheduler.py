@@ -9,12 +9,21 @@ requests give the same steps (scheduler.py:7-20).
 
 What happens when pages run out
 -------------------------------
-* At admission a request needs the pages of all its tokens plus one page to grow
-  in every group, free now; else it waits and a later, smaller request may pass
-  it (scheduler.py:466-489).  After ``reservation_after_steps`` steps of being
-  passed, the head of the queue alone may be admitted (scheduler.py:421-439).
-* A request that could never fit (its tokens plus a page exceed the usable pool)
-  is refused when added, or finished with ``length`` if it grew to that size.
+* Pages are taken portion by portion, when a portion is put into a step, not for
+  the whole prompt at admission (the reference takes them all at admission:
+  scheduler.py:597-627).  What a request will hold at most is its *claim*:
+  ``CacheLayout.peak_pages`` per group, all its pages where every key is kept,
+  window + portion where a window is.  Admission wants the claim plus one page
+  to grow, beside what the running requests still have to take of their claims,
+  free now in every group; else the request waits and a later, smaller one may
+  pass it (scheduler.py:466-489).  After ``reservation_after_steps`` steps of
+  being passed, the head of the queue alone may be admitted (scheduler.py:421-439).
+* ``add_request`` judges by the same claim against the usable pool: what it
+  accepts, an idle scheduler can admit.  A request that could never fit is refused
+  when added, or finished with ``length`` if it grew to that size.
+* A portion is cut to the pages that are free (beyond the page each decoding
+  request needs next); a request that gets none waits a step.  If nobody can take
+  a step, the newest running request is preempted.
 * Before a step, every decoding request must be able to take its next page; if
   not, the newest running request is preempted: its pages are freed, its outputs
   are kept, and it goes to the FRONT of the queue to be run again from its first
@@ -125,6 +134,7 @@ class Scheduler:
         self.step_t = 0
         self._next_seq_id = 0
         self._skipped_head_steps = 0
+        self._decode_need: List[int] = [0] * len(cache.groups)
         self.last_plan: Optional[StepPlan] = None
 
     # ------------------------------------------------------------------ queue
@@ -132,12 +142,25 @@ class Scheduler:
     def has_work(self) -> bool:
         return bool(self.waiting or self.running)
 
+    def _claim(self, total_tokens: int) -> List[int]:
+        """Most pages per group a request of ``total_tokens`` holds at any time."""
+        portion = self.config.max_num_batched_tokens
+        if not self.config.enable_chunked_prefill:
+            portion = max(portion, total_tokens)
+        return [self.cache.peak_pages(g, total_tokens, portion) for g in range(len(self.cache.groups))]
+
     def _fits_ever(self, total_tokens: int) -> bool:
-        budget = self.config.max_num_batched_tokens
-        for g in range(len(self.cache.groups)):
-            if self.cache.peak_pages(g, total_tokens, budget) + 1 > self.cache.usable_pages(g):
-                return False
-        return True
+        return all(c + 1 <= self.cache.usable_pages(g)
+                   for g, c in enumerate(self._claim(total_tokens)))
+
+    def _unclaimed(self, seqs) -> List[int]:
+        """Pages per group that ``seqs`` have yet to take of their claims."""
+        out = [0] * len(self.cache.groups)
+        for seq in seqs:
+            held = self.cache.pages_held(seq.seq_id)
+            for g, c in enumerate(self._claim(seq.total_tokens)):
+                out[g] += max(0, c - held[g])
+        return out
 
     def add_request(self, request: Request, rng_seed: int = 0) -> int:
         """Validate and queue (python/helios/core/scheduler.py:219-276)."""
@@ -316,7 +339,7 @@ class Scheduler:
                 self.waiting.remove(seq)
                 self._retire(seq, FinishReason.LENGTH if seq.num_output_tokens else FinishReason.ABORTED)
                 continue
-            if not self._reserve(seq):
+            if not self._reserve(seq, admitted):
                 continue          # does not fit now; a smaller one behind it may
             seq.state = SeqState.RUNNING
             admitted.append(seq)
@@ -329,33 +352,47 @@ class Scheduler:
             self.waiting.remove(seq)
             self.running.append(seq)
 
-    def _reserve(self, seq: Sequence) -> bool:
-        """A slot, the pages of all its tokens, and one page left to grow in every group."""
+    def _reserve(self, seq: Sequence, admitted: List[Sequence]) -> bool:
+        """A slot, if the request's claim and a page to grow are free in every group beside
+        what the running requests (and those admitted in this step) have yet to take.
+        The pages themselves are taken portion by portion (``_build_plan``)."""
         cache = self.cache
         if cache.num_free_slots == 0:
             return False
+        promised = self._unclaimed(self.running + admitted)
+        for g, c in enumerate(self._claim(seq.total_tokens)):
+            if c + 1 + promised[g] > cache.pools[g].num_free:
+                return False
         cache.admit(seq.seq_id)
-        if not cache.can_extend(seq.seq_id, seq.total_tokens, keep_free=1):
-            cache.release(seq.seq_id)
-            return False
-        cache.extend(seq.seq_id, seq.total_tokens)
         return True
 
     # ------------------------------------------------------------------ progress guarantee
     def _ensure_running_can_progress(self) -> None:
+        """Every decoding request must be able to place its next sampled token, and when
+        nobody decodes, some request must be able to take a portion; else the newest
+        running request gives way (python/helios/core/scheduler.py:682-712).  Leaves in
+        ``_decode_need`` the pages per group that portions must leave to the decoders."""
         guard = 0
+        self._decode_need = [0] * len(self.cache.groups)
         while self.running and guard <= self.config.max_num_seqs + 1:
             guard += 1
             need = [0] * len(self.cache.groups)
+            decoding = False
             for seq in self.running:
                 if seq.num_pending_tokens == 1:
+                    decoding = True
                     # its next sampled token will need a place
                     for g, n in enumerate(self.cache.pages_needed(seq.seq_id, 2)):
                         need[g] += n
             if all(n <= pool.num_free for n, pool in zip(need, self.cache.pools)):
-                return
+                if decoding or any(self.cache.tokens_that_fit(s.seq_id) > 0 for s in self.running):
+                    self._decode_need = need
+                    return
             victim = self._pick_victim()
             if victim is None:
+                if not decoding:
+                    # alone, and not a page to be had for its next portion: it cannot go on
+                    self._finish(self.running[0], FinishReason.LENGTH)
                 return
             self._preempt(victim)
 
@@ -381,8 +418,12 @@ class Scheduler:
         rest of the budget in admission order (python/helios/core/scheduler.py:790-861)."""
         plan = StepPlan(self.step_t)
         budget = self.config.max_num_batched_tokens
-        decoding = [s for s in self.running if s.num_pending_tokens == 1]
-        prefilling = [s for s in self.running if s.num_pending_tokens > 1]
+        # a decoding request holds the place of its one token already (``_accept`` took it);
+        # a request of one token that was just admitted takes it like any portion
+        decoding = [s for s in self.running if s.num_pending_tokens == 1
+                    and not any(self.cache.pages_needed(s.seq_id, 1))]
+        placed = {s.seq_id for s in decoding}
+        prefilling = [s for s in self.running if s.num_pending_tokens >= 1 and s.seq_id not in placed]
         decoding = decoding[:budget]
         prefill_budget = max(0, budget - len(decoding))
         for seq in prefilling:
@@ -393,6 +434,14 @@ class Scheduler:
                 n = seq.num_pending_tokens
                 if n > prefill_budget and (plan.items or decoding):
                     continue
+            # the portion's pages are taken now; it is cut to what is free beyond the page
+            # every decoding request needs next (without chunking: all or nothing)
+            fit = self.cache.tokens_that_fit(seq.seq_id, self._decode_need)
+            if fit < n:
+                if not self.config.enable_chunked_prefill or fit <= 0:
+                    continue
+                n = fit
+            self.cache.extend(seq.seq_id, n)
             plan.items.append(self._item(seq, n))
             prefill_budget -= n
         for seq in decoding:

@@ -1,15 +1,15 @@
-from .base import (Block, FeedForward, LayerCache, Mixer, Norm, PagedCacheSpec, Part,
+from .base import (Block, FeedForward, InputStage, LayerCache, Mixer, Norm, OutputStage, PagedCacheSpec, Part,
                    PositionEncoding, StateSpec, WeightSpec, known_parts, part_class,
                    register_part)
 from .norm import RMSNorm
 from .rotary import RotaryEncoding, rotary_frequencies
 from .attention import GQAAttention
 from .mlp import SwiGLU
-from .embedding import OutputHead, TokenEmbedding
+from .embedding import NormedHead, OutputHead, TokenEmbedding
 from .block import PreNormBlock
 from .plan import ModelPlan, Run
 
-__all__ = ["Block", "FeedForward", "LayerCache", "Mixer", "Norm", "PagedCacheSpec", "Part",
+__all__ = ["Block", "FeedForward", "InputStage", "OutputStage", "NormedHead", "LayerCache", "Mixer", "Norm", "PagedCacheSpec", "Part",
            "PositionEncoding", "StateSpec", "WeightSpec", "known_parts", "part_class",
            "register_part", "RMSNorm", "RotaryEncoding", "rotary_frequencies", "GQAAttention",
            "SwiGLU", "OutputHead", "TokenEmbedding", "PreNormBlock", "ModelPlan", "Run"]

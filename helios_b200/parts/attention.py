@@ -20,7 +20,10 @@ from .base import LayerCache, Mixer, PagedCacheSpec, WeightSpec, register_part
 class GQAAttention(Mixer):
     def __init__(self, width: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  scale: float, qkv_bias: bool, window: Optional[int] = None,
-                 rotary: bool = True) -> None:
+                 rotary: bool = True, position=None) -> None:
+        """``position``: the encoding whose cos/sin tables rotate q and k (its
+        ``tables(ctx)``); None takes the tables the plan's own encoding left on the step
+        context.  ``rotary=False``: no rotation at all."""
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} KV heads")
         if head_dim % 2 or head_dim > 256:
@@ -33,6 +36,7 @@ class GQAAttention(Mixer):
         self.qkv_bias = qkv_bias
         self.window = window
         self.rotary = rotary
+        self.position = position
         self.w_qkv = self.b_qkv = self.w_o = None
 
     # ---------------------------------------------------------------- what it keeps
@@ -66,8 +70,10 @@ class GQAAttention(Mixer):
     def forward(self, ctx, x: torch.Tensor, cache: LayerCache, state=None) -> torch.Tensor:
         qkv = ops.linear(x, self.w_qkv, self.b_qkv)
         table = ctx.block_tables[cache.group]
-        cos = ctx.rotary_cos if self.rotary else None
-        sin = ctx.rotary_sin if self.rotary else None
+        cos = sin = None
+        if self.rotary:
+            cos, sin = self.position.tables(ctx) if self.position is not None else \
+                (ctx.rotary_cos, ctx.rotary_sin)
         ops.rope_kv_write(qkv, cos, sin, ctx.positions, ctx.seq_of_token, table,
                           cache.k_pages, cache.v_pages, self.num_heads, self.num_kv_heads,
                           self.head_dim, cache.page_size, write_cache=cache.write)

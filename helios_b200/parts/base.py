@@ -95,11 +95,44 @@ class Norm(Part):
 
 class PositionEncoding(Part):
     def prepare(self, ctx) -> None:
-        """Called once per step before the layers; may leave tables on ``ctx``."""
+        """Called once per step before the layers for the plan's own encoding; may leave
+        tables on ``ctx`` for the mixers that were given no encoding of their own."""
+
+    def tables(self, ctx):
+        """What a mixer that was handed THIS encoding reads for the step's tokens, made at
+        most once per step and kept in ``ctx.step_tables`` under the encoding's identity: so
+        a model may hold several encodings (another base on every other layer) and each mixer
+        gets its own.  Default: nothing."""
+        return None
 
     def embed(self, ctx, hidden: torch.Tensor) -> torch.Tensor:
         """An additive encoding changes the embedded tokens here; default: nothing."""
         return hidden
+
+
+class InputStage(Part):
+    """Turns the step's token ids into the float32 residual stream [T, width].  The plain
+    one is a table look-up (``TokenEmbedding``); a scale or anything else an architecture
+    does before its first block is a subclass."""
+
+    #: ids must lie in [0, vocab_size)
+    vocab_size: int = 0
+
+    def forward(self, ctx) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class OutputStage(Part):
+    """Turns the residual stream into float32 logits [wanted, vocab] at ``ctx.want_rows``
+    only.  The plain one (``NormedHead``) is a final norm and a projection; a missing norm,
+    a cap on the logits or a bias is a subclass.  It may be made of several parts with
+    tensors: ``named_parts`` gives (checkpoint prefix, part) for each."""
+
+    def named_parts(self) -> List[Tuple[str, Part]]:
+        return []
+
+    def forward(self, ctx, residual: torch.Tensor, delta: Optional[torch.Tensor]) -> torch.Tensor:
+        raise NotImplementedError
 
 
 class Mixer(Part):
@@ -118,6 +151,11 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    def state_spec(self) -> Optional[StateSpec]:
+        """A feed-forward may keep a tensor of fixed size per request too; it then finds it
+        in ``ctx.part_state(self)`` as [slots, *shape]."""
+        return None
+
     def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
@@ -132,6 +170,18 @@ class Block:
     @property
     def mixer(self) -> Optional[Mixer]:
         return None
+
+    def state_specs(self) -> List[Tuple[Part, StateSpec]]:
+        """(part, spec) of every part of the block OTHER than the mixer that keeps a tensor of
+        fixed size per request slot (the mixer's comes to ``forward`` as ``state``).  The cache
+        manager makes one tensor [slots, *shape] per schedule entry and part, zeroed when a slot
+        is handed out; the part finds it in ``ctx.part_state(part)`` while its block runs."""
+        out = []
+        for _prefix, part in self.named_parts():
+            spec = getattr(part, "state_spec", lambda: None)()
+            if spec is not None and part is not self.mixer:
+                out.append((part, spec))
+        return out
 
     def forward(self, ctx, residual: torch.Tensor, delta: Optional[torch.Tensor],
                 cache: Optional[LayerCache], state: Optional[torch.Tensor]):

@@ -6,15 +6,16 @@ from typing import Dict
 import torch
 
 from ..csrc import ops
-from .base import Part, WeightSpec
+from .base import InputStage, Norm, OutputStage, Part, WeightSpec
 
 
-class TokenEmbedding(Part):
+class TokenEmbedding(InputStage):
     """hidden = table[token ids]; no scale and no position term.  The residual stream
     it starts is float32."""
 
     def __init__(self, vocab: int, width: int) -> None:
         self.vocab = vocab
+        self.vocab_size = vocab
         self.width = width
         self.table = None
 
@@ -44,3 +45,27 @@ class OutputHead(Part):
 
     def forward(self, ctx, rows: torch.Tensor) -> torch.Tensor:
         return ops.linear_logits(rows, self.weight)
+
+
+class NormedHead(OutputStage):
+    """The usual end of a decoder: the last pending add and the final norm on the wanted rows
+    only, then the projection to the vocabulary (python/helios/exec/model.py:491-496 norms
+    every row and then selects)."""
+
+    def __init__(self, norm: Norm, head: Part, norm_prefix: str = "model.norm.",
+                 head_prefix: str = "lm_head.") -> None:
+        self.norm = norm
+        self.head = head
+        self.norm_prefix = norm_prefix
+        self.head_prefix = head_prefix
+
+    @property
+    def graph_safe(self) -> bool:
+        return self.norm.graph_safe and self.head.graph_safe
+
+    def named_parts(self):
+        return [(self.norm_prefix, self.norm), (self.head_prefix, self.head)]
+
+    def forward(self, ctx, residual: torch.Tensor, delta) -> torch.Tensor:
+        rows = self.norm.add_forward(residual, delta, ctx.act_dtype, rows=ctx.want_rows)
+        return self.head.forward(ctx, rows)

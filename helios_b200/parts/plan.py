@@ -12,8 +12,8 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Any, Dict, Iterator, List, Optional, Tuple
 
-from .base import Block, Norm, Part, PositionEncoding
-from .embedding import OutputHead, TokenEmbedding
+from .base import Block, InputStage, Norm, OutputStage, Part, PositionEncoding
+from .embedding import NormedHead
 
 
 @dataclass(frozen=True)
@@ -25,14 +25,18 @@ class Run:
 
 @dataclass
 class ModelPlan:
+    """``embedding`` is the input stage (token ids -> residual stream); the output stage
+    (residual stream -> logits at the wanted rows) is ``output``, or, when ``final_norm`` and
+    ``head`` are given instead, the usual ``NormedHead`` made of the two."""
     config: Any
-    embedding: TokenEmbedding
+    embedding: InputStage
     position: Optional[PositionEncoding]
     layers: List[Block]
     layer_prefixes: List[str]
-    final_norm: Norm
-    head: OutputHead
+    final_norm: Optional[Norm] = None
+    head: Optional[Part] = None
     schedule: List[Run] = field(default_factory=list)
+    output: Optional[OutputStage] = None
     embedding_prefix: str = "model.embed_tokens."
     position_prefix: str = "model.position."
     final_norm_prefix: str = "model.norm."
@@ -43,6 +47,11 @@ class ModelPlan:
     benign_suffixes: Tuple[str, ...] = (".rotary_emb.inv_freq", ".attn.bias", ".attn.masked_bias")
 
     def __post_init__(self) -> None:
+        if self.output is None:
+            if self.final_norm is None or self.head is None:
+                raise ValueError("a plan needs an output stage, or a final norm and a head")
+            self.output = NormedHead(self.final_norm, self.head, self.final_norm_prefix,
+                                     self.head_prefix)
         if not self.schedule:
             self.schedule = [Run(i) for i in range(len(self.layers))]
         for i, run in enumerate(self.schedule):
@@ -67,8 +76,13 @@ class ModelPlan:
         for prefix, block in zip(self.layer_prefixes, self.layers):
             for sub, part in block.named_parts():
                 yield prefix + sub, part
-        yield self.final_norm_prefix, self.final_norm
-        yield self.head_prefix, self.head
+        yield from self.output.named_parts()
+
+    @property
+    def vocab_size(self) -> int:
+        """Token ids a step may bring: the configuration's ``vocab_size``, else the input
+        stage's."""
+        return int(getattr(self.config, "vocab_size", 0) or self.embedding.vocab_size)
 
     @property
     def graph_safe(self) -> bool:

@@ -3,7 +3,9 @@ convention, with the ``llama3`` frequency scaling (not in the reference).
 
 Frequencies are computed once on the host in float64.  Each step the part turns
 the batch's positions into a cos/sin table [T, rot/2] (float32, angles taken in
-float64), which every mixer of the step reads.
+float64), kept for the step under the encoding's own identity: a mixer that was
+handed an encoding reads that encoding's table, so layers may rotate by different
+bases.
 """
 from __future__ import annotations
 
@@ -47,10 +49,18 @@ class RotaryEncoding(PositionEncoding):
         self.inv_freq64 = rotary_frequencies(rotary_dim, theta, scaling)
         self._dev: Optional[torch.Tensor] = None
 
+    def tables(self, ctx):
+        """(cos, sin) [T, rot/2] for the step's positions, computed once per step."""
+        hit = ctx.step_tables.get(id(self))
+        if hit is None:
+            if self._dev is None or self._dev.device != ctx.positions.device:
+                self._dev = self.inv_freq64.to(ctx.positions.device)
+            hit = ctx.step_tables[id(self)] = ops.rotary_table(ctx.positions, self._dev)
+        return hit
+
     def prepare(self, ctx) -> None:
-        if self._dev is None or self._dev.device != ctx.positions.device:
-            self._dev = self.inv_freq64.to(ctx.positions.device)
-        ctx.rotary_cos, ctx.rotary_sin = ops.rotary_table(ctx.positions, self._dev)
+        # the plan's own encoding also serves the mixers that were given none
+        ctx.rotary_cos, ctx.rotary_sin = self.tables(ctx)
 
 
 register_part("position_encoding", "rotary", RotaryEncoding)

@@ -63,9 +63,9 @@ TINY_WINDOW = {
     "hidden_act": "silu", "torch_dtype": "float32",
 }
 # Head sizes the tensor-core attention kernels take (32), GQA 6/2, a window on every
-# second layer by an explicit layer_types list, other scaling constants.
+# second layer by an explicit layer_types list, other scaling constants, no bias although Qwen2.
 TINY_TILED = {
-    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
     "vocab_size": 270, "hidden_size": 96, "intermediate_size": 160, "num_hidden_layers": 3,
     "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 32,
     "max_position_embeddings": 2048, "rms_norm_eps": 2e-5, "rope_theta": 10000.0,

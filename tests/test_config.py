@@ -69,6 +69,17 @@ def test_rope_scaling_and_windows():
     assert DenseDecoderConfig.from_hf(raw).layer_windows == (40, None, 40, None)
 
 
+def test_a_llama_configuration_with_a_window_is_refused():
+    for change in ({"sliding_window": 8, "layer_types": ["sliding_attention", "full_attention"]},
+                   {"sliding_window": 8, "use_sliding_window": True, "max_window_layers": 0}):
+        with pytest.raises(ConfigError) as exc:
+            DenseDecoderConfig.from_hf(dict(TINY_LLAMA, **change))
+        assert "LlamaForCausalLM" in str(exc.value)
+    # keys that are present but switch nothing on are fine, as in Qwen2.5's own files
+    DenseDecoderConfig.from_hf(dict(TINY_LLAMA, sliding_window=8, use_sliding_window=False))
+    DenseDecoderConfig.from_hf(dict(TINY_LLAMA, sliding_window=8, layer_types=["full_attention"] * 2))
+
+
 @pytest.mark.parametrize("change, word", [
     ({"vocab_size": None}, "vocab_size"),
     ({"num_key_value_heads": 3}, "num_key_value_heads"),

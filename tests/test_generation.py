@@ -236,25 +236,86 @@ def test_stop_token_and_max_model_len(model_folders):
 
 
 def test_command_line(model_folders, tmp_path):
+    from helios_b200.weights import write_model_folder
+
     folder = model_folders["tiny_llama"]
     cfg, weights = read_folder(folder)
     run = lambda *a: subprocess.run([sys.executable, "-m", "helios_b200.cli", *a], cwd=str(ROOT),
                                     capture_output=True, text=True, timeout=300)
-    out = run("generate", "--model", str(folder), "--prompt-ids", "5,17,3", "8,8", "--max-tokens", "5",
+    # the same weights in a folder without a tokenizer: the ids themselves are printed
+    bare = write_model_folder(tmp_path / "bare", TINY_CONFIGS["tiny_llama"], 11, tokenizer=False)
+    out = run("generate", "--model", str(bare), "--prompt-ids", "5,17,3", "8,8", "--max-tokens", "5",
               "--dtype", "float32", "--kv-mb", "16")
     assert out.returncode == 0, out.stderr
     lines = out.stdout.strip().splitlines()
     assert lines[0] == "--- batch-0 ---" and lines[2] == "[5 tokens, finish=length]"
-    ids = [int(t) for t in lines[1][len("(token ids: ["):-2].split(",")] if lines[1].startswith("(token") else None
-    want = plain_model.greedy_generate(cfg, weights, [5, 17, 3], 5)
-    if ids is not None:
-        assert ids == want
+    assert lines[3] == "--- batch-1 ---"
+    for line, prompt in ((lines[1], [5, 17, 3]), (lines[4], [8, 8])):
+        assert line.startswith("(token ids: [") and line.endswith("])"), line
+        ids = [int(t) for t in line[len("(token ids: ["):-2].split(",")]
+        assert ids == plain_model.greedy_generate(cfg, weights, prompt, 5)
+    # with the byte tokenizer the text form is printed; its bytes are the same tokens
+    text = run("generate", "--model", str(folder), "--prompt-ids", "5,17,3", "--max-tokens", "5",
+               "--dtype", "float32", "--kv-mb", "16")
+    assert text.returncode == 0 and "[5 tokens" in text.stdout
     text = run("generate", "--model", str(folder), "--prompt", "hi", "--max-tokens", "3", "--dtype", "float32",
                "--kv-mb", "16")
     assert text.returncode == 0 and "[3 tokens" in text.stdout
     info = run("info", "--model", str(folder))
-    assert info.returncode == 0 and "bytes/block" in info.stdout and "GQA group=2" in info.stdout
+    assert info.returncode == 0 and "LlamaForCausalLM" in info.stdout
+    assert "2 x PreNormBlock(RMSNorm, GQAAttention, RMSNorm, SwiGLU)" in info.stdout
+    n_params = sum(t.numel() for t in weights.values())
+    assert f"{n_params:,} parameters" in info.stdout and "bytes a page" in info.stdout
     toy = run("make-toy-model", "--out", str(tmp_path / "toy"), "--arch", "qwen2", "--tie", "--layers", "1")
     assert toy.returncode == 0 and (tmp_path / "toy" / "model.safetensors").exists()
+    toy_cfg, toy_w = read_folder(tmp_path / "toy")
+    assert toy_cfg["architectures"] == ["Qwen2ForCausalLM"] and "lm_head.weight" not in toy_w
+    assert "model.layers.0.self_attn.q_proj.bias" in toy_w
     bad = run("generate", "--model", str(tmp_path / "nowhere"), "--prompt-ids", "1")
     assert bad.returncode == 2 and bad.stderr.startswith("error:")
+    bad = run("make-toy-model", "--out", str(tmp_path / "toy2"), "--arch", "mamba")
+    assert bad.returncode == 2 and "known:" in bad.stderr
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_model_whose_every_layer_has_a_window_runs_past_its_pool(tmp_path, dtype):
+    """Every layer sees only the last 24 keys, so the cache holds window + portion whatever
+    the length: a prompt three times the pool is admitted, fed portion by portion (pages
+    taken per portion and given back behind the window), and generates the tokens of a roomy
+    pool; its logits are the plain implementation's."""
+    from conftest import assert_logits_close
+    from helios_b200.engine.batch import StepEntry
+    from helios_b200.engine.types import SamplingParams
+    from helios_b200.weights import write_model_folder
+
+    cfg = dict(TINY_CONFIGS["tiny_window"], sliding_window=24, max_window_layers=0, max_position_embeddings=4096)
+    folder = write_model_folder(tmp_path / "all_window", cfg, 5)
+    _, weights = read_folder(folder)
+    w = bf16_round(weights) if dtype == "bfloat16" else weights
+    page, pages = 8, 12                                   # 96 tokens of cache
+    prompts = [random_tokens(cfg["vocab_size"], n, 70 + n) for n in (300, 41)]
+    tight = _engine(folder, dtype=dtype, num_blocks=pages, block_size=page, max_num_batched_tokens=16,
+                    watermark=0.0, max_num_seqs=2)
+    assert tight.max_model_len == 4096                    # not the pool's 96 tokens
+    got = tight.generate(prompts, SamplingParams(max_tokens=12))
+    assert [o.finish_reason.value for o in got] == ["length", "length"]
+    tight.scheduler.check_invariants()
+    assert all(p.num_used == 0 for p in tight.core.cache.pools)
+    roomy = _engine(folder, dtype=dtype, num_blocks=200, block_size=page, max_num_batched_tokens=16)
+    want = roomy.generate(prompts, SamplingParams(max_tokens=12))
+    if dtype == "float32":
+        assert [o.token_ids for o in got] == [o.token_ids for o in want]
+    for prompt, out in zip(prompts, got):
+        _check_greedy(cfg, w, prompt, out.token_ids, dtype)
+    # the same through the step function: portions of 16, logits wanted at the end of each
+    core = tight.core
+    toks = prompts[0]
+    plain = plain_model.forward_logits(cfg, w, toks)
+    rows, places = [], []
+    for lo in range(0, len(toks), 16):
+        part = toks[lo:lo + 16]
+        rows.append(core.step([StepEntry("again", part, [0, len(part) - 1])]).clone())
+        places += [lo, lo + len(part) - 1]
+        assert max(p.num_used for p in core.cache.pools) <= pages
+    assert_logits_close(torch.cat(rows), plain[places], dtype, "all-window model, portions of 16")
+    core.end("again")

@@ -213,6 +213,108 @@ def test_one_far_key_among_hundreds_and_the_windows_edge(dtype, hd):
                                           else dict(atol=0.3, rtol=3e-2)))
 
 
+def _marker_case(seqs, nh, nkv, hd, page, dtype, far, window, seed):
+    """A paged case whose LAST query row points along e0 and whose key ``far`` of the last
+    request does too (score 900 * scale: it takes all the weight when it is seen); that key's
+    value is 100.  With a window, the pages that lie wholly before the first query's window
+    are taken out of the table (-1, as the cache manager gives them back) and poisoned."""
+    case = make_paged_case(seqs, nh, nkv, hd, page, dtype, DEV, seed=seed)
+    i = len(seqs) - 1
+    q, k, v, a = case.dense[i]
+    mark = torch.zeros(hd)
+    mark[0] = 30.0
+    pg, slot = int(case.table[i, far // page]), far % page
+    case.k_pages[pg, :, slot] = mark.to(dtype)
+    case.v_pages[pg, :, slot] = 100.0
+    k[far] = mark.double()
+    v[far] = 100.0
+    case.qkv[-1, : nh * hd] = mark.repeat(nh).to(dtype)
+    q[-1] = mark.double()
+    if window:
+        for r, (before, _n) in enumerate(seqs):
+            for j in range(max(0, before - window + 1) // page):
+                gone = int(case.table[r, j])
+                case.k_pages[gone] = float("nan")
+                case.v_pages[gone] = float("nan")
+                case.table[r, j] = -1
+    return case
+
+
+MARKER_SIZES = [(8, 2, 64), (7, 1, 64), (4, 1, 128), (14, 2, 128), (6, 2, 32), (6, 6, 96)]
+
+
+def _marker_places(ctx, W, page):
+    """(far key, window, is it seen) for a last query at position ctx - 1."""
+    return [(3, None, True), (ctx - W, W, True), (ctx - W - 1, W, False), (ctx - 1, W, True),
+            (page * 7 - 1, None, True), (page * 7, None, True), (ctx - 1, None, True)]
+
+
+def _check_marker(got, want, seen, what):
+    last = got[-1].float().cpu()
+    if seen:
+        assert (last > 90).all(), f"{what}: the far key was not seen"
+    else:
+        assert (last.abs() < 10).all(), f"{what}: a key outside the window was seen"
+    torch.testing.assert_close(got.cpu().double(), want, atol=0.3, rtol=3e-2)
+
+
+@pytest.mark.parametrize("nh,nkv,hd", MARKER_SIZES)
+@pytest.mark.parametrize("splits,cluster", [(1, True), (3, True), (8, True), (5, False), (13, True)])
+def test_the_decode_kernel_sees_one_far_key_and_the_windows_edge(nh, nkv, hd, splits, cluster, monkeypatch):
+    """Each context slice, the cluster merge and the merge kernel; a second request beside it."""
+    monkeypatch.setattr(ops(), "ATTENTION_CLUSTER_MERGE", cluster)
+    page, ctx, W = 16, 900, 64
+    scale = 1.0 / math.sqrt(hd)
+    for far, window, seen in _marker_places(ctx, W, page):
+        case = _marker_case([(411, 1), (ctx - 1, 1)], nh, nkv, hd, page, torch.bfloat16, far, window, seed=far)
+        got = ops().attention_decode_bf16(case.qkv, case.k_pages, case.v_pages, case.table, case.positions,
+                                          nh, nkv, hd, page, window, scale, splits)
+        _check_marker(got, dense_attention(case, scale, window), seen,
+                      f"decode, {splits} slices, key {far}, window {window}")
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [s for s in MARKER_SIZES if s[2] in (64, 128)])
+@pytest.mark.parametrize("pairs", [False, True])
+@pytest.mark.parametrize("page", [16, 8, 128])
+def test_the_tensor_memory_kernels_see_one_far_key_and_the_windows_edge(nh, nkv, hd, pairs, page):
+    """One and two query tiles a block; portions that end a tile, span tiles, and a page size
+    below and at the key tile."""
+    ctx, W = 900, 64
+    scale = 1.0 / math.sqrt(hd)
+    tile = (2 if pairs else 1) * (128 // (nh // nkv))
+    for n_new in (5, 40, 300):
+        for far, window, seen in _marker_places(ctx, W, page):
+            if far >= ctx - n_new and far != ctx - 1:
+                continue          # the far key must lie in the cache of earlier steps (or be the query's own)
+            seqs = [(100, 33), (ctx - n_new, n_new)]
+            case = _marker_case(seqs, nh, nkv, hd, page, torch.bfloat16, far, window, seed=far + n_new)
+            tiles = ops().query_tiles([n for _, n in seqs], tile, DEV, [a for a, _ in seqs])
+            got = ops().attention_prefill_tc(case.qkv, case.k_pages, case.v_pages, case.table, tiles,
+                                             case.cu_tokens, case.start_pos, nh, nkv, hd, page, window, scale,
+                                             pairs=pairs)
+            ops().check_kernel_errors()
+            _check_marker(got, dense_attention(case, scale, window), seen,
+                          f"tcgen05 pairs={pairs}, portion {n_new}, key {far}, window {window}")
+
+
+@pytest.mark.parametrize("nh,nkv,hd", MARKER_SIZES)
+def test_the_tiled_prefill_kernel_sees_one_far_key_and_the_windows_edge(nh, nkv, hd):
+    page, ctx, W = 16, 900, 64
+    scale = 1.0 / math.sqrt(hd)
+    _, subtiles = ops().prefill_tiling(nh, nkv)
+    for n_new in (5, 40):
+        for far, window, seen in _marker_places(ctx, W, page):
+            if far >= ctx - n_new and far != ctx - 1:
+                continue
+            seqs = [(100, 33), (ctx - n_new, n_new)]
+            case = _marker_case(seqs, nh, nkv, hd, page, torch.bfloat16, far, window, seed=far + n_new)
+            tiles = ops().query_tiles([n for _, n in seqs], 16 * subtiles, DEV)
+            got = ops().attention_prefill_bf16(case.qkv, case.k_pages, case.v_pages, case.table, tiles,
+                                               case.cu_tokens, case.start_pos, nh, nkv, hd, page, window, scale)
+            _check_marker(got, dense_attention(case, scale, window), seen,
+                          f"tiled prefill, portion {n_new}, key {far}, window {window}")
+
+
 def test_attention_does_not_depend_on_the_batch_in_float32():
     """A token's output is bit-equal whether its request is alone, in portions, or beside others."""
     nh, nkv, hd, page = 6, 2, 32, 8

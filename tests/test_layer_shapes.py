@@ -60,3 +60,65 @@ def test_one_layer_of_the_benchmarks_sizes_matches_the_plain_implementation():
         assert_logits_close(got, want8, "bfloat16", f"batch of eight, {back} from the end")
     from helios_b200.csrc import ops
     ops.check_kernel_errors()
+
+
+def test_one_layer_of_the_benchmarks_sizes_in_float32():
+    """The 32-bit path at the real widths: the FMA product's grid at 4096 x 14336, the generic
+    attention kernel at 32 heads of 128; whole, in portions, and eight requests decoding."""
+    from helios_b200.engine.batch import StepEntry
+    from helios_b200.engine.core import EngineCore
+    from helios_b200.engine.model import DecoderModel
+
+    model = DecoderModel.from_config(CONFIG, seed=6, dtype="float32")
+    weights = _export(model.plan)
+    core = EngineCore(model, page_size=16, num_pages=200, max_slots=10)
+    n = 300
+    toks = random_tokens(CONFIG["vocab_size"], n + 2, 78)
+    want = plain_model.forward_logits(CONFIG, weights, toks)
+    places = [0, 1, 127, 128, 129, n - 1]
+    got = core.step([StepEntry("whole", toks[:n], places)])
+    assert_logits_close(got, want[places], "float32", "300 tokens in one step, float32")
+    for i in range(2):
+        got = core.step([StepEntry("whole", [toks[n + i]], [0])])
+        assert_logits_close(got, want[n + i:n + i + 1], "float32", f"decoded token {i}, float32")
+    core.end("whole")
+    core.step([StepEntry("cut", toks[:131], [])])
+    got = core.step([StepEntry("cut", toks[131:n], [0, n - 132])])
+    assert_logits_close(got, want[[131, n - 1]], "float32", "portions of 131 and 169 tokens, float32")
+    core.end("cut")
+    prompts = [random_tokens(CONFIG["vocab_size"], 12 + 5 * i, 200 + i) for i in range(8)]
+    refs = [plain_model.forward_logits(CONFIG, weights, p) for p in prompts]
+    core.step([StepEntry(f"b{i}", p[:-3], []) for i, p in enumerate(prompts)])
+    for back in (3, 2, 1):
+        got = core.step([StepEntry(f"b{i}", [p[-back]], [0]) for i, p in enumerate(prompts)])
+        want8 = torch.stack([r[len(p) - back] for r, p in zip(refs, prompts)])
+        assert_logits_close(got, want8, "float32", f"batch of eight, {back} from the end, float32")
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_a_long_portion_beside_decoded_tokens_at_the_benchmarks_sizes(graphs):
+    """A mixed step at the real widths: 700 tokens of one prompt beside six requests that decode,
+    three times over (with graphs: kernel by kernel, on the graph's buffers, replayed)."""
+    from helios_b200.engine.batch import StepEntry
+    from helios_b200.engine.core import EngineCore
+    from helios_b200.engine.model import DecoderModel
+
+    model = DecoderModel.from_config(CONFIG, seed=5, dtype="bfloat16")
+    weights = _export(model.plan)
+    core = EngineCore(model, page_size=16, num_pages=400, max_slots=10, use_cuda_graphs=graphs)
+    prompts = [random_tokens(CONFIG["vocab_size"], 30 + 21 * i, 300 + i) for i in range(6)]
+    refs = [plain_model.forward_logits(CONFIG, weights, p, dtype=torch.float32) for p in prompts]
+    core.step([StepEntry(f"d{i}", p[:-3], []) for i, p in enumerate(prompts)])
+    for rep in range(3):
+        long = random_tokens(CONFIG["vocab_size"], 800, 400 + rep)
+        ref_long = plain_model.forward_logits(CONFIG, weights, long, dtype=torch.float32)
+        back = 3 - rep
+        got = core.step([StepEntry(f"long{rep}", long[:700], [699])]
+                        + [StepEntry(f"d{i}", [p[-back]], [0]) for i, p in enumerate(prompts)]).clone()
+        want = torch.stack([ref_long[699]] + [r[len(p) - back] for r, p in zip(refs, prompts)])
+        assert_logits_close(got, want, "bfloat16", f"700 tokens beside six decoded, run {rep}")
+        got = core.step([StepEntry(f"long{rep}", long[700:], [99])])
+        assert_logits_close(got, ref_long[799:800], "bfloat16", f"the rest of the long prompt, run {rep}")
+        core.end(f"long{rep}")
+    from helios_b200.csrc import ops
+    ops.check_kernel_errors()

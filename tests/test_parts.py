@@ -450,3 +450,127 @@ def test_a_toy_routed_feed_forward_and_a_learned_position_encoding_are_registere
         assert_logits_close(torch.cat(got_b), plain(model.config, model.plan, b), "float32", "toy routed model, b")
     finally:
         unregister_architecture("ToyRoutedForCausalLM")
+
+
+# ---------------------------------------------------------------------- other stages, two encodings, a feed-forward with state
+def test_a_toy_plan_with_stages_of_its_own_two_rotary_bases_and_a_feed_forward_with_state():
+    """What an architecture may differ in without a change to the engine, all defined here: an
+    input stage that scales the embedded tokens, an output stage without a final norm that caps
+    the logits, attention layers that rotate by two different bases (local and global layers,
+    each handed its own encoding), and a feed-forward that keeps a fixed-size state per request
+    (the number of tokens it has seen, which it scales its output by).  Compared with a plain
+    computation on whole sequences; portions and a batch of two must agree with it."""
+    from helios_b200.config import DenseDecoderConfig, register_architecture, unregister_architecture
+    from helios_b200.engine.batch import StepEntry
+    from helios_b200.engine.core import EngineCore
+    from helios_b200.engine.model import DecoderModel
+    from helios_b200.parts import (FeedForward, ModelPlan, OutputHead, OutputStage, StateSpec, TokenEmbedding,
+                                   part_class)
+
+    CAP, THETAS = 3.0, (10000.0, 37.0)
+
+    class ScaledEmbedding(TokenEmbedding):
+        def forward(self, ctx):
+            return super().forward(ctx) * math.sqrt(self.width)
+
+    class CappedHead(OutputStage):
+        """No final norm: the pending add, then logits = CAP * tanh(x W^T / CAP)."""
+
+        def __init__(self, vocab, width):
+            self.head = OutputHead(vocab, width)
+
+        def named_parts(self):
+            return [("lm_head.", self.head)]
+
+        def forward(self, ctx, residual, delta):
+            rows = ctx.want_rows.long()
+            x = residual.index_select(0, rows) + delta.index_select(0, rows).float()
+            return CAP * torch.tanh(self.head.forward(ctx, x.to(ctx.act_dtype)) / CAP)
+
+    class CountingFeedForward(FeedForward):
+        """SwiGLU whose output is divided by (1 + tokens of the request seen so far / 8)."""
+        graph_safe = False
+
+        def __init__(self, width, inner):
+            self.inner_ffn = part_class("feed_forward", "swiglu")(width, inner)
+
+        def state_spec(self):
+            return StateSpec((1,), torch.float32)
+
+        def weight_specs(self):
+            return self.inner_ffn.weight_specs()
+
+        def bind(self, tensors):
+            self.inner_ffn.bind(tensors)
+
+        def forward(self, ctx, x):
+            y = self.inner_ffn.forward(ctx, x).float()
+            seen = ctx.part_state(self)
+            for seq in ctx.seqs:
+                rows = slice(seq.token_offset, seq.token_offset + seq.num_tokens)
+                count = seen[seq.slot, 0] + torch.arange(seq.num_tokens, device=x.device)
+                y[rows] /= (1 + count / 8)[:, None]
+                seen[seq.slot, 0] += seq.num_tokens
+            return y.to(x.dtype)
+
+    def build(cfg):
+        norm, block = part_class("norm", "rmsnorm"), part_class("block", "pre_norm")
+        attn, rope = part_class("mixer", "gqa_attention"), part_class("position_encoding", "rotary")
+        ropes = [rope(cfg.head_dim, t) for t in THETAS]
+        layers = [block(norm(cfg.hidden_size, cfg.rms_norm_eps),
+                        attn(cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
+                             cfg.attention_scale, False, position=ropes[i % 2]),
+                        norm(cfg.hidden_size, cfg.rms_norm_eps),
+                        CountingFeedForward(cfg.hidden_size, cfg.intermediate_size))
+                  for i in range(cfg.num_hidden_layers)]
+        return ModelPlan(config=cfg, embedding=ScaledEmbedding(cfg.vocab_size, cfg.hidden_size), position=None,
+                         layers=layers, layer_prefixes=[f"model.layers.{i}." for i in range(cfg.num_hidden_layers)],
+                         output=CappedHead(cfg.vocab_size, cfg.hidden_size))
+
+    def plain(cfg, plan, toks):
+        f = lambda t: t.double().cpu()
+        n = len(toks)
+        h = f(plan.embedding.table)[toks] * math.sqrt(cfg.hidden_size)
+        nh, nkv, hd = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        pos = torch.arange(n)
+        for i, block in enumerate(plan.layers):
+            inv = plain_model.rope_inv_freq(hd, THETAS[i % 2], None)
+            x = plain_model.rms_norm(h, f(block.mixer_norm.weight), cfg.rms_norm_eps)
+            q, k, v = (x @ f(block.mixer.w_qkv).T).split([nh * hd, nkv * hd, nkv * hd], dim=-1)
+            q = plain_model.apply_rope(q.reshape(n, nh, hd), pos, inv)
+            k = plain_model.apply_rope(k.reshape(n, nkv, hd), pos, inv)
+            a = plain_model.causal_attention(q, k, v.reshape(n, nkv, hd), cfg.attention_scale, None)
+            h = h + a.reshape(n, nh * hd) @ f(block.mixer.w_o).T
+            x = plain_model.rms_norm(h, f(block.ffn_norm.weight), cfg.rms_norm_eps)
+            gu, inner = f(block.ffn.inner_ffn.w_gate_up), block.ffn.inner_ffn.inner
+            y = plain_model.swiglu(x, gu[:inner], gu[inner:], f(block.ffn.inner_ffn.w_down))
+            h = h + y / (1 + pos.double() / 8)[:, None]
+        return CAP * torch.tanh(h @ f(plan.output.head.weight).T / CAP)
+
+    name = "ToyStagesForCausalLM"
+    register_architecture(name, lambda d: DenseDecoderConfig.from_hf(d, name), build, replace=True)
+    try:
+        cfg_json = dict(TINY_LLAMA, architectures=[name], num_hidden_layers=4, rope_scaling=None)
+        model = DecoderModel.from_config(cfg_json, seed=21, dtype="float32")
+        from helios_b200.weights import expected_tensors
+        assert "model.norm.weight" not in expected_tensors(model.plan)          # no final norm to load
+        core = EngineCore(model, page_size=8, num_pages=32, max_slots=2)
+        assert sorted(core.cache.other_states) == [0, 1, 2, 3]                  # one counter per layer
+        a, b = random_tokens(256, 31, 5), random_tokens(256, 10, 6)
+        want_a, want_b = plain(model.config, model.plan, a), plain(model.config, model.plan, b)
+        whole = core.step([StepEntry("a", a, list(range(31)))]).clone()
+        core.end("a")
+        assert_logits_close(whole, want_a, "float32", "toy stages, whole")
+        # with one base for every layer the logits would differ: the second encoding is used
+        inv0, inv1 = (plain_model.rope_inv_freq(16, t, None) for t in THETAS)
+        assert (inv0 - inv1).abs().max() > 0.1
+        got_a, got_b = [], []
+        for (sa, ea), (sb, eb) in zip([(0, 9), (9, 10), (10, 29), (29, 31)], [(0, 3), (3, 4), (4, 9), (9, 10)]):
+            out = core.step([StepEntry("b", b[sb:eb], list(range(eb - sb))),      # b takes a's old slot: zeroed
+                             StepEntry("a", a[sa:ea], list(range(ea - sa)))])
+            got_b.append(out[: eb - sb].clone())
+            got_a.append(out[eb - sb:].clone())
+        assert_logits_close(torch.cat(got_a), want_a, "float32", "toy stages, a in portions beside b")
+        assert_logits_close(torch.cat(got_b), want_b, "float32", "toy stages, b in portions beside a")
+    finally:
+        unregister_architecture(name)

@@ -38,7 +38,7 @@ def draw_config(seed, scale, head_dims=(16, 32, 48, 64, 80, 96, 112, 128, 144, 1
         cfg["rope_scaling"] = {"rope_type": "llama3", "factor": rng.choice([2.0, 8.0, 32.0]),
                                "low_freq_factor": 1.0, "high_freq_factor": rng.choice([2.0, 4.0]),
                                "original_max_position_embeddings": rng.choice([16, 64, 256])}
-    if rng.random() < 0.5:
+    if rng.random() < 0.5 and qwen:           # a Llama configuration with a window is refused
         cfg["sliding_window"] = rng.randint(3, 90)
         cfg["layer_types"] = [rng.choice(["full_attention", "sliding_attention"]) for _ in range(layers)]
     return cfg, rng

@@ -259,6 +259,109 @@ def test_window_group_lets_long_requests_share_a_small_pool():
     assert all(p.num_free == p.num_pages for p in cache.pools)
 
 
+def make_groups(groups, page, budget, max_seqs=4, max_len=4096):
+    cache = CacheLayout(groups, page, max_slots=max_seqs)
+    sched = Scheduler(SchedulerConfig(max_num_seqs=max_seqs, max_num_batched_tokens=budget,
+                                      max_model_len=max_len), cache)
+    return sched, cache
+
+
+@pytest.mark.parametrize("groups,page,budget,prompt", [
+    ([GroupLayout(8, 10)], 4, 16, 100),                          # every group has a window
+    ([GroupLayout(32, 10)], 16, 16, 159),
+    ([GroupLayout(None, 10), GroupLayout(32, 5)], 16, 16, 100),  # pools of different size
+])
+def test_what_add_request_accepts_is_admitted_and_finishes(groups, page, budget, prompt):
+    # pages are taken portion by portion, so a window pool far smaller than the prompt
+    # serves it; the request never holds more than its claim
+    sched, cache = make_groups(groups, page, budget)
+    sched.add_request(req(prompt, max_tokens=30))
+    ex = ScriptedExecutor()
+    steps = 0
+    while sched.has_work:
+        sched.step(ex)
+        sched.check_invariants()
+        for g, pool in enumerate(cache.pools):
+            assert pool.num_used <= cache.peak_pages(g, prompt + 30, budget) + 1
+        steps += 1
+        assert steps < 200, "accepted, but never admitted or never finished"
+    seq = sched.take_finished()[0]
+    assert seq.output_token_ids == [1000 + k for k in range(30)]
+    assert all(p.num_free == p.num_pages for p in cache.pools)
+    # ... and what cannot fit even alone is refused when it is added
+    too_long = max(g.num_pages for g in groups if g.window is None) * page + 1 \
+        if any(g.window is None for g in groups) else None
+    if too_long is not None:
+        with pytest.raises(ValueError):
+            sched.add_request(req(too_long))
+
+
+def test_pages_are_taken_portion_by_portion():
+    sched, cache = make(num_pages=64, page=4, budget=16)
+    sched.add_request(req(40, max_tokens=2))
+    ex = ScriptedExecutor()
+    used = []
+    while sched.has_work:
+        sched.step(ex)
+        used.append(cache.pools[0].num_used)
+    assert used[:3] == [4, 8, 11]          # 16, 32, 40 tokens and the place of the first new one
+
+
+def test_admission_counts_what_running_requests_have_yet_to_take():
+    # two prompts of 5 pages each in a pool of 10: the second may not come in on the pages
+    # the first has not taken yet
+    sched, cache = make(num_pages=10, page=4, budget=8)
+    sched.add_request(req(20, max_tokens=2, rid="first"))
+    sched.add_request(req(20, max_tokens=2, rid="second"))
+    ex = ScriptedExecutor()
+    sched.step(ex)
+    assert [s.request.request_id for s in sched.running] == ["first"]
+    assert cache.pools[0].num_used == 2
+    run_all(sched, ex)
+    assert sched.stats.preemptions == 0 and len(sched.take_finished()) == 2
+
+
+def test_a_portion_is_cut_to_the_free_pages_and_decoders_keep_their_next_page():
+    # two decoding requests grow into the pages a later prompt was admitted on: its portions
+    # shrink to what is free beyond the decoders' next pages, and nobody loses a token
+    def run(num_pages):
+        sched, cache = make(num_pages=num_pages, page=4, budget=4)
+        sched.add_request(req(3, max_tokens=30, rid="d0"))
+        sched.add_request(req(3, max_tokens=30, rid="d1"))
+        ex = ScriptedExecutor()
+        for _ in range(12):
+            sched.step(ex)
+        sched.add_request(req(10, max_tokens=3, rid="long"))
+        sizes = []
+        while sched.has_work:
+            sched.step(ex)
+            sched.check_invariants()
+            sizes += [i.num_tokens for i in ex.plans[-1].items if i.seq_id == 2 and not i.sample]
+            assert len(ex.plans) < 300
+        out = {s.request.request_id: s.output_token_ids for s in sched.take_finished()}
+        return out, sizes, sched.stats.preemptions
+
+    roomy, sizes0, _ = run(64)
+    tight, sizes1, preempted = run(12)
+    assert tight == roomy and len(tight) == 3
+    assert sizes0 and all(n == 2 for n in sizes0)
+    assert preempted or any(n < 2 for n in sizes1) or len(sizes1) != len(sizes0)
+
+
+def test_preemption_with_a_window_group_gives_the_same_outputs():
+    def outputs(num_pages):
+        sched, _ = make(num_pages=num_pages, page=4, budget=8, window=8)
+        sched.add_request(req(7, max_tokens=14, rid="old"))
+        sched.add_request(req(7, max_tokens=14, rid="new"))
+        run_all(sched, ScriptedExecutor())
+        return {s.request.request_id: s.output_token_ids for s in sched.take_finished()}, \
+            sched.stats.preemptions
+
+    roomy, n0 = outputs(64)
+    tight, n1 = outputs(8)
+    assert n0 == 0 and n1 >= 1 and tight == roomy
+
+
 def test_same_requests_same_steps():
     # python/helios/core/scheduler.py:7-20: no clock, no randomness
     def trace():
