@@ -2,13 +2,20 @@
 """Decode and prefill throughput of helios_b200 on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--model llama8b|qwen7b|qwen0.5b] [--workload decode|mixed]
 
 Default run: the layer sizes of Llama-3.1-8B with random bfloat16 weights, a decode
 batch of 8 at a context of 4,096 tokens; it prints ONE JSON line.  ``value`` is
 decoded tokens a second of the step function alone (device-timed), ``e2e`` the same
 through the Python entry point (host token ids in, sampled ids out), ``prefill`` a
 2,048-token prompt, ``points`` decoding at batch 1 and 64, ``roofline`` the bytes the
-decode step has to read over its time.  Synthetic token ids, uniform from a seed.
+decode step has to read over its time.  ``points`` also carries the other two size sets
+(``--extra-models``): Qwen2.5-7B sizes (decode, prefill, and the mixed workload of 32
+requests with prompts of 128 to 4,096 tokens under a budget of 2,048 tokens a step) and
+Qwen2.5-0.5B sizes (decode at batch 1, 64 and 256 from 512 to 1,024 tokens, prefill).
+``--model`` makes one of them the headline instead; ``--workload mixed`` runs the mixed
+workload through ``LLMEngine`` and reports wall time, tokens a second, the steps by size
+and the pages' high-water mark.  Synthetic token ids, uniform from a seed.
 """
 from __future__ import annotations
 
@@ -24,7 +31,8 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-LLAMA_31_8B = {
+MODELS = {}
+LLAMA_31_8B = MODELS["llama8b"] = {
     "architectures": ["LlamaForCausalLM"], "model_type": "llama", "vocab_size": 128256,
     "hidden_size": 4096, "intermediate_size": 14336, "num_hidden_layers": 32,
     "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128,
@@ -34,7 +42,24 @@ LLAMA_31_8B = {
     "attention_bias": False, "tie_word_embeddings": False, "hidden_act": "silu",
     "torch_dtype": "bfloat16",
 }
-FULL_LAYERS = 32
+QWEN25_7B = MODELS["qwen7b"] = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "vocab_size": 152064,
+    "hidden_size": 3584, "intermediate_size": 18944, "num_hidden_layers": 28,
+    "num_attention_heads": 28, "num_key_value_heads": 4, "head_dim": 128,
+    "max_position_embeddings": 32768, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
+    "attention_bias": True, "tie_word_embeddings": False, "hidden_act": "silu",
+    "sliding_window": 131072, "use_sliding_window": False, "torch_dtype": "bfloat16",
+}
+QWEN25_05B = MODELS["qwen0.5b"] = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "vocab_size": 151936,
+    "hidden_size": 896, "intermediate_size": 4864, "num_hidden_layers": 24,
+    "num_attention_heads": 14, "num_key_value_heads": 2, "head_dim": 64,
+    "max_position_embeddings": 32768, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
+    "attention_bias": True, "tie_word_embeddings": True, "hidden_act": "silu",
+    "sliding_window": 32768, "use_sliding_window": False, "torch_dtype": "bfloat16",
+}
+MODEL_NAMES = {"llama8b": "Llama-3.1-8B sizes", "qwen7b": "Qwen2.5-7B sizes",
+               "qwen0.5b": "Qwen2.5-0.5B sizes"}
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
@@ -123,9 +148,17 @@ def decode_bytes(cfg, layers, batch, ctx, dtype_bytes=2):
     H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
     nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
     w = layers * ((nh + 2 * nkv) * hd * H + nh * hd * H + 3 * H * I) * dtype_bytes
-    w += V * H * dtype_bytes + batch * H * dtype_bytes       # output head, embedding rows
+    w += V * H * dtype_bytes + batch * H * dtype_bytes       # output head (tied or not: read once), embedding rows
     kv = layers * batch * ctx * 2 * nkv * hd * dtype_bytes
     return w + kv
+
+
+def metric_name(args):
+    """The same words in both arms: the dtype is in ``dtype``, not here."""
+    if args.workload == "mixed":
+        return (f"mixed continuous batching tokens/s ({MODEL_NAMES[args.model]}, {args.requests} requests, "
+                f"prompts {args.min_prompt}-{args.max_prompt}, budget {args.budget}, {args.new_tokens} new tokens)")
+    return f"decode tokens/s ({MODEL_NAMES[args.model]}, batch {args.batch}, context {args.context})"
 
 
 def run_reference(args):
@@ -150,9 +183,10 @@ def run_reference(args):
         print(json.dumps({"impl": "reference", "unavailable": "no CUDA device"}))
         return 0
 
-    layers = args.ref_layers
-    cfg = dict(LLAMA_31_8B, num_hidden_layers=layers)
-    folder = os.path.join(args.ref_dir, f"helios_ref_llama8b_L{layers}_s{args.seed}")
+    full_layers = MODELS[args.model]["num_hidden_layers"]
+    layers = args.ref_layers or full_layers
+    cfg = dict(MODELS[args.model], num_hidden_layers=layers)
+    folder = os.path.join(args.ref_dir, f"helios_ref_{args.model}_L{layers}_s{args.seed}")
     t_setup = time.time()
     if not os.path.exists(os.path.join(folder, "model.safetensors")):
         from safetensors.torch import save_file
@@ -164,8 +198,10 @@ def run_reference(args):
         def rnd(*shape):
             return (torch.randn(*shape, generator=gen, device="cuda") * 0.02).half().cpu()
 
-        tensors = {"model.embed_tokens.weight": rnd(V, H), "lm_head.weight": rnd(V, H),
+        tensors = {"model.embed_tokens.weight": rnd(V, H),
                    "model.norm.weight": torch.ones(H, dtype=torch.float16)}
+        if not cfg["tie_word_embeddings"]:
+            tensors["lm_head.weight"] = rnd(V, H)
         for i in range(layers):
             p = f"model.layers.{i}."
             tensors.update({
@@ -175,6 +211,9 @@ def run_reference(args):
                 p + "mlp.down_proj.weight": rnd(H, I),
                 p + "input_layernorm.weight": torch.ones(H, dtype=torch.float16),
                 p + "post_attention_layernorm.weight": torch.ones(H, dtype=torch.float16)})
+            if cfg["attention_bias"]:
+                tensors.update({p + "self_attn.q_proj.bias": rnd(q), p + "self_attn.k_proj.bias": rnd(kv),
+                                p + "self_attn.v_proj.bias": rnd(kv)})
         save_file(tensors, os.path.join(folder, "model.safetensors"))
         del tensors
         with open(os.path.join(folder, "config.json"), "w") as f:
@@ -240,14 +279,16 @@ def run_reference(args):
     running = len(engine.scheduler.running)
     line = {
         "impl": "reference",
-        "metric": "decode tokens/s (Llama-3.1-8B sizes, batch 8, context 4096)",
+        "metric": metric_name(args),
         "value": round(running / ms * 1e3, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
         "warmup": warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "fp16 (the reference's own choice on CUDA)",
         "data": "synthetic token ids (uniform, seeded), random weights N(0, 0.02)",
-        "config": {"model": "Llama-3.1-8B sizes", "layers": layers, "layers_full": FULL_LAYERS,
-                   "hidden": 4096, "heads": 32, "kv_heads": 8, "head_dim": 128, "intermediate": 14336,
-                   "vocab": 128256, "global_batch": args.batch, "live_requests": running,
+        "config": {"model": MODEL_NAMES[args.model], "layers": layers, "layers_full": full_layers,
+                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                   "global_batch": args.batch, "live_requests": running,
                    "seq_len": args.context, "page_size": page, "parallelism": "single GPU",
                    "api": "helios.engine.LLMEngine.step", "setup_s": round(setup_s, 1)},
         "clocks": sampler.summary(t0, t1), "gpu_launches": 0, "prefill": prefill,
@@ -258,17 +299,76 @@ def run_reference(args):
     return 0
 
 
+def mixed_prompts(args, vocab, gen):
+    """BASELINE config 4's workload: prompt lengths uniform in [min, max], ids uniform."""
+    import torch
+    lens = torch.randint(args.min_prompt, args.max_prompt + 1, (args.requests,), generator=gen).tolist()
+    return [torch.randint(0, vocab, (n,), generator=gen).tolist() for n in lens]
+
+
+def run_mixed(engine, prompts, new_tokens, sampling_cls):
+    """All requests at once through ``LLMEngine``; wall time from the first step to the last,
+    the device's busy share of it (CUDA events around every launch), the steps by size and the
+    pages' high-water mark."""
+    import torch
+
+    launch = engine.executor.launch
+    marks, sizes = [], []
+
+    def timed_launch(plan, feed=None):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        handle = launch(plan, feed)
+        b.record()
+        marks.append((a, b))
+        sizes.append(plan.num_tokens)
+        return handle
+
+    engine.executor.launch = timed_launch
+    for i, p in enumerate(prompts):
+        engine.add_request(f"m{i}", p, sampling_cls(max_tokens=new_tokens))
+    high = 0
+    torch.cuda.synchronize()
+    w0 = time.perf_counter()
+    while engine.scheduler.has_work:
+        engine.step()
+        high = max(high, max(pool.num_used for pool in engine.core.cache.pools))
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - w0
+    engine.executor.launch = launch
+    busy = sum(a.elapsed_time(b) for a, b in marks) * 1e-3
+    classes = {"decode_le_64": 0, "le_512": 0, "513_to_1791": 0, "ge_1792": 0}
+    for n in sizes:
+        key = "decode_le_64" if n <= 64 else "le_512" if n <= 512 else "513_to_1791" if n < 1792 else "ge_1792"
+        classes[key] += 1
+    done = engine._completed
+    generated = sum(o.completion_tokens for o in done)
+    prompt_tokens = sum(len(p) for p in prompts)
+    return {"wall_s": round(wall, 3), "tokens": prompt_tokens + generated, "generated": generated,
+            "tokens_per_s": round((prompt_tokens + generated) / wall, 1),
+            "generated_per_s": round(generated / wall, 1), "steps": len(sizes),
+            "device_busy": round(busy / wall, 3), "steps_by_tokens": classes,
+            "pages_high_water": high, "pages": engine.core.cache.pools[0].num_pages,
+            "preemptions": engine.scheduler.stats.preemptions}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="llama8b", choices=sorted(MODELS),
+                    help="the size set of the headline numbers")
+    ap.add_argument("--workload", default="decode", choices=["decode", "mixed"])
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS,
-                    help="fewer layers than the model has (both numbers are reported)")
+    ap.add_argument("--layers", type=int, default=0,
+                    help="fewer layers than the model has (both numbers are reported); 0 = all")
     ap.add_argument("--context", type=int, default=CONTEXT)
     ap.add_argument("--points", default="1,64", help="further decode batch sizes")
+    ap.add_argument("--extra-models", default=None,
+                    help="size sets whose numbers go into ``points`` beside the headline's "
+                         "(default: qwen7b,qwen0.5b for the default headline, none otherwise)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--prefill-start", type=int, default=0,
@@ -278,10 +378,16 @@ def main():
                     help="end to end: read every step's tokens before the next step is launched")
     ap.add_argument("--no-graphs", action="store_true",
                     help="run decode steps kernel by kernel (for profilers) instead of as captured graphs")
-    ap.add_argument("--ref-layers", type=int, default=FULL_LAYERS,
+    ap.add_argument("--ref-layers", type=int, default=0,
                     help="layers of the reference arm's model (its loader builds the model in "
-                         "float32 on the host first)")
+                         "float32 on the host first); 0 = all")
     ap.add_argument("--ref-dir", default="/tmp", help="where the reference arm's model folder is written")
+    # the mixed workload (BASELINE config 4)
+    ap.add_argument("--requests", type=int, default=32)
+    ap.add_argument("--min-prompt", type=int, default=128)
+    ap.add_argument("--max-prompt", type=int, default=4096)
+    ap.add_argument("--budget", type=int, default=2048, help="tokens a step (chunked prefill)")
+    ap.add_argument("--new-tokens", type=int, default=256)
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
@@ -292,78 +398,72 @@ def main():
         args.warmup = 3
 
     import torch
+    from helios_b200.config import EngineConfig
     from helios_b200.csrc import ops
     from helios_b200.engine.batch import StepEntry
     from helios_b200.engine.core import EngineCore
+    from helios_b200.engine.llm import LLMEngine
     from helios_b200.engine.model import DecoderModel
+    from helios_b200.engine.types import SamplingParams
 
     peaks = load_peaks()
-    cfg = dict(LLAMA_31_8B, num_hidden_layers=args.layers)
     torch.cuda.set_device(0)
     dev = torch.device("cuda:0")
-    model = DecoderModel.from_config(cfg, seed=args.seed, dtype="bfloat16", device=dev)
     page = 16
-    point_batches = [int(b) for b in args.points.split(",") if b.strip()]
-    max_batch = max([args.batch] + point_batches)
-    core = EngineCore(model, page_size=page, num_pages=max_batch * (args.context // page) + 64,
-                      max_slots=max_batch, max_model_len=args.context + 1,
-                      use_cuda_graphs=not args.no_graphs)
     gen = torch.Generator().manual_seed(args.seed)
 
-    def tokens(n):
-        return torch.randint(0, cfg["vocab_size"], (n,), generator=gen).tolist()
+    def make_model(name, layers=0):
+        full = MODELS[name]["num_hidden_layers"]
+        cfg = dict(MODELS[name], num_hidden_layers=layers or full)
+        return cfg, full, DecoderModel.from_config(cfg, seed=args.seed, dtype="bfloat16", device=dev)
 
-    def timed(fn, n):
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    def timed_steps(fn, n):
+        """(mean, median) milliseconds of ``n`` calls, each between two CUDA events."""
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(n + 1)]
         torch.cuda.synchronize()
-        start.record()
-        for _ in range(n):
+        marks[0].record()
+        for i in range(n):
             fn()
-        end.record()
+            marks[i + 1].record()
         torch.cuda.synchronize()
-        return start.elapsed_time(end) / n
+        each = [marks[i].elapsed_time(marks[i + 1]) for i in range(n)]
+        return marks[0].elapsed_time(marks[n]) / n, statistics.median(each)
 
-    # ---------------------------------------------------------------- prefill
-    prefill = None
-    if not args.no_prefill:
+    def measure_prefill(core, cfg, start=0):
+        vocab, layers = cfg["vocab_size"], cfg["num_hidden_layers"]
         times = []
-        start = args.prefill_start
-        if start + PREFILL_TOKENS > args.context:
-            raise SystemExit(f"--prefill-start {start} needs --context >= {start + PREFILL_TOKENS}")
         # the first runs of the shape go kernel by kernel, one more on the graph's buffers, the
         # next captures the graph (EngineCore.FULL_GRAPH_EAGER_RUNS): the last three are replays
         runs = EngineCore.FULL_GRAPH_EAGER_RUNS + 5
         for i in range(runs):
             # the prompt's first ``start`` tokens go into the cache untimed, in portions
             for p0 in range(0, start, PREFILL_TOKENS):
-                core.step([StepEntry("p", tokens(min(PREFILL_TOKENS, start - p0)), [])])
-            toks = tokens(PREFILL_TOKENS)
-            ms = timed(lambda: core.step([StepEntry("p", toks, [PREFILL_TOKENS - 1])]), 1)
+                n = min(PREFILL_TOKENS, start - p0)
+                core.step([StepEntry("p", torch.randint(0, vocab, (n,), generator=gen).tolist(), [])])
+            toks = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=gen).tolist()
+            ms, _ = timed_steps(lambda: core.step([StepEntry("p", toks, [PREFILL_TOKENS - 1])]), 1)
             core.end("p")
             if i >= runs - 3:
                 times.append(ms)
         ms = statistics.median(times)
-        flops = step_flops(cfg, args.layers, PREFILL_TOKENS, start)
-        prefill = {"value": round(PREFILL_TOKENS / ms * 1e3, 1), "tokens": PREFILL_TOKENS,
-                   "ms": round(ms, 3),
-                   "frac": round(flops / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
+        flops = step_flops(cfg, layers, PREFILL_TOKENS, start)
+        out = {"value": round(PREFILL_TOKENS / ms * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(ms, 3),
+               "frac": round(flops / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
         if start:
-            prefill["start"] = start
+            out["start"] = start
+        return out
 
-    # ---------------------------------------------------------------- decode
-    def fill(batch, ctx0):
-        """``batch`` requests with ``ctx0`` tokens of real prompt in the cache."""
+    def measure_decode(core, cfg, batch, ctx_end, steps, warmup):
+        """``steps`` decode steps of ``batch`` requests that end at context ``ctx_end``."""
+        vocab = cfg["vocab_size"]
+        ctx0 = ctx_end - steps - warmup
         for b in range(batch):
             left = ctx0
             while left > 0:
                 n = min(left, PREFILL_TOKENS)
-                core.step([StepEntry(f"d{b}", tokens(n), [])])
+                core.step([StepEntry(f"d{b}", torch.randint(0, vocab, (n,), generator=gen).tolist(), [])])
                 left -= n
-
-    def decode_run(batch, steps, warmup):
-        ctx0 = args.context - steps - warmup
-        fill(batch, ctx0)
-        last = tokens(batch)
+        last = torch.randint(0, vocab, (batch,), generator=gen).tolist()
 
         def one():
             core.step([StepEntry(f"d{b}", [last[b]], [0]) for b in range(batch)])
@@ -371,39 +471,94 @@ def main():
         for _ in range(warmup):
             one()
         before = ops.launch_count
-        ms = timed(one, steps)
+        mean, median = timed_steps(one, steps)
         launches = ops.launch_count - before
         for b in range(batch):
             core.end(f"d{b}")
-        return ms, launches, ctx0 + warmup + steps // 2
+        mean_ctx = ctx0 + warmup + steps // 2
+        need = decode_bytes(cfg, cfg["num_hidden_layers"], batch, mean_ctx)
+        return {"ms": mean, "ms_median": median, "launches": launches, "mean_ctx": mean_ctx,
+                "tokens_per_s": batch / mean * 1e3, "gbs": need / (mean * 1e-3) / 1e9}
 
+    def mixed_engine(model, cfg):
+        pool_tokens = sum(min(args.max_prompt, 8192) + args.new_tokens + page for _ in range(args.requests))
+        return LLMEngine(EngineConfig(
+            model_dir="", dtype="bfloat16", block_size=page, max_num_seqs=args.requests,
+            max_num_batched_tokens=args.budget, max_model_len=args.max_prompt + args.new_tokens + 8,
+            num_blocks=pool_tokens // page + 8, watermark=0.0, run_ahead=not args.no_run_ahead), model=model)
+
+    def measure_mixed(model, cfg):
+        """Once to warm up (kernels compiled, shapes seen, graphs captured), once timed, on a
+        fresh engine each (the timed one meets the same shapes with its own graphs: captures
+        are part of what a server pays, so they are inside the wall time)."""
+        g = torch.Generator().manual_seed(args.seed + 1)
+        prompts = mixed_prompts(args, cfg["vocab_size"], g)
+        run_mixed(mixed_engine(model, cfg), prompts[:4], 8, SamplingParams)
+        torch.cuda.empty_cache()
+        return run_mixed(mixed_engine(model, cfg), prompts, args.new_tokens, SamplingParams)
+
+    # ---------------------------------------------------------------- the headline model
+    cfg, full_layers, model = make_model(args.model, args.layers)
+    layers = cfg["num_hidden_layers"]
     sampler = ClockSampler()
     sampler.start()
+    config = {"model": MODEL_NAMES[args.model], "layers": layers, "layers_full": full_layers,
+              "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+              "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+              "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+              "global_batch": args.batch, "seq_len": args.context, "page_size": page,
+              "parallelism": "single GPU", "l2": "inputs (weights + cache) larger than L2",
+              "seed": args.seed, "workload": args.workload}
+
+    if args.workload == "mixed":
+        t0 = time.time()
+        res = measure_mixed(model, cfg)
+        clocks = sampler.summary(t0, time.time())
+        sampler.stop()
+        config.update(global_batch=args.requests, seq_len=args.max_prompt + args.new_tokens)
+        line = {"metric": metric_name(args), "value": res["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1,
+                "steps": res["steps"], "warmup": args.warmup,
+                "ms_per_step": round(res["wall_s"] * 1e3 / max(1, res["steps"]), 4),
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+                "data": "synthetic token ids and prompt lengths (uniform, seeded), random weights N(0, 0.02)",
+                "impl": "ours", "config": config, "clocks": clocks, "gpu_launches": ops.launch_count,
+                "mixed": res,
+                "e2e": {"value": res["tokens_per_s"], "unit": "tokens/s",
+                        "h2d_bytes_per_step": "token ids, positions and block tables of the step",
+                        "d2h_bytes_per_step": "4 per sampled request"}}
+        print(json.dumps(line))
+        return 0
+
+    point_batches = [int(b) for b in args.points.split(",") if b.strip()]
+    max_batch = max([args.batch] + point_batches)
+    core = EngineCore(model, page_size=page, num_pages=max_batch * (args.context // page) + 64,
+                      max_slots=max_batch, max_model_len=args.context + 1,
+                      use_cuda_graphs=not args.no_graphs)
+    prefill = None
+    if not args.no_prefill:
+        if args.prefill_start + PREFILL_TOKENS > args.context:
+            raise SystemExit(f"--prefill-start {args.prefill_start} needs --context >= "
+                             f"{args.prefill_start + PREFILL_TOKENS}")
+        prefill = measure_prefill(core, cfg, args.prefill_start)
+
     t0 = time.time()
-    ms, launches, mean_ctx = decode_run(args.batch, args.steps, args.warmup)
+    head = measure_decode(core, cfg, args.batch, args.context, args.steps, args.warmup)
     t1 = time.time()
     clocks = sampler.summary(t0, t1)
-    value = args.batch / ms * 1e3
-    need = decode_bytes(cfg, args.layers, args.batch, mean_ctx)
-    achieved = need / (ms * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
-                "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
+    roofline = {"bound": "hbm", "achieved": round(head["gbs"], 1), "peak": peaks["hbm_gbs"],
+                "unit": "GB/s", "frac": round(head["gbs"] / peaks["hbm_gbs"], 4),
                 "peak_source": peaks["source"]}
-
     points = {}
     for b in point_batches:
-        pms, _, _ = decode_run(b, max(8, args.steps // 2), args.warmup)
-        points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
+        r = measure_decode(core, cfg, b, args.context, max(8, args.steps // 2), args.warmup)
+        points[f"decode_b{b}"] = round(r["tokens_per_s"], 1)
+        points[f"decode_b{b}_hbm_frac"] = round(r["gbs"] / peaks["hbm_gbs"], 4)
 
     # ---------------------------------------------------------------- end to end
     e2e = None
+    del core
+    torch.cuda.empty_cache()
     if not args.no_e2e:
-        from helios_b200.config import EngineConfig
-        from helios_b200.engine.llm import LLMEngine
-        from helios_b200.engine.types import SamplingParams
-
-        del core
-        torch.cuda.empty_cache()
         engine = LLMEngine(EngineConfig(
             model_dir="", dtype="bfloat16", block_size=page, max_num_seqs=args.batch,
             max_num_batched_tokens=PREFILL_TOKENS, max_model_len=args.context + 8,
@@ -413,43 +568,64 @@ def main():
         # every request must still be decoding when the timed steps end, whenever its
         # prompt was finished
         for b in range(args.batch):
-            engine.add_request(f"e{b}", tokens(ctx0 - 64),
-                               SamplingParams(max_tokens=args.steps + args.warmup + 64))
+            toks = torch.randint(0, cfg["vocab_size"], (ctx0 - 64,), generator=gen).tolist()
+            engine.add_request(f"e{b}", toks, SamplingParams(max_tokens=args.steps + args.warmup + 64))
         while any(s.num_pending_tokens > 1 for s in engine.scheduler.running) or engine.scheduler.waiting:
             engine.step()
         for _ in range(args.warmup):
             engine.step()
         torch.cuda.synchronize()
-        per_step = []
         w0 = time.perf_counter()
         for _ in range(args.steps):
-            s0 = time.perf_counter()
             engine.step()
-            per_step.append(time.perf_counter() - s0)
         torch.cuda.synchronize()
         wall = (time.perf_counter() - w0) / args.steps
-        if os.environ.get("HELIOS_BENCH_DEBUG"):
-            print("e2e per-step ms:", [round(x * 1e3, 2) for x in per_step], file=sys.stderr)
-            print("running:", len(engine.scheduler.running), engine.stats_snapshot(), file=sys.stderr)
         h2d = 4 * (args.batch * 8 + args.batch * (args.context // page + 1)) + args.batch * 28
         e2e = {"value": round(args.batch / wall, 1), "unit": "tokens/s",
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch,
                "steps_launched_ahead": engine.steps_ahead}
+        del engine
     sampler.stop()
+    del model
+    torch.cuda.empty_cache()
+
+    # ---------------------------------------------------------------- the other size sets
+    extra = args.extra_models
+    if extra is None:
+        extra = "qwen7b,qwen0.5b" if (args.model == "llama8b" and args.layers in (0, full_layers)) else ""
+    for name in [n for n in extra.split(",") if n.strip() and n != args.model]:
+        xcfg, _xfull, xmodel = make_model(name)
+        if name == "qwen0.5b":
+            # BASELINE config 5: 512-token prompts grown to 1,024, batch 1 / 64 / 256
+            batches, ctx_end, steps = (1, 64, 256), 1024, 256
+        else:
+            batches, ctx_end, steps = (64,), args.context, max(8, args.steps // 2)
+        xcore = EngineCore(xmodel, page_size=page, num_pages=max(batches) * (ctx_end // page) + 256,
+                           max_slots=max(batches), max_model_len=max(ctx_end, PREFILL_TOKENS) + 1)
+        points[f"{name}_prefill_{PREFILL_TOKENS}"] = measure_prefill(xcore, xcfg)["value"]
+        for b in batches:
+            r = measure_decode(xcore, xcfg, b, ctx_end, steps, args.warmup)
+            points[f"{name}_decode_b{b}"] = round(r["tokens_per_s"], 1)
+            points[f"{name}_decode_b{b}_hbm_frac"] = round(r["gbs"] / peaks["hbm_gbs"], 4)
+        del xcore
+        torch.cuda.empty_cache()
+        if name == "qwen7b":
+            res = measure_mixed(xmodel, xcfg)
+            points["qwen7b_mixed_tokens_per_s"] = res["tokens_per_s"]
+            points["qwen7b_mixed_wall_s"] = res["wall_s"]
+            points["qwen7b_mixed_device_busy"] = res["device_busy"]
+        del xmodel
+        torch.cuda.empty_cache()
 
     line = {
-        "metric": "decode tokens/s (Llama-3.1-8B sizes, bf16, batch 8, context 4096)",
-        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
+        "metric": metric_name(args),
+        "value": round(head["tokens_per_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(head["ms"], 4),
+        "ms_per_step_median": round(head["ms_median"], 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic token ids (uniform, seeded), random weights N(0, 0.02)",
-        "impl": "ours",
-        "config": {"model": "Llama-3.1-8B sizes", "layers": args.layers, "layers_full": FULL_LAYERS,
-                   "hidden": 4096, "heads": 32, "kv_heads": 8, "head_dim": 128,
-                   "intermediate": 14336, "vocab": 128256, "global_batch": args.batch,
-                   "seq_len": args.context, "page_size": page, "parallelism": "single GPU",
-                   "l2": "inputs (weights + cache) larger than L2", "seed": args.seed},
-        "clocks": clocks, "gpu_launches": launches, "prefill": prefill, "roofline": roofline,
+        "impl": "ours", "config": config,
+        "clocks": clocks, "gpu_launches": head["launches"], "prefill": prefill, "roofline": roofline,
         "points": points, "e2e": e2e,
     }
     print(json.dumps(line))

@@ -62,6 +62,16 @@ def test_one_layer_of_the_benchmarks_sizes_matches_the_plain_implementation():
     ops.check_kernel_errors()
 
 
+def _close_f32(got, want, what):
+    """Sums of 4,096 and 14,336 float32 products, and logits that reach 5 where the tiny
+    models' stay near 1: the error is judged against the row's largest |logit|, at 2e-5 of it
+    (which is what the tiny models' absolute 2e-5 amounts to for them)."""
+    got, want = got.detach().double().cpu(), want.double()
+    assert got.shape == want.shape and torch.isfinite(got).all(), what
+    rel = ((got - want).abs() / want.abs().amax(dim=-1, keepdim=True)).max().item()
+    assert rel <= 2e-5, f"{what}: max |err| / max |logit| = {rel:.3e} > 2e-5"
+
+
 def test_one_layer_of_the_benchmarks_sizes_in_float32():
     """The 32-bit path at the real widths: the FMA product's grid at 4096 x 14336, the generic
     attention kernel at 32 heads of 128; whole, in portions, and eight requests decoding."""
@@ -77,14 +87,14 @@ def test_one_layer_of_the_benchmarks_sizes_in_float32():
     want = plain_model.forward_logits(CONFIG, weights, toks)
     places = [0, 1, 127, 128, 129, n - 1]
     got = core.step([StepEntry("whole", toks[:n], places)])
-    assert_logits_close(got, want[places], "float32", "300 tokens in one step, float32")
+    _close_f32(got, want[places], "300 tokens in one step, float32")
     for i in range(2):
         got = core.step([StepEntry("whole", [toks[n + i]], [0])])
-        assert_logits_close(got, want[n + i:n + i + 1], "float32", f"decoded token {i}, float32")
+        _close_f32(got, want[n + i:n + i + 1], f"decoded token {i}, float32")
     core.end("whole")
     core.step([StepEntry("cut", toks[:131], [])])
     got = core.step([StepEntry("cut", toks[131:n], [0, n - 132])])
-    assert_logits_close(got, want[[131, n - 1]], "float32", "portions of 131 and 169 tokens, float32")
+    _close_f32(got, want[[131, n - 1]], "portions of 131 and 169 tokens, float32")
     core.end("cut")
     prompts = [random_tokens(CONFIG["vocab_size"], 12 + 5 * i, 200 + i) for i in range(8)]
     refs = [plain_model.forward_logits(CONFIG, weights, p) for p in prompts]
@@ -92,7 +102,7 @@ def test_one_layer_of_the_benchmarks_sizes_in_float32():
     for back in (3, 2, 1):
         got = core.step([StepEntry(f"b{i}", [p[-back]], [0]) for i, p in enumerate(prompts)])
         want8 = torch.stack([r[len(p) - back] for r, p in zip(refs, prompts)])
-        assert_logits_close(got, want8, "float32", f"batch of eight, {back} from the end, float32")
+        _close_f32(got, want8, f"batch of eight, {back} from the end, float32")
 
 
 @pytest.mark.parametrize("graphs", [False, True])
