@@ -129,18 +129,9 @@ __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&m)[2], f
 }
 
 // ------------------------------------------------------------------------ decode
-#ifndef HB_DEC_WARPS
-#define HB_DEC_WARPS 4
-#endif
-#ifndef HB_DEC_TILE
-#define HB_DEC_TILE 16
-#endif
-#ifndef HB_DEC_STAGES
-#define HB_DEC_STAGES 3
-#endif
-constexpr int DEC_WARPS = HB_DEC_WARPS;
-constexpr int DEC_TILE = HB_DEC_TILE;      // keys per warp tile
-constexpr int DEC_STAGES = HB_DEC_STAGES;  // tiles a warp keeps in shared memory (all but one in flight)
+constexpr int DEC_WARPS = 4;
+constexpr int DEC_TILE = 16;      // keys per warp tile
+constexpr int DEC_STAGES = 3;     // tiles a warp keeps in shared memory (all but one in flight)
 
 template <int HD>
 __global__ void __launch_bounds__(DEC_WARPS * 32)

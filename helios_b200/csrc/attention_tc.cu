@@ -23,9 +23,6 @@
 // Every mbarrier wait is bounded; on a timeout the block raises the error word, frees its
 // tensor memory and returns.
 #include "tcgen05.cuh"
-#ifdef HB_ATTN_TIMING
-#include <cstdio>
-#endif
 
 namespace {
 
@@ -77,9 +74,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   constexpr uint32_t S_COL = 0, O_COL = 128;
 
   extern __shared__ unsigned char smem_raw[];
-#ifdef HB_ATTN_TIMING
-  const long long t_entry = clock64();
-#endif
   pdl_launch_dependents();
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* aligned = smem_raw + (base - smem_u32(smem_raw));
@@ -204,30 +198,19 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         return true;
       };
       if (ok && n_it > 0) ok = issue_qk(0);
-#ifdef HB_ATTN_TIMING
-      long long mt[4] = {0, 0, 0, 0};
-      long long mprev = clock64();
-#define HB_MTICK(i) { const long long now = clock64(); mt[i] += now - mprev; mprev = now; }
-#else
-#define HB_MTICK(i)
-#endif
       for (int it = 0; it < n_it && ok; ++it) {
         const int s = it & 1;
         if (it + 1 < n_it) {
           ok = mbar_wait(bar(8), it & 1, abort_flag, a.error, 17);     // S(it) is in registers
           if (!ok) break;
           tc_fence_after();
-          HB_MTICK(0)
           ok = issue_qk(it + 1);
           if (!ok) break;
-          HB_MTICK(1)
         }
         ok = mbar_wait(bar(9 + s), (it >> 1) & 1, abort_flag, a.error, 18);     // V(it) has arrived
         if (!ok) break;
-        HB_MTICK(2)
         ok = mbar_wait(bar(6), it & 1, abort_flag, a.error, 14);
         if (!ok) break;
-        HB_MTICK(3)
         tc_fence_after();
         const uint32_t vs = v_smem + s * QKV_BYTES;
 #pragma unroll
@@ -237,11 +220,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         umma_commit(bar(11 + s));    // the V stage is free
         umma_commit(bar(7));         // O_tile complete
       }
-#ifdef HB_ATTN_TIMING
-      if (blockIdx.x == 0 && blockIdx.y == 0)
-        printf("mma thread per tile: wait s_free %lld  issue_qk (wait K) %lld  wait V %lld  wait p_ready %lld\n",
-               mt[0] / n_it, mt[1] / n_it, mt[2] / n_it, mt[3] / n_it);
-#endif
     }
     __syncwarp();
   } else {
@@ -290,20 +268,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     float m_ref = -INFINITY, l_run = 0.f;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     bool ok = true;
-
-#ifdef HB_ATTN_TIMING
-    long long tphase[6] = {0, 0, 0, 0, 0, 0};
-    long long tprev = clock64();
-    const long long t_loop = tprev;
-#define HB_TICK(i) { const long long now = clock64(); tphase[i] += now - tprev; tprev = now; }
-#else
-#define HB_TICK(i)
-#endif
     for (int it = 0; it < n_it; ++it) {
       const int key_base = (kt_begin + it) * TILE;
       if (!mbar_wait(bar(5), it & 1, abort_flag, a.error, 15)) { ok = false; break; }
       tc_fence_after();
-      HB_TICK(0)
       const bool masked_tile = key_base + TILE - 1 > p_first || key_base < k_min ||
                                (a.window > 0 && key_base <= p_last - a.window);
       // this thread's 64 scores stay in registers; the maximum goes over to the other
@@ -335,7 +303,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       max_exchange[((it & 1) * 2 + half) * TILE + m] = mx;
       named_barrier(2 + quarter, 64);
       mx = fmaxf(mx, max_exchange[((it & 1) * 2 + (half ^ 1)) * TILE + m]) * a.scale_log2;
-      HB_TICK(1)
       // move the reference?  Both threads of a row see the same numbers; the rows of a warp
       // decide together, because tensor memory is read and written by whole warps.
       const bool move = mx > m_ref + LAG || (m_ref == -INFINITY && mx > -INFINITY);
@@ -360,7 +327,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         packed[j] = *reinterpret_cast<uint32_t*>(&pk);
       }
       l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      HB_TICK(2)
       if (it > 0) {
         // P of the tile before has been read, and its product is in the output
         if (!mbar_wait(bar(7), (it - 1) & 1, abort_flag, a.error, 16)) { ok = false; break; }
@@ -376,7 +342,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
           }
         }
       }
-      HB_TICK(4)
 #pragma unroll
       for (int c8 = 0; c8 < 8; ++c8)
         st_shared_v4(p_smem + half * HALF_BYTES + swz(m, c8), packed[4 * c8], packed[4 * c8 + 1],
@@ -404,8 +369,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       fence_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(6));
-      HB_TICK(3)
-      HB_TICK(5)
     }
     float o_reg[OWN];
 #pragma unroll
@@ -425,13 +388,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         ok = false;
       }
     }
-#ifdef HB_ATTN_TIMING
-    if (threadIdx.x == 64 && (blockIdx.x == 0 || blockIdx.x == 300))
-      printf("block %d: entry->loop %lld, loop %lld cycles\n", blockIdx.x, t_loop - t_entry, clock64() - t_loop);
-    if (threadIdx.x == 64 && blockIdx.x == 0 && blockIdx.y == 0)
-      printf("tiles %d: wait_s %lld  pass1 %lld  exps %lld  store+arrive %lld  wait_o+rescale %lld (cycles per tile)\n",
-             n_it, tphase[0] / n_it, tphase[1] / n_it, tphase[2] / n_it, tphase[3] / n_it, tphase[4] / n_it);
-#endif
 
     // the two threads of a row add their sums
     if (half == 1) l_exchange[m] = l_run;

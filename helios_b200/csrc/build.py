@@ -108,8 +108,8 @@ def library_path(name: str) -> Path:
 
 
 def _extra_flags(name: str) -> List[str]:
-    """Per-library flags, plus whatever $HELIOS_B200_NVCC_FLAGS adds (for experiments)."""
-    return list(EXTRA_FLAGS.get(name, [])) + os.environ.get("HELIOS_B200_NVCC_FLAGS", "").split()
+    """Per-library flags."""
+    return list(EXTRA_FLAGS.get(name, []))
 
 
 EXTRA_FLAGS: Dict[str, List[str]] = {}

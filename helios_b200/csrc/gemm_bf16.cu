@@ -19,13 +19,6 @@
 // mbarrier is bounded: when it runs out the block raises an error word in global
 // memory, frees its tensor memory and returns.
 #include "tcgen05.cuh"
-#ifdef HB_GEMM_TIMING
-#include <cstdio>
-#endif
-
-#ifndef HB_SWAP_BUDGET_KB
-#define HB_SWAP_BUDGET_KB 108
-#endif
 
 namespace {
 
@@ -60,13 +53,11 @@ struct Config {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_TILES * A_BYTES + B_BYTES;
-  // swapped (decode): about 72 KB of stages, so that three blocks fit an SM: grids are
-  // sized for two per SM and the blocks of the next kernel move in (and fetch their
-  // weights) while the last blocks of this one drain; otherwise one block per SM, 196 KB
-  static constexpr int BUDGET = SWAP ? HB_SWAP_BUDGET_KB * 1024 : 196 * 1024;
+  // swapped (decode): 108 KB of stages, two blocks per SM; otherwise one block per SM, 196 KB
+  static constexpr int BUDGET = SWAP ? 108 * 1024 : 196 * 1024;
   static constexpr int STAGES_FIT = BUDGET / STAGE_BYTES;
   static constexpr int STAGES = STAGES_FIT > 8 ? 8 : (STAGES_FIT < 2 ? 2 : STAGES_FIT);
-  static constexpr int MIN_BLOCKS = SWAP ? (HB_SWAP_BUDGET_KB <= 72 ? 3 : 2) : 1;
+  static constexpr int MIN_BLOCKS = SWAP ? 2 : 1;
   static constexpr int ACC_COLS = BN * A_TILES;            // float32 columns of tensor memory in use
   static constexpr uint32_t TMEM_COLS = pow2_cols(ACC_COLS);
   static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
@@ -403,210 +394,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   }
 }
 
-// ------------------------------------------------------------------ persistent kernel (prefill)
-// Tokens on the M axis, tiles of 128 tokens x 256 weight rows (SwiGLU: 128 gate + 128 up
-// rows -> 128 result features).  One block per SM walks the tiles (token tiles fastest, so
-// blocks that run together share a weight tile in L2).  Tensor memory holds TWO accumulators
-// (2 x 256 columns): while the epilogue warps drain one, the MMA warp fills the other, so
-// the epilogue costs nothing as long as it is shorter than a tile's main loop.
-constexpr int P_BN = 256;
-constexpr int P_STAGES = 4;
-constexpr int P_A_BYTES = BM * BK * 2;
-constexpr int P_B_BYTES = P_BN * BK * 2;
-constexpr int P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
-constexpr size_t P_SMEM = (size_t)P_STAGES * P_STAGE_BYTES + 1024 + 256;
-
-template <int EPI>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_bf16_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                            GemmArgs args, int tiles_m, int tiles_n) {
-  extern __shared__ unsigned char smem_raw[];
-  pdl_launch_dependents();
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  unsigned char* aligned = smem_raw + (base - smem_u32(smem_raw));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + (size_t)P_STAGES * P_STAGE_BYTES);
-  // bars[0..S): full, [S..2S): empty, [2S..2S+2): accumulator full, [2S+2..2S+4): accumulator empty
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * P_STAGES + 4);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kb_total = (args.K + BK - 1) / BK;
-  const int n_tiles = tiles_m * tiles_n;
-  constexpr int RESULT_COLS = (EPI == EPI_GLU) ? P_BN / 2 : P_BN;
-
-  auto full_bar = [&](int s) { return smem_u32(bars + s); };
-  auto empty_bar = [&](int s) { return smem_u32(bars + P_STAGES + s); };
-  auto acc_full = [&](int b) { return smem_u32(bars + 2 * P_STAGES + b); };
-  auto acc_empty = [&](int b) { return smem_u32(bars + 2 * P_STAGES + 2 + b); };
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < P_STAGES; ++s) {
-      mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), 1);
-    }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(acc_full(b), 1);
-      mbar_init(acc_empty(b), 4);          // one arrival per epilogue warp
-    }
-    *abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), 512);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-
-  if (warp == 0) {
-    if (lane == 0) {
-      // ---------------------------------------------------------- TMA producer
-      // `it` counts k-blocks over all of this block's tiles; stage = it % P_STAGES.  (No
-      // 64-bit arithmetic and no divisions by run-time values inside the k loop: this thread
-      // has to keep several stages ahead of the tensor cores.)
-      pdl_wait();
-      uint32_t it = 0;
-      for (int q = blockIdx.x; q < n_tiles; q += gridDim.x) {
-        const int tile_m = q % tiles_m, tile_n = q / tiles_m;
-        const int a_row = tile_m * BM;
-        const int b_row0 = tile_n * RESULT_COLS, b_row1 = args.glu_offset + tile_n * RESULT_COLS;
-        for (int kb = 0; kb < kb_total; ++kb, ++it) {
-          const int s = it % P_STAGES;
-          const uint32_t ph = (it / P_STAGES) & 1;
-          if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, args.error, 1)) { q = n_tiles; break; }
-          const uint32_t sa = base + s * P_STAGE_BYTES, sb = sa + P_A_BYTES;
-          mbar_expect_tx(full_bar(s), P_STAGE_BYTES);
-          const int k0 = kb * BK;
-          tma_load_2d(sb, &map_b, full_bar(s), k0, b_row0);
-          if (EPI == EPI_GLU) tma_load_2d(sb + P_B_BYTES / 2, &map_b, full_bar(s), k0, b_row1);
-          tma_load_2d(sa, &map_a, full_bar(s), k0, a_row);
-        }
-      }
-    }
-    __syncwarp();
-  } else if (warp == 1) {
-    if (lane == 0) {
-      // ---------------------------------------------------------- MMA issuer
-      constexpr uint32_t idesc = instr_desc(BM, P_BN);
-      int it = 0, j = 0;
-      bool ok = true;
-#ifdef HB_GEMM_TIMING
-      long long t_wait = 0, t_issue = 0;
-#endif
-      for (int q = blockIdx.x; q < n_tiles && ok; q += gridDim.x, ++j) {
-        const int b = j & 1;
-        const uint32_t use = (uint32_t)(j >> 1);
-        ok = mbar_wait(acc_empty(b), (use & 1) ^ 1, abort_flag, args.error, 4);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t acc_addr = tmem_base + (uint32_t)(b * P_BN);
-        for (int kb = 0; kb < kb_total; ++kb, ++it) {
-          const int s = it % P_STAGES;
-          const uint32_t ph = (it / P_STAGES) & 1;
-#ifdef HB_GEMM_TIMING
-          const long long t0 = clock64();
-#endif
-          ok = mbar_wait(full_bar(s), ph, abort_flag, args.error, 2);
-          if (!ok) break;
-          tc_fence_after();
-#ifdef HB_GEMM_TIMING
-          const long long t1 = clock64();
-          t_wait += t1 - t0;
-#endif
-          const uint32_t sa = base + s * P_STAGE_BYTES, sb = sa + P_A_BYTES;
-#pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k)
-            umma_bf16(acc_addr, smem_desc(sa + k * UMMA_K * 2), smem_desc(sb + k * UMMA_K * 2), idesc,
-                      (kb > 0 || k > 0) ? 1u : 0u);
-          umma_commit(empty_bar(s));
-#ifdef HB_GEMM_TIMING
-          t_issue += clock64() - t1;
-#endif
-        }
-        if (ok) umma_commit(acc_full(b));
-      }
-#ifdef HB_GEMM_TIMING
-      if (blockIdx.x == 0)
-        printf("1-SM MMA thread: %d k-blocks, per k-block: wait for operands %lld cycles, issue %lld cycles\n",
-               it, t_wait / (it ? it : 1), t_issue / (it ? it : 1));
-#endif
-    }
-    __syncwarp();
-  } else {
-    // ------------------------------------------------------------ epilogue warps
-    pdl_wait();
-    const int quarter = warp & 3;
-    const int r = quarter * 32 + lane;
-    int j = 0;
-    for (int q = blockIdx.x; q < n_tiles; q += gridDim.x, ++j) {
-      const int b = j & 1;
-      const uint32_t use = (uint32_t)(j >> 1);
-      const int tile_m = q % tiles_m, tile_n = q / tiles_m;
-      if (!mbar_wait(acc_full(b), use & 1, abort_flag, args.error, 3)) break;
-      if (*abort_flag) break;
-      tc_fence_after();
-      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(b * P_BN);
-      const int t = tile_m * BM + r;
-      for (int c = 0; c < RESULT_COLS; c += 16) {
-        float val[16];
-        if (EPI == EPI_GLU) {
-          float g[16], u[16];
-          tmem_ld16(taddr + c, g);
-          tmem_ld16(taddr + RESULT_COLS + c, u);
-#pragma unroll
-          for (int i = 0; i < 16; ++i) val[i] = g[i] / (1.f + __expf(-g[i])) * u[i];
-        } else {
-          tmem_ld16(taddr + c, val);
-        }
-        const int n0 = tile_n * RESULT_COLS + c;
-        if (t < args.T) {
-          if (args.bias) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) if (n0 + i < args.N) val[i] += args.bias[n0 + i];
-          }
-          if (!args.out_f32 && n0 + 16 <= args.N && (args.ldo & 7) == 0) {
-            uint32_t packed[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              __nv_bfloat162 p = __floats2bfloat162_rn(val[2 * i], val[2 * i + 1]);
-              packed[i] = *reinterpret_cast<uint32_t*>(&p);
-            }
-            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(args.out) + (size_t)t * args.ldo + n0);
-            dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-            dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              if (n0 + i < args.N) {
-                if (args.out_f32) reinterpret_cast<float*>(args.out)[(size_t)t * args.ldo + n0 + i] = val[i];
-                else reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)t * args.ldo + n0 + i] = __float2bfloat16_rn(val[i]);
-              }
-            }
-          }
-        }
-      }
-      // this warp has read its lanes of the accumulator: hand it back to the MMA warp
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) {
-        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty(b)) : "memory");
-      }
-    }
-  }
-
-  tc_fence_before();
-  __syncthreads();
-  if (*abort_flag && threadIdx.x == 0) {
-    for (int i = 0; i < 2000; ++i) __nanosleep(100);
-  }
-  __syncthreads();
-  if (warp == 1) {
-    tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
-  }
-}
-
 // ------------------------------------------------------------------ two-SM persistent kernel (prefill)
 // A cluster of two blocks works on tiles of 256 tokens x 256 weight rows with
 // tcgen05.mma.cta_group::2: each block stages its 128 token rows and HALF of the weight
@@ -797,6 +584,13 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
 }
 
 // ------------------------------------------------------------------ host side
+constexpr int HB_MAX_DEVICES = 64;
+inline int current_device() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= HB_MAX_DEVICES) return -1;
+  return dev;
+}
+
 template <int BN, bool SWAP, int EPI>
 int launch(const void* x, const void* w, const GemmArgs& args, int w_rows, int ldx, int ldw,
            cudaStream_t stream) {
@@ -811,11 +605,14 @@ int launch(const void* x, const void* w, const GemmArgs& args, int w_rows, int l
     if (!make_map(&map_b, w, w_rows, args.K, ldw, EPI == EPI_GLU ? BN / 2 : BN)) return HB_LAUNCH_FAILED;
   }
   auto kernel = gemm_bf16_kernel<BN, SWAP, EPI>;
-  static bool configured = false;
-  if (!configured) {
+  // the shared-memory limit is a per-device attribute of the kernel
+  static bool configured[HB_MAX_DEVICES] = {};
+  const int dev = current_device();
+  if (dev < 0) return HB_LAUNCH_FAILED;
+  if (!configured[dev]) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM) != cudaSuccess)
       return HB_LAUNCH_FAILED;
-    configured = true;
+    configured[dev] = true;
   }
   dim3 grid;
   if (SWAP) {
@@ -850,49 +647,23 @@ int launch(const void* x, const void* w, const GemmArgs& args, int w_rows, int l
 }
 
 template <int EPI>
-int launch_persistent(const void* x, const void* w, const GemmArgs& args, int w_rows, int ldx, int ldw,
-                      cudaStream_t stream) {
-  CUtensorMap map_a, map_b;
-  if (!make_map(&map_a, x, args.T, args.K, ldx, BM)) return HB_LAUNCH_FAILED;
-  if (!make_map(&map_b, w, w_rows, args.K, ldw, EPI == EPI_GLU ? P_BN / 2 : P_BN)) return HB_LAUNCH_FAILED;
-  auto kernel = gemm_bf16_persistent_kernel<EPI>;
-  static bool configured = false;
-  static int sm_count = 0;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P_SMEM) != cudaSuccess)
-      return HB_LAUNCH_FAILED;
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess ||
-        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0)
-      return HB_LAUNCH_FAILED;
-    configured = true;
-  }
-  const int per_tile = (EPI == EPI_GLU) ? P_BN / 2 : P_BN;
-  const int tiles_m = (args.T + BM - 1) / BM, tiles_n = (args.N + per_tile - 1) / per_tile;
-  const int n_tiles = tiles_m * tiles_n;
-  const int blocks = n_tiles < sm_count ? n_tiles : sm_count;
-  hb_launch(kernel, dim3(blocks), dim3(GEMM_THREADS), P_SMEM, stream, map_a, map_b, args, tiles_m, tiles_n);
-  return hb_check_launch();
-}
-
-template <int EPI>
 int launch_2sm(const void* x, const void* w, const GemmArgs& args, int w_rows, int ldx, int ldw,
                cudaStream_t stream) {
   CUtensorMap map_a, map_b;
   if (!make_map(&map_a, x, args.T, args.K, ldx, BM)) return HB_LAUNCH_FAILED;
   if (!make_map(&map_b, w, w_rows, args.K, ldw, 128)) return HB_LAUNCH_FAILED;
   auto kernel = gemm_bf16_2sm_kernel<EPI>;
-  static bool configured = false;
-  static int sm_count = 0;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)T2_SMEM) != cudaSuccess)
+  static int sm_counts[HB_MAX_DEVICES] = {};         // 0: this device is not set up yet
+  const int dev = current_device();
+  if (dev < 0) return HB_LAUNCH_FAILED;
+  if (sm_counts[dev] == 0) {
+    int n = 0;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)T2_SMEM) != cudaSuccess ||
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
       return HB_LAUNCH_FAILED;
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess ||
-        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0)
-      return HB_LAUNCH_FAILED;
-    configured = true;
+    sm_counts[dev] = n;
   }
+  const int sm_count = sm_counts[dev];
   const int per_tile = (EPI == EPI_GLU) ? 128 : 256;
   const int tiles_m = (args.T + 255) / 256, tiles_n = (args.N + per_tile - 1) / per_tile;
   const int n_tiles = tiles_m * tiles_n;
@@ -1000,13 +771,9 @@ HB_EXPORT int hb_gemm_bf16(void* out, const void* x, const void* w, const float*
 #define HB_GEMM_CASE(BN_, SWAP_)                                                              \
   return glu ? launch<BN_, SWAP_, EPI_GLU>(x, w, a, w_rows, ldx, ldw, stream)                 \
              : launch<BN_, SWAP_, EPI_STORE>(x, w, a, w_rows, ldx, ldw, stream)
-  if (swap_bn == 0 && k_splits == 1) {    // prefill: a persistent kernel, two SMs a tile or one
-    if (cluster == 2)
-      return glu ? launch_2sm<EPI_GLU>(x, w, a, w_rows, ldx, ldw, stream)
-                 : launch_2sm<EPI_STORE>(x, w, a, w_rows, ldx, ldw, stream);
-    return glu ? launch_persistent<EPI_GLU>(x, w, a, w_rows, ldx, ldw, stream)
-               : launch_persistent<EPI_STORE>(x, w, a, w_rows, ldx, ldw, stream);
-  }
+  if (swap_bn == 0 && k_splits == 1 && cluster == 2)    // prefill: a persistent kernel on pairs of SMs
+    return glu ? launch_2sm<EPI_GLU>(x, w, a, w_rows, ldx, ldw, stream)
+               : launch_2sm<EPI_STORE>(x, w, a, w_rows, ldx, ldw, stream);
   switch (swap_bn) {
     case 0: HB_GEMM_CASE(256, false);
     case 16: HB_GEMM_CASE(16, true);

@@ -23,8 +23,10 @@ constexpr size_t PARTIAL_FLOATS = (HB_GEMM_NOALLOC_SCRATCH_BYTES - PARTIALS_OFFS
 // GPU can reach host memory, scribble over the wrong bytes).
 static __device__ __align__(256) unsigned char g_noalloc_scratch[HB_GEMM_NOALLOC_SCRATCH_BYTES];
 
-constexpr int MAX_DEVICES = 64;
-unsigned char* g_scratch_ptr[MAX_DEVICES] = {};   // device address of the array, per device
+constexpr int MAX_DEVICES = HB_MAX_DEVICES;
+// device address of the array, per device.  Written without a lock: two host threads that
+// make the first call on a device at once would both look the same address up.
+unsigned char* g_scratch_ptr[MAX_DEVICES] = {};
 
 int fail(int code, char* err, int err_len, const char* fmt, long long a = 0, long long b = 0) {
   if (err != nullptr && err_len > 0) std::snprintf(err, (size_t)err_len, fmt, a, b);
@@ -80,20 +82,28 @@ int hb_gemm_bf16_noalloc(void* out, const void* x, const void* w, int T, int N, 
   unsigned char* scratch = g_scratch_ptr[dev];
   int* error_word = reinterpret_cast<int*>(scratch);
 
-  // the error word of the launch before (the stream has to be idle to read it; only looked
-  // at when that costs nothing, i.e. when the stream has finished)
+  // The error word of earlier launches.  A kernel that gives up a bounded wait sets it and
+  // nothing but this block clears it, so a code is never lost: it is reported by the first
+  // call that finds the stream idle (reading it earlier would make this call wait for the
+  // work in flight).  The read is a copy on `stream` itself, not on the legacy default
+  // stream, so it neither waits for other streams nor disturbs a capture elsewhere.
   cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
   cudaStreamIsCapturing(stream, &capturing);
   if (!first && capturing == cudaStreamCaptureStatusNone && cudaStreamQuery(stream) == cudaSuccess) {
     int code = 0;
-    if (cudaMemcpy(&code, error_word, sizeof(int), cudaMemcpyDeviceToHost) == cudaSuccess && code != 0) {
+    if (cudaMemcpyAsync(&code, error_word, sizeof(int), cudaMemcpyDeviceToHost, stream) == cudaSuccess &&
+        cudaStreamSynchronize(stream) == cudaSuccess && code != 0) {
       cudaMemsetAsync(error_word, 0, sizeof(int), stream);
       return fail(HB_NOALLOC_KERNEL_GAVE_UP, err, err_len,
-                  "hb_gemm_bf16_noalloc: the previous launch gave up a bounded wait (code %lld)", code);
+                  "hb_gemm_bf16_noalloc: an earlier launch gave up a bounded wait (code %lld)", code);
     }
   }
-  // tickets and the error word start at zero; the partial sums need no clearing
-  if (cudaMemsetAsync(scratch, 0, PARTIALS_OFFSET, stream) != cudaSuccess)
+  // The tickets start at zero (the last block of a tile resets its ticket, but a launch that
+  // gave up may have left some behind); the partial sums need no clearing.  On the first call
+  // the error word is cleared too: the array's initial contents are not relied on.
+  if (first && cudaMemsetAsync(error_word, 0, sizeof(int), stream) != cudaSuccess)
+    return fail(HB_NOALLOC_LAUNCH_FAILED, err, err_len, "hb_gemm_bf16_noalloc: cudaMemsetAsync failed");
+  if (cudaMemsetAsync(scratch + TICKETS_OFFSET, 0, 4 * HB_GEMM_NOALLOC_MAX_TILES, stream) != cudaSuccess)
     return fail(HB_NOALLOC_LAUNCH_FAILED, err, err_len, "hb_gemm_bf16_noalloc: cudaMemsetAsync failed");
 
   GemmArgs a;

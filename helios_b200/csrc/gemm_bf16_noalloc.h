@@ -32,15 +32,16 @@
  *
  * The caller owns x, w and out (device memory, out = T * N bfloat16).  The
  * function calls no cudaMalloc, cudaFree or any other allocating routine; it
- * issues one cudaMemsetAsync (the tickets and the error word must start at
- * zero; the partial sums need no clearing, every slot is written before it is
- * read) and one kernel launch on `stream`.
+ * issues one cudaMemsetAsync (the tickets must start at zero; the partial sums
+ * need no clearing, every slot is written before it is read) and one kernel
+ * launch on `stream`.
  *
  * First call on a device: the address of the scratch array is looked up with
  * cudaGetSymbolAddress (the array's name is only a host-side handle, not a
- * device pointer) and the kernel's shared-memory limit is raised.  This set-up
- * happens inside the first call for each device, with that device current, and is
- * remembered.  Make that first call outside of any stream capture.
+ * device pointer) and the kernel's shared-memory limit is raised; both are kept
+ * per device.  This set-up happens inside the first call for each device, with
+ * that device current.  Make that first call outside of any stream capture, and
+ * from one host thread.
  *
  * All calls on a device share the one scratch area, and it keeps what the last
  * call left there.  Two calls that overlap on the GPU (different streams, or
@@ -49,9 +50,12 @@
  *
  * Returns 0 on success, else one of the codes below; if `err` is not NULL a
  * one-line message is written there (at most err_len bytes, always terminated).
- * A kernel that gave up a bounded wait reports through hb_gemm_bf16_noalloc's
- * error word only on the NEXT call on that device (code HB_NOALLOC_KERNEL_GAVE_UP),
- * since reading it needs the stream to have finished.
+ * A kernel that gave up a bounded wait leaves a code in the scratch area's error
+ * word.  It is read, reported (HB_NOALLOC_KERNEL_GAVE_UP) and cleared by the first
+ * later call on that device that finds `stream` idle: reading it while work is in
+ * flight would make the call wait.  A caller that issues calls back to back
+ * without ever letting the stream drain therefore hears of it late, but the code
+ * is not lost.  That read is a 4-byte copy on `stream` followed by a wait for it.
  */
 #ifndef HELIOS_B200_GEMM_BF16_NOALLOC_H
 #define HELIOS_B200_GEMM_BF16_NOALLOC_H
@@ -72,7 +76,7 @@ enum {
   HB_NOALLOC_TOO_LARGE = 2,        /* T, the tile count or the partial sums exceed the maximum */
   HB_NOALLOC_SETUP_FAILED = 3,     /* cudaGetSymbolAddress or another set-up call failed */
   HB_NOALLOC_LAUNCH_FAILED = 4,
-  HB_NOALLOC_KERNEL_GAVE_UP = 5    /* the previous launch on this device ran out of a bounded wait */
+  HB_NOALLOC_KERNEL_GAVE_UP = 5    /* an earlier launch on this device ran out of a bounded wait */
 };
 
 int hb_gemm_bf16_noalloc(void* out, const void* x, const void* w, int T, int N, int K,

@@ -1,9 +1,11 @@
 """Python launchers of the CUDA kernels.
 
 Every function checks its tensors (device, dtype, layout, sizes) and raises a
-clear error for a size the kernel does not take; it never computes on the CPU
-and never falls back to a library.  Kernels run on torch's current stream, so
-they can be captured into a CUDA graph with the rest of a step.
+clear error for a size the kernel does not take; it never computes on the CPU.
+Two kinds of matrix product go to the library (cuBLAS through torch), as all of
+the reference's do: see ``linear`` and ``GEMM_LIBRARY_TOKEN_RANGE``.  Kernels run
+on torch's current stream, so they can be captured into a CUDA graph with the
+rest of a step.
 """
 from __future__ import annotations
 
@@ -330,7 +332,7 @@ def cluster_capacity(bn: int, glu: bool, size: int) -> int:
         lib = load_library("gemm_bf16")
         n = int(lib.hb_gemm_bf16_max_clusters(bn, int(glu), size))
         if n <= 0:
-            n = _SM_COUNT // size
+            n = sm_count() // size
         _cluster_capacity[key] = n * (2 if bn else 1)
     return _cluster_capacity[key]
 
@@ -359,12 +361,12 @@ def _gemm_plan(T: int, N: int, K: int, glu: bool):
         bn = 16 if T <= 16 else 32 if T <= 32 else 64 if T <= 64 else 128
         tiles = -(-N // 128) * -(-T // bn)
         cols = bn * (2 if glu else 1)
-        slots = 2 * _SM_COUNT
+        slots = 2 * sm_count()
     else:
         bn = 0
         tiles = -(-T // 128) * -(-N // (128 if glu else 256))
         cols = 256
-        slots = _SM_COUNT
+        slots = sm_count()
         if GEMM_TWO_SM:
             # the two-SM kernel takes whole reductions only; even with part of the pairs idle
             # it beats the one-SM kernel with a split reduction (20 against 85 microseconds
@@ -474,8 +476,9 @@ def _library_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.
     padded = -(-T // step) * step if step > 1 else T
     if padded == T:
         return torch.nn.functional.linear(x, weight, bias)
-    rows = x.new_empty((padded, x.shape[1]))      # what the spare rows hold reaches no result row
+    rows = x.new_empty((padded, x.shape[1]))
     rows[:T].copy_(x)
+    rows[T:].zero_()                              # they reach no result row, but must not hold NaN
     return torch.nn.functional.linear(rows, weight, bias)[:T]
 
 
@@ -563,7 +566,16 @@ ATTENTION_TILE_PAIRS = True
 #: ... and the step gives at least this many blocks of two tiles: with fewer, the blocks of one
 #: tile (twice as many, each about 1/1.5 as long) still fit the 148 SMs in one round
 ATTENTION_PAIR_MIN_BLOCKS = 75
-_SM_COUNT = 148
+_sm_counts = {}
+
+
+def sm_count(device=None) -> int:
+    """Streaming multiprocessors of the (current) device."""
+    index = torch.cuda.current_device() if device is None else torch.device(device).index or 0
+    n = _sm_counts.get(index)
+    if n is None:
+        n = _sm_counts[index] = torch.cuda.get_device_properties(index).multi_processor_count
+    return n
 
 
 def _wave_splits(blocks: int, slots: int, most: int) -> int:
@@ -584,7 +596,7 @@ def _wave_splits(blocks: int, slots: int, most: int) -> int:
 def decode_splits(num_seqs: int, num_kv_heads: int, max_context: int) -> int:
     """Slices of the context per (request, KV head) of the decode attention kernel: two
     blocks are resident per SM; a slice has at least 128 keys."""
-    return _wave_splits(max(1, num_seqs * num_kv_heads), 2 * _SM_COUNT,
+    return _wave_splits(max(1, num_seqs * num_kv_heads), 2 * sm_count(),
                         max(1, min(32, max_context // 128)))
 
 
@@ -614,7 +626,7 @@ def attention_decode_bf16(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: tor
     part_o = part_ml = None
     # slices as one cluster only while all blocks are resident at once: with several rounds
     # of blocks, clusters (whose blocks must start together) cost more than the merge kernel
-    one_round = S * num_kv_heads * n_splits <= 2 * _SM_COUNT
+    one_round = S * num_kv_heads * n_splits <= 2 * sm_count()
     if n_splits > 8 or (n_splits > 1 and not (ATTENTION_CLUSTER_MERGE and one_round)):
         part_o = torch.empty((S, num_heads, n_splits, head_dim), dtype=torch.float32, device=qkv.device)
         part_ml = torch.empty((S, num_heads, n_splits, 2), dtype=torch.float32, device=qkv.device)

@@ -104,8 +104,8 @@ def test_k_that_is_no_multiple_of_8_goes_to_the_library_and_is_refused_by_the_ke
                                    (1000, 1000, 520), (513, 6144, 4096)])
 @pytest.mark.parametrize("glu", [False, True])
 def test_prefill_kernels_one_and_two_sm(T, N, K, glu, two_sm):
-    """Tokens on the M axis: the one-SM persistent kernel and the cta_group::2 kernel
-    (pairs of SMs on 256x256 tiles), ragged in every dimension."""
+    """Tokens on the M axis: one block per 128x256 tile, and the persistent cta_group::2
+    kernel (pairs of SMs on 256x256 tiles), ragged in every dimension."""
     x, w, b = _case(T, N, K, T + N + K, glu)
     xd, wd = x.double(), w.double()
     if glu:
