@@ -15,6 +15,7 @@ import torch
 
 from ..csrc import ops
 from .base import LayerCache, Mixer, PagedCacheSpec, WeightSpec, register_part
+from .norm import RMSNorm
 
 
 class GQAAttention(Mixer):
@@ -67,13 +68,37 @@ class GQAAttention(Mixer):
                                     tensors["v_proj.bias"]], dim=0).contiguous()
 
     # ---------------------------------------------------------------- forward
+    def _rotary_tables(self, ctx):
+        if not self.rotary:
+            return None, None
+        if self.position is not None:
+            return self.position.tables(ctx)
+        return ctx.rotary_cos, ctx.rotary_sin
+
+    def forward_from_residual(self, ctx, residual: torch.Tensor, norm, cache: LayerCache, state=None) -> bool:
+        """Steps of very few tokens: norm + projection + rotation + cache write in one launch,
+        attention, output projection + residual add in one launch."""
+        if ctx.act_dtype != torch.bfloat16 or type(norm) is not RMSNorm or cache is None \
+                or self.head_dim % 8 \
+                or not ops.small_step_fits(ctx.num_tokens, self.width, self.width, self.num_heads * self.head_dim):
+            return False
+        cos, sin = self._rotary_tables(ctx)
+        if cos is None or cos.shape[1] * 2 != self.head_dim:
+            return False
+        table = ctx.block_tables[cache.group]
+        qkv = ops.small_norm_qkv_rope(residual, norm.weight, norm.eps, self.w_qkv, self.b_qkv, cos, sin,
+                                      ctx.positions, ctx.seq_of_token, table, cache.k_pages, cache.v_pages,
+                                      self.num_heads, self.num_kv_heads, self.head_dim, cache.page_size,
+                                      write_cache=cache.write)
+        attn = ops.attention(ctx, qkv, cache.k_pages, cache.v_pages, table, self.num_heads,
+                             self.num_kv_heads, self.head_dim, cache.page_size, self.window, self.scale)
+        ops.small_linear_residual(residual, attn, self.w_o)
+        return True
+
     def forward(self, ctx, x: torch.Tensor, cache: LayerCache, state=None) -> torch.Tensor:
         qkv = ops.linear(x, self.w_qkv, self.b_qkv)
         table = ctx.block_tables[cache.group]
-        cos = sin = None
-        if self.rotary:
-            cos, sin = self.position.tables(ctx) if self.position is not None else \
-                (ctx.rotary_cos, ctx.rotary_sin)
+        cos, sin = self._rotary_tables(ctx)
         ops.rope_kv_write(qkv, cos, sin, ctx.positions, ctx.seq_of_token, table,
                           cache.k_pages, cache.v_pages, self.num_heads, self.num_kv_heads,
                           self.head_dim, cache.page_size, write_cache=cache.write)

@@ -149,6 +149,14 @@ class Mixer(Part):
         [slots, *state_spec.shape]; a request's row is ``ctx.slots[seq]``."""
         raise NotImplementedError
 
+    def forward_from_residual(self, ctx, residual: torch.Tensor, norm: "Norm",
+                              cache: Optional[LayerCache], state: Optional[torch.Tensor]) -> bool:
+        """Optional fusion with the norm before and the add after: apply ``norm`` to the
+        float32 residual stream (to which nothing is pending), run, and ADD the output to
+        ``residual`` in place.  Return False, having done nothing, where the part has no such
+        path for this step; the block then norms, calls ``forward`` and adds as usual."""
+        return False
+
 
 class FeedForward(Part):
     def state_spec(self) -> Optional[StateSpec]:
@@ -158,6 +166,10 @@ class FeedForward(Part):
 
     def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
+
+    def forward_from_residual(self, ctx, residual: torch.Tensor, norm: "Norm") -> bool:
+        """As ``Mixer.forward_from_residual``: norm, run and add in place, or return False."""
+        return False
 
 
 class Block:

@@ -36,10 +36,18 @@ class PreNormBlock(Block):
 
     def forward(self, ctx, residual: torch.Tensor, delta: Optional[torch.Tensor],
                 cache: Optional[LayerCache], state: Optional[torch.Tensor]):
-        x = self.mixer_norm.add_forward(residual, delta, ctx.act_dtype)
-        delta = self._mixer.forward(ctx, x, cache, state)
-        x = self.ffn_norm.add_forward(residual, delta, ctx.act_dtype)
-        delta = self.ffn.forward(ctx, x)
+        # a part may take the norm before it and the add after it into its own kernels (steps
+        # of very few tokens); that needs a residual stream to which nothing is pending
+        if delta is None and self._mixer.forward_from_residual(ctx, residual, self.mixer_norm, cache, state):
+            pass
+        else:
+            x = self.mixer_norm.add_forward(residual, delta, ctx.act_dtype)
+            delta = self._mixer.forward(ctx, x, cache, state)
+        if delta is None and self.ffn.forward_from_residual(ctx, residual, self.ffn_norm):
+            pass
+        else:
+            x = self.ffn_norm.add_forward(residual, delta, ctx.act_dtype)
+            delta = self.ffn.forward(ctx, x)
         return residual, delta
 
 

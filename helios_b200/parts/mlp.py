@@ -8,6 +8,7 @@ import torch
 
 from ..csrc import ops
 from .base import FeedForward, WeightSpec, register_part
+from .norm import RMSNorm
 
 
 class SwiGLU(FeedForward):
@@ -30,6 +31,16 @@ class SwiGLU(FeedForward):
 
     def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
         return ops.linear(ops.linear_swiglu(x, self.w_gate_up), self.w_down)
+
+    def forward_from_residual(self, ctx, residual: torch.Tensor, norm) -> bool:
+        """Steps of very few tokens: norm + gate|up + SwiGLU in one launch, down + residual
+        add in another."""
+        if ctx.act_dtype != torch.bfloat16 or type(norm) is not RMSNorm \
+                or not ops.small_step_fits(ctx.num_tokens, self.width, self.width, self.inner):
+            return False
+        h = ops.small_norm_swiglu(residual, norm.weight, norm.eps, self.w_gate_up)
+        ops.small_linear_residual(residual, h, self.w_down)
+        return True
 
 
 register_part("feed_forward", "swiglu", SwiGLU)
