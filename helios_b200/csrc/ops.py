@@ -91,7 +91,7 @@ def preload(dtype: torch.dtype) -> None:
 
     names = ["elementwise", "attention_generic"]
     names += ["gemm_f32"] if dtype == torch.float32 else ["attention_bf16", "attention_tc", "attention_pair",
-                                                          "gemm_bf16", "small_step"]
+                                                          "gemm_bf16", "small_step", "decode_step"]
     build_all(names)
     for n in names:
         load_library(n)
@@ -308,6 +308,8 @@ def _gemm_workspace(device):
 
 def check_kernel_errors(device=None) -> None:
     """Raise if a kernel of this package gave up a bounded wait (synchronises)."""
+    from ..models import dense_decode_step
+    dense_decode_step.check_errors()
     for dev, (_s, _t, err) in _gemm_ws.items():
         if device is not None and dev != torch.device(device):
             continue

@@ -33,7 +33,7 @@ def build_dense_decoder_plan(cfg: DenseDecoderConfig) -> ModelPlan:
         ))
         prefixes.append(f"model.layers.{i}.")
     tied = {"lm_head.weight": "model.embed_tokens.weight"} if cfg.tie_word_embeddings else {}
-    return ModelPlan(
+    plan = ModelPlan(
         config=cfg,
         embedding=TokenEmbedding(cfg.vocab_size, cfg.hidden_size),
         position=rope,
@@ -43,6 +43,10 @@ def build_dense_decoder_plan(cfg: DenseDecoderConfig) -> ModelPlan:
         head=OutputHead(cfg.vocab_size, cfg.hidden_size),
         tied=tied,
     )
+    # decode steps of a few requests run as one persistent kernel where it fits
+    from .dense_decode_step import DenseDecodeStep
+    plan.fused_steps.append(DenseDecodeStep(plan))
+    return plan
 
 
 def _toy_config(architecture: str, model_type: str):
