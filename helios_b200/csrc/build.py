@@ -39,14 +39,12 @@ LIBRARIES: Dict[str, str] = {
     "gemm_bf16": "gemm_bf16.cu",
     "gemm_bf16_noalloc": "gemm_bf16_noalloc.cu",
     "small_step": "small_step.cu",
-    "decode_step": "decode_step.cu",
     "sampling": "sampling.cu",
 }
 _HEADERS = ["common.cuh", "tcgen05.cuh"]
 # further files a library's source includes
 _INCLUDES: Dict[str, List[str]] = {"gemm_bf16_noalloc": ["gemm_bf16.cu", "gemm_bf16_noalloc.h"],
-                                   "attention_bf16": ["attention_mma.cuh"],
-                                   "decode_step": ["attention_mma.cuh"]}
+                                   "attention_bf16": ["attention_mma.cuh"]}
 
 NVCC_FLAGS = [
     "-O3", "-std=c++17",

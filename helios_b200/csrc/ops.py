@@ -91,7 +91,7 @@ def preload(dtype: torch.dtype) -> None:
 
     names = ["elementwise", "attention_generic"]
     names += ["gemm_f32"] if dtype == torch.float32 else ["attention_bf16", "attention_tc", "attention_pair",
-                                                          "gemm_bf16", "small_step", "decode_step"]
+                                                          "gemm_bf16", "small_step"]
     build_all(names)
     for n in names:
         load_library(n)
@@ -308,8 +308,6 @@ def _gemm_workspace(device):
 
 def check_kernel_errors(device=None) -> None:
     """Raise if a kernel of this package gave up a bounded wait (synchronises)."""
-    from ..models import dense_decode_step
-    dense_decode_step.check_errors()
     for dev, (_s, _t, err) in _gemm_ws.items():
         if device is not None and dev != torch.device(device):
             continue
@@ -533,10 +531,10 @@ def small_step_fits(tokens: int, width: int, *ks: int) -> bool:
     if not 0 < tokens <= min(limit, 16):
         return False
     # the step's activations must fit a block's shared memory as bfloat16 rows
-    most = _small_max_k.get(tokens <= 8)
+    most = _small_max_k.get(tokens)
     if most is None:
         lib = load_library("small_step")
-        most = _small_max_k[tokens <= 8] = int(lib.hb_small_step_max_k(int(tokens)))
+        most = _small_max_k[tokens] = int(lib.hb_small_step_max_k(int(tokens)))
     return all(k % 8 == 0 and k <= most for k in ks)
 
 

@@ -105,13 +105,15 @@ __device__ __forceinline__ int tile_row(const SmallArgs& a, int tile, int n) {
 // 16-byte reads of two neighbouring rows fall into different banks.
 __host__ __device__ inline int x_row_bytes(int K) { return ((2 * K + 63) / 128) * 128 + 64; }
 
-template <int MODE, int NT, bool NORM, bool T8>
-__global__ void __launch_bounds__(SS_THREADS, 2)
+// DEEP: twice the weights requested at once (and twice the registers, so one block an SM):
+// for long reductions in launches of at most one block per SM, where the second round trip
+// to memory would otherwise wait for the first.
+template <int MODE, int NT, bool NORM, bool T8, bool DEEP>
+__global__ void __launch_bounds__(SS_THREADS, DEEP ? 1 : 2)
 small_step_kernel(const SmallArgs a) {
-  constexpr int U = 8 / NT;                 // blocks of 32 k whose weights a warp requests at once
-  constexpr int ROWS = T8 ? 8 : 16;
+  constexpr int U = (DEEP ? 16 : 8) / NT;   // blocks of 32 k whose weights a warp requests at once
   pdl_launch_dependents();
-  extern __shared__ __align__(16) unsigned char xs[];     // [ROWS][x_row_bytes(K)] bfloat16 activations
+  extern __shared__ __align__(16) unsigned char xs[];     // [T][x_row_bytes(K)] bfloat16 activations
   __shared__ float red[SS_WARPS][NT][16][8];
   __shared__ float rstd_of[16];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -145,33 +147,29 @@ small_step_kernel(const SmallArgs a) {
   const int chunks = a.K >> 3;              // 16-byte chunks of a row
   if (NORM) {
     // a warp takes a row: bfloat16(residual * norm weight) and the row's sum of squares
-    if (warp < ROWS) {
+    if (warp < a.T) {
       float ss = 0.f;
       unsigned char* dst = xs + (size_t)warp * stride;
-      if (warp < a.T) {
-        const float* src = a.residual_in + (size_t)warp * a.K;
+      const float* src = a.residual_in + (size_t)warp * a.K;
 #pragma unroll 4
-        for (int c = lane; c < chunks; c += 32) {
-          const float4 p = *reinterpret_cast<const float4*>(src + c * 8);
-          const float4 q = *reinterpret_cast<const float4*>(src + c * 8 + 4);
-          const float4 wp = *reinterpret_cast<const float4*>(a.norm_weight + c * 8);
-          const float4 wq = *reinterpret_cast<const float4*>(a.norm_weight + c * 8 + 4);
-          ss += p.x * p.x + p.y * p.y + p.z * p.z + p.w * p.w + q.x * q.x + q.y * q.y + q.z * q.z + q.w * q.w;
-          *reinterpret_cast<uint4*>(dst + c * 16) =
-              make_uint4(pack2(p.x * wp.x, p.y * wp.y), pack2(p.z * wp.z, p.w * wp.w),
-                         pack2(q.x * wq.x, q.y * wq.y), pack2(q.z * wq.z, q.w * wq.w));
-        }
-      } else {
-        for (int c = lane; c < chunks; c += 32) *reinterpret_cast<uint4*>(dst + c * 16) = zero4;
+      for (int c = lane; c < chunks; c += 32) {
+        const float4 p = *reinterpret_cast<const float4*>(src + c * 8);
+        const float4 q = *reinterpret_cast<const float4*>(src + c * 8 + 4);
+        const float4 wp = *reinterpret_cast<const float4*>(a.norm_weight + c * 8);
+        const float4 wq = *reinterpret_cast<const float4*>(a.norm_weight + c * 8 + 4);
+        ss += p.x * p.x + p.y * p.y + p.z * p.z + p.w * p.w + q.x * q.x + q.y * q.y + q.z * q.z + q.w * q.w;
+        *reinterpret_cast<uint4*>(dst + c * 16) =
+            make_uint4(pack2(p.x * wp.x, p.y * wp.y), pack2(p.z * wp.z, p.w * wp.w),
+                       pack2(q.x * wq.x, q.y * wq.y), pack2(q.z * wq.z, q.w * wq.w));
       }
       ss = warp_sum(ss);
       if (lane == 0) rstd_of[warp] = rsqrtf(ss / (float)a.K + a.eps);
     }
   } else {
-    for (int c = threadIdx.x; c < ROWS * chunks; c += SS_THREADS) {
+    for (int c = threadIdx.x; c < a.T * chunks; c += SS_THREADS) {
       const int row = c / chunks, cc = c - row * chunks;
       *reinterpret_cast<uint4*>(xs + (size_t)row * stride + cc * 16) =
-          row < a.T ? *reinterpret_cast<const uint4*>(a.x + (size_t)row * a.K + cc * 8) : zero4;
+          *reinterpret_cast<const uint4*>(a.x + (size_t)row * a.K + cc * 8);
     }
   }
   __syncthreads();
@@ -191,8 +189,9 @@ small_step_kernel(const SmallArgs a) {
     for (int u = 0; u < U; ++u) {
       const int kbu = kb + u * SS_WARPS;
       const bool in = kbu < nkb && kbu * 32 + t4 * 8 < a.K;
-      const uint4 lo = in ? *reinterpret_cast<const uint4*>(x_lo + kbu * 64) : zero4;
-      const uint4 hi = (!T8 && in) ? *reinterpret_cast<const uint4*>(x_hi + kbu * 64) : zero4;
+      // rows beyond the step's tokens are not in shared memory: their fragments are zero
+      const uint4 lo = (in && g < a.T) ? *reinterpret_cast<const uint4*>(x_lo + kbu * 64) : zero4;
+      const uint4 hi = (!T8 && in && g + 8 < a.T) ? *reinterpret_cast<const uint4*>(x_hi + kbu * 64) : zero4;
 #pragma unroll
       for (int j = 0; j < NT; ++j) {
         mma_bf16(acc[j], lo.x, hi.x, lo.y, hi.y, wreg[u][j].x, wreg[u][j].y);
@@ -279,16 +278,33 @@ int launch_one(dim3 grid, size_t smem, const SmallArgs& a, cudaStream_t stream) 
   return hb_check_launch();
 }
 
+int sm_count_of_current_device() {
+  static int counts[64] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (counts[dev] == 0) cudaDeviceGetAttribute(&counts[dev], cudaDevAttrMultiProcessorCount, dev);
+  return counts[dev];
+}
+
 template <int MODE, bool NORM>
 int launch_small(const SmallArgs& a, int tiles, int nt, cudaStream_t stream) {
   const bool t8 = a.T <= 8;
-  const size_t smem = (size_t)(t8 ? 8 : 16) * x_row_bytes(a.K);
+  const size_t smem = (size_t)a.T * x_row_bytes(a.K);
   if (smem > (size_t)SS_MAX_DYNAMIC_SMEM) return HB_BAD_ARGUMENT;
+  const int blocks = (tiles + nt - 1) / nt;
+  // a warp's share of K in blocks of 32; more than one request of 8 / nt blocks, in a launch
+  // that leaves room for one block per SM: the deep variant
+  const int per_warp = ((a.K + 31) / 32 + SS_WARPS - 1) / SS_WARPS;
+  const bool deep = per_warp * nt > 8 && blocks <= sm_count_of_current_device();
 #define HB_SS_CASE(NT_)                                                                                   \
   {                                                                                                       \
-    const dim3 grid((tiles + NT_ - 1) / NT_);                                                             \
-    if (t8) return launch_one<small_step_kernel<MODE, NT_, NORM, true>>(grid, smem, a, stream);           \
-    return launch_one<small_step_kernel<MODE, NT_, NORM, false>>(grid, smem, a, stream);                  \
+    const dim3 grid(blocks);                                                                              \
+    if (deep) {                                                                                           \
+      if (t8) return launch_one<small_step_kernel<MODE, NT_, NORM, true, true>>(grid, smem, a, stream);   \
+      return launch_one<small_step_kernel<MODE, NT_, NORM, false, true>>(grid, smem, a, stream);          \
+    }                                                                                                     \
+    if (t8) return launch_one<small_step_kernel<MODE, NT_, NORM, true, false>>(grid, smem, a, stream);    \
+    return launch_one<small_step_kernel<MODE, NT_, NORM, false, false>>(grid, smem, a, stream);           \
   }
   switch (nt) {
     case 1: HB_SS_CASE(1)
@@ -307,7 +323,7 @@ bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
 // Most reduction length (K) the kernels take for a step of T tokens: the activations, as
 // bfloat16 rows, must fit the block's shared memory.
 HB_EXPORT int hb_small_step_max_k(int T) {
-  const int rows = T <= 8 ? 8 : 16;
+  const int rows = T < 1 ? 1 : T;
   return ((SS_MAX_DYNAMIC_SMEM / rows - 64) / 128) * 64;
 }
 

@@ -72,10 +72,6 @@ class DecoderModel:
         return float32 logits [wanted, vocab] (None if nothing is wanted)."""
         plan = self.plan
         ctx.step_tables = {}
-        for fused in plan.fused_steps:
-            logits = fused.run(ctx, cache)
-            if logits is not NotImplemented:
-                return logits
         if plan.position is not None:
             plan.position.prepare(ctx)
         residual = plan.embedding.forward(ctx)

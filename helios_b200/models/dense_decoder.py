@@ -43,9 +43,6 @@ def build_dense_decoder_plan(cfg: DenseDecoderConfig) -> ModelPlan:
         head=OutputHead(cfg.vocab_size, cfg.hidden_size),
         tied=tied,
     )
-    # decode steps of a few requests run as one persistent kernel where it fits
-    from .dense_decode_step import DenseDecodeStep
-    plan.fused_steps.append(DenseDecodeStep(plan))
     return plan
 
 

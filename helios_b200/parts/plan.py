@@ -37,10 +37,6 @@ class ModelPlan:
     head: Optional[Part] = None
     schedule: List[Run] = field(default_factory=list)
     output: Optional[OutputStage] = None
-    # Objects with ``run(ctx, cache) -> logits | NotImplemented`` that may take a whole step
-    # over (one kernel for a decode step, say); asked in turn before the parts run one by one.
-    # The plan builder of an architecture attaches them; an empty list is always right.
-    fused_steps: List[Any] = field(default_factory=list)
     embedding_prefix: str = "model.embed_tokens."
     position_prefix: str = "model.position."
     final_norm_prefix: str = "model.norm."
