@@ -724,9 +724,14 @@ def _wave_splits(blocks: int, slots: int, most: int) -> int:
 
 def decode_splits(num_seqs: int, num_kv_heads: int, max_context: int) -> int:
     """Slices of the context per (request, KV head) of the decode attention kernel: two
-    blocks are resident per SM; a slice has at least 128 keys."""
-    return _wave_splits(max(1, num_seqs * num_kv_heads), 2 * sm_count(),
-                        max(1, min(32, max_context // 128)))
+    blocks are resident per SM; a slice has at least 128 keys.  Once the (request, KV head)
+    pairs alone fill the SMs the context is not cut: every slice costs a merge, and a fuller
+    last round does not pay for it (measured at 64 requests x 8 KV heads: 50 against 62
+    microseconds at context 1,024, 180 against 177 at 4,096)."""
+    blocks = max(1, num_seqs * num_kv_heads)
+    if blocks >= 2 * sm_count():
+        return 1
+    return _wave_splits(blocks, 2 * sm_count(), max(1, min(32, max_context // 128)))
 
 
 def attention_decode_bf16(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
