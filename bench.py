@@ -15,7 +15,8 @@ requests with prompts of 128 to 4,096 tokens under a budget of 2,048 tokens a st
 Qwen2.5-0.5B sizes (decode at batch 1, 64 and 256 from 512 to 1,024 tokens, prefill).
 ``--model`` makes one of them the headline instead; ``--workload mixed`` runs the mixed
 workload through ``LLMEngine`` and reports wall time, tokens a second, the steps by size
-and the pages' high-water mark.  Synthetic token ids, uniform from a seed.
+and the pages' high-water mark; ``--micro`` times single kernels as chains in a captured
+graph (the tables under ``profiles/``).  Synthetic token ids, uniform from a seed.
 """
 from __future__ import annotations
 
@@ -352,6 +353,101 @@ def run_mixed(engine, prompts, new_tokens, sampling_cls):
             "preemptions": engine.scheduler.stats.preemptions}
 
 
+def run_micro(args):
+    """Single kernels as they follow one another in a step: a captured graph of ``--micro-launches``
+    launches of ONE kernel over rotating copies of its weights (more bytes than L2 holds),
+    CUDA events around five replays.  Prints one JSON line per case: microseconds a launch and
+    the bytes it must read over that time over the measured copy bandwidth."""
+    import torch
+    from helios_b200.csrc import ops
+
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(0)
+    peaks = load_peaks()
+    cfg = MODELS[args.model]
+    H, I = cfg["hidden_size"], cfg["intermediate_size"]
+    nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    n = args.micro_launches
+    torch.manual_seed(args.seed)
+
+    def chain_us(fn):
+        for i in range(3):
+            fn(i)
+        torch.cuda.synchronize()
+        if n < 8:                       # a profiler's run: a few plain launches
+            for i in range(n):
+                fn(i)
+            torch.cuda.synchronize()
+            return float("nan")
+        graph, stream = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            graph.capture_begin()
+            for i in range(n):
+                fn(i)
+            graph.capture_end()
+        torch.cuda.synchronize()
+        graph.replay()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(5):
+            graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / 5 / n * 1e3
+
+    def report(case, us, nbytes, **more):
+        frac = nbytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"] if us == us else None
+        print(json.dumps(dict(micro=args.micro, model=MODEL_NAMES[args.model], case=case, us=round(us, 2),
+                              hbm_frac=None if frac is None else round(frac, 3), **more)), flush=True)
+
+    def weights(rows, cols):
+        copies = max(2, min(96, int(3e9 // (rows * cols * 2))))
+        return [(torch.randn(rows, cols, device=dev) * 0.02).bfloat16() for _ in range(copies)]
+
+    if args.micro == "gemm":
+        shapes = {"gate_up": (2 * I, H), "down": (H, I), "qkv": ((nh + 2 * nkv) * hd, H), "o": (H, nh * hd)}
+        for name, (rows, cols) in shapes.items():
+            w = weights(rows, cols)
+            for T in (8, 16, 32, 64, 128):
+                x = torch.randn(T, cols, device=dev).bfloat16()
+                if name == "gate_up":
+                    us = chain_us(lambda i: ops.linear_swiglu(x, w[i % len(w)]))
+                else:
+                    us = chain_us(lambda i: ops.linear(x, w[i % len(w)]))
+                report(name, us, rows * cols * 2, tokens=T)
+            del w
+    elif args.micro == "small_step":
+        T = args.batch
+        res, nw = torch.randn(T, H, device=dev), torch.ones(H, device=dev)
+        cases = {"o_into_residual": (H, nh * hd), "down_into_residual": (H, I), "norm_gate_up_swiglu": (2 * I, H)}
+        for name, (rows, cols) in cases.items():
+            w = weights(rows, cols)
+            x = torch.randn(T, cols, device=dev).bfloat16()
+            if name == "norm_gate_up_swiglu":
+                us = chain_us(lambda i: ops.small_norm_swiglu(res, nw, 1e-6, w[i % len(w)]))
+            else:
+                us = chain_us(lambda i: ops.small_linear_residual(res, x, w[i % len(w)]))
+            report(name, us, rows * cols * 2, tokens=T)
+            del w
+        delta = torch.randn(T, H, device=dev).bfloat16()
+        report("add_rmsnorm", chain_us(lambda i: ops.add_rmsnorm(res, delta, nw, 1e-6, torch.bfloat16)), 0, tokens=T)
+    else:
+        B, ctx, page = args.batch, args.context, 16
+        pages = B * (ctx // page)
+        k = torch.randn(pages, nkv, page, hd, device=dev).bfloat16()
+        v = torch.randn_like(k)
+        table = torch.randperm(pages, device=dev).int().reshape(B, ctx // page).contiguous()
+        pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=dev)
+        qkv = torch.randn(B, (nh + 2 * nkv) * hd, device=dev).bfloat16()
+        nbytes = B * ctx * nkv * hd * 2 * 2
+        for splits in sorted({1, 2, 4, 8, ops.decode_splits(B, nkv, ctx)}):
+            us = chain_us(lambda i: ops.attention_decode_bf16(qkv, k, v, table, pos, nh, nkv, hd, page, None,
+                                                              hd ** -0.5, splits))
+            report("attention_decode", us, nbytes, batch=B, context=ctx, splits=splits,
+                   chosen=splits == ops.decode_splits(B, nkv, ctx))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -388,12 +484,19 @@ def main():
     ap.add_argument("--max-prompt", type=int, default=4096)
     ap.add_argument("--budget", type=int, default=2048, help="tokens a step (chunked prefill)")
     ap.add_argument("--new-tokens", type=int, default=256)
+    ap.add_argument("--micro", default=None, choices=["gemm", "small_step", "attention_decode"],
+                    help="time one kind of kernel as a chain in a captured graph instead of the step "
+                         "(sizes of --model; --batch tokens or requests, --context keys)")
+    ap.add_argument("--micro-launches", type=int, default=48,
+                    help="launches in the chain; below 8 they run plainly, for a profiler")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     if args.impl == "reference":
         return run_reference(args)
+    if args.micro:
+        return run_micro(args)
     if args.warmup < 3:
         args.warmup = 3
 
