@@ -464,11 +464,29 @@ GEMM_LIBRARY_TOKEN_RANGE = (129, 512)
 #: the first time a shape is seen; token counts are rounded up to a multiple of this (on a
 #: padded copy of the rows) so that a serving run meets a handful of shapes, not hundreds.
 GEMM_LIBRARY_TOKEN_STEP = 64
+#: Weight matrices of at most this many bytes (the products of models about 1,000 wide: 2 to
+#: 17 MB) go to the library from GEMM_LIBRARY_SMALL_TOKENS[0] tokens on: a product that short
+#: is bound by the kernel's own latency, where the tensor-memory kernels (set-up, a cluster for
+#: the split reduction) lose to the library's plain ones.  Measured at Qwen2.5-0.5B sizes,
+#: microseconds a launch in a chain, this package's kernel against the library, at 24 / 64 /
+#: 256 tokens: q|k|v 5.0 / 7.2 / 10.9 against 4.0 / 3.9 / 4.2; down 6.8 / 8.5 / 29.7 against
+#: 9.4 / 8.6 / 8.8; gate|up with SwiGLU 14.4 / 18.9 / 16.5 against 8.6 / 8.7 / 12.8 (library
+#: product + gate kernel).  Up to 32 tokens this package's kernels win as a whole (a step of
+#: 32 requests: 28,300 against 25,900 tokens/s), up to 16 the fused few-token kernels run.
+#: 0 bytes turns it off.
+GEMM_LIBRARY_SMALL_WEIGHT_BYTES = 20 * 1024 * 1024
+GEMM_LIBRARY_SMALL_TOKENS = (33, 512)
 
 
 def _library_range(tokens: int) -> bool:
     lo, hi = GEMM_LIBRARY_TOKEN_RANGE
     return lo <= tokens <= hi
+
+
+def _small_weight_library(tokens: int, weight: torch.Tensor) -> bool:
+    lo, hi = GEMM_LIBRARY_SMALL_TOKENS
+    return lo <= tokens <= hi and \
+        weight.numel() * weight.element_size() <= GEMM_LIBRARY_SMALL_WEIGHT_BYTES
 
 
 def _library_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
@@ -491,7 +509,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
         return linear_f32(x, weight, bias)
     _check(x, "x", torch.bfloat16, 2)
     _check(weight, "weight", torch.bfloat16, 2)
-    if tc_gemm_supported(x, weight) and not (bias is None and _library_range(x.shape[0])):
+    T = x.shape[0]
+    to_library = (bias is None and _library_range(T)) or _small_weight_library(T, weight)
+    if tc_gemm_supported(x, weight) and not to_library:
         return linear_bf16(x, weight, bias)
     b = None if bias is None else bias.to(torch.bfloat16)
     return _library_linear(x, weight, b)
@@ -502,6 +522,8 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     product's epilogue in bfloat16, two kernels otherwise."""
     if x.dtype == torch.bfloat16 and tc_gemm_supported(x, w_gate_up):
         T = x.shape[0]
+        if _small_weight_library(T, w_gate_up):
+            return silu_mul(_library_linear(x, w_gate_up, None))
         if 64 < T <= 128:
             # with 128 tokens on the MMA N axis a stage of gate AND up tiles leaves a ring of
             # two stages; the plain product (three) and a gate kernel are faster (measured
