@@ -132,3 +132,65 @@ def test_a_long_portion_beside_decoded_tokens_at_the_benchmarks_sizes(graphs):
         core.end(f"long{rep}")
     from helios_b200.csrc import ops
     ops.check_kernel_errors()
+
+
+@pytest.mark.parametrize("n", [128, 192])
+def test_a_portion_on_either_side_of_the_library_boundary(n):
+    """Up to 128 tokens the products run on this package's decode kernel, from 129 to 512 the
+    plain ones go to the library: a request's bfloat16 numbers are not bit-equal across that
+    line, but either side must match the plain model."""
+    from helios_b200.engine.batch import StepEntry
+    from helios_b200.engine.core import EngineCore
+    from helios_b200.engine.model import DecoderModel
+
+    model = DecoderModel.from_config(CONFIG, seed=5, dtype="bfloat16")
+    weights = _export(model.plan)
+    core = EngineCore(model, page_size=16, num_pages=64, max_slots=2)
+    toks = random_tokens(CONFIG["vocab_size"], n, 79)
+    want = plain_model.forward_logits(CONFIG, weights, toks, dtype=torch.float32)
+    places = [0, 1, n // 2, n - 1]
+    got = core.step([StepEntry("p", toks, places)])
+    assert_logits_close(got, want[places], "bfloat16", f"a portion of {n} tokens")
+
+
+SMALL = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "vocab_size": 1000, "hidden_size": 896, "intermediate_size": 4864, "num_hidden_layers": 2,
+    "num_attention_heads": 14, "num_key_value_heads": 2, "head_dim": 64,
+    "max_position_embeddings": 4096, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
+    "tie_word_embeddings": True, "hidden_act": "silu",
+}
+
+
+def test_two_layers_of_the_small_models_sizes_across_the_kernel_choices():
+    """Qwen2.5-0.5B layer sizes: steps of up to 16 tokens run the fused few-token kernels, up
+    to 32 the tensor-memory products, beyond that the library's (small weight matrices); every
+    side of each line against the plain implementation, as portions and as batches of
+    requests that decode."""
+    from helios_b200.engine.batch import StepEntry
+    from helios_b200.engine.core import EngineCore
+    from helios_b200.engine.model import DecoderModel
+
+    model = DecoderModel.from_config(SMALL, seed=8, dtype="bfloat16")
+    weights = _export(model.plan)
+    core = EngineCore(model, page_size=16, num_pages=400, max_slots=40)
+    toks = random_tokens(SMALL["vocab_size"], 260, 80)
+    want = plain_model.forward_logits(SMALL, weights, toks, dtype=torch.float32)
+    lo = 0
+    for n in (16, 17, 32, 33, 64, 98):
+        got = core.step([StepEntry("p", toks[lo:lo + n], [0, n - 1])])
+        assert_logits_close(got, want[[lo, lo + n - 1]], "bfloat16", f"portion of {n} tokens at {lo}")
+        lo += n
+    core.end("p")
+    for batch in (8, 16, 17, 33):
+        prompts = [random_tokens(SMALL["vocab_size"], 9 + 3 * i, 600 + i) for i in range(batch)]
+        refs = [plain_model.forward_logits(SMALL, weights, p, dtype=torch.float32) for p in prompts]
+        core.step([StepEntry(f"b{batch}_{i}", p[:-2], []) for i, p in enumerate(prompts)])
+        for back in (2, 1):
+            got = core.step([StepEntry(f"b{batch}_{i}", [p[-back]], [0]) for i, p in enumerate(prompts)])
+            wantb = torch.stack([r[len(p) - back] for r, p in zip(refs, prompts)])
+            assert_logits_close(got, wantb, "bfloat16", f"{batch} requests decoding, {back} from the end")
+        for i in range(batch):
+            core.end(f"b{batch}_{i}")
+    from helios_b200.csrc import ops
+    ops.check_kernel_errors()

@@ -198,6 +198,10 @@ def _export(plan):
         w = m.w_qkv.float().cpu()
         out[p + "self_attn.q_proj.weight"], out[p + "self_attn.k_proj.weight"], out[p + "self_attn.v_proj.weight"] = \
             w[:q], w[q:q + kv], w[q + kv:]
+        if m.b_qkv is not None:
+            b = m.b_qkv.float().cpu()
+            out[p + "self_attn.q_proj.bias"], out[p + "self_attn.k_proj.bias"], out[p + "self_attn.v_proj.bias"] = \
+                b[:q], b[q:q + kv], b[q + kv:]
         out[p + "self_attn.o_proj.weight"] = m.w_o.float().cpu()
         gu = f.w_gate_up.float().cpu()
         out[p + "mlp.gate_proj.weight"], out[p + "mlp.up_proj.weight"] = gu[:f.inner], gu[f.inner:]
