@@ -452,14 +452,19 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
     return out
 
 
-#: Token counts between the decode kernel's range (up to 128, weights streamed once with
-#: the tokens on the MMA N axis) and the prefill kernel's (pairs of SMs on 256x256 tiles;
-#: on a par with the library above 512 tokens) leave most SMs of the two-SM kernel without a
-#: tile.  There plain products (no bias, bfloat16 out) go to the library (cuBLAS through
-#: torch), which the reference uses for every product (python/helios/exec/model.py:170-181).
-#: Fused products (bias, float32 logits, SwiGLU from 384 tokens up) always run on this
-#: package's kernel.  (0, 0) turns the library off.
-GEMM_LIBRARY_TOKEN_RANGE = (129, 512)
+#: Between the decode kernel's best range (up to 32 tokens: weights streamed once with the
+#: tokens on a narrow MMA N axis, a deep ring of weight stages) and the prefill kernel's (pairs
+#: of SMs on 256x256 tiles; on a par with the library above 512 tokens) plain products (no
+#: bias, bfloat16 out) go to the library (cuBLAS through torch), which the reference uses for
+#: every product (python/helios/exec/model.py:170-181): from 33 tokens on a stage of the decode
+#: kernel holds 8-16 KB of tokens beside its 16 KB of weights, the ring gets shallow, and the
+#: library is ahead (Llama-3.1-8B sizes at 64 tokens, microseconds in a chain: q|k|v 15.2
+#: against 11.5, O 11.1 against 10.0, down 24.3 against 24.2, gate|up + SwiGLU 54.1 against
+#: 46.9 with the gate as a kernel of its own; a decode step of 64 requests 6,300-6,460 against
+#: 6,690 tokens/s); from 129 to 512 tokens most SMs of the two-SM kernel have no tile.
+#: Products with a bias or float32 logits, SwiGLU from 384 tokens up, and everything up to 32
+#: tokens always run on this package's kernels.  (0, 0) turns the library off.
+GEMM_LIBRARY_TOKEN_RANGE = (33, 512)
 #: The library chooses its kernel per shape, which takes about a millisecond of host time
 #: the first time a shape is seen; token counts are rounded up to a multiple of this (on a
 #: padded copy of the rows) so that a serving run meets a handful of shapes, not hundreds.
@@ -524,11 +529,6 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
         T = x.shape[0]
         if _small_weight_library(T, w_gate_up):
             return silu_mul(_library_linear(x, w_gate_up, None))
-        if 64 < T <= 128:
-            # with 128 tokens on the MMA N axis a stage of gate AND up tiles leaves a ring of
-            # two stages; the plain product (three) and a gate kernel are faster (measured
-            # 62 against 74 microseconds for 2 x 14336 x 4096)
-            return silu_mul(linear_bf16(x, w_gate_up))
         if not (_library_range(T) and T < 384):
             return linear_bf16(x, w_gate_up, glu=True)
     return silu_mul(linear(x, w_gate_up))
@@ -744,16 +744,21 @@ def _wave_splits(blocks: int, slots: int, most: int) -> int:
     return max(1, min(most, slots // blocks))
 
 
-def decode_splits(num_seqs: int, num_kv_heads: int, max_context: int) -> int:
-    """Slices of the context per (request, KV head) of the decode attention kernel: two
-    blocks are resident per SM; a slice has at least 128 keys.  Once the (request, KV head)
-    pairs alone fill the SMs the context is not cut: every slice costs a merge, and a fuller
-    last round does not pay for it (measured at 64 requests x 8 KV heads: 50 against 62
-    microseconds at context 1,024, 180 against 177 at 4,096)."""
+def decode_splits(num_seqs: int, num_kv_heads: int, max_context: int, head_dim: int = 128) -> int:
+    """Slices of the context per (request, KV head) of the decode attention kernel, by a cost
+    model fitted to measurements (64 requests x 8 KV heads of 128 at contexts 1,024 and 4,096;
+    it then predicts 40 to 96 requests within 5 %): two blocks are resident per SM, the blocks
+    run in rounds of that many, and a block costs its keys plus a fixed part (set-up, merge)
+    worth about 176 keys of 128 values.  A slice has at least 128 keys."""
     blocks = max(1, num_seqs * num_kv_heads)
-    if blocks >= 2 * sm_count():
-        return 1
-    return _wave_splits(blocks, 2 * sm_count(), max(1, min(32, max_context // 128)))
+    slots = 2 * sm_count()
+    fixed = 176.0 * 128.0 / max(1, head_dim)
+    best, best_cost = 1, None
+    for s in range(1, max(1, min(32, max_context // 128)) + 1):
+        cost = -(-blocks * s // slots) * (max_context / s + fixed)
+        if best_cost is None or cost < best_cost * 0.94:      # fewer slices unless clearly better
+            best, best_cost = s, cost
+    return best
 
 
 def attention_decode_bf16(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
@@ -929,7 +934,7 @@ def attention(ctx, qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
         if ctx.decode_only and num_heads // num_kv_heads <= 16:
             splits = ctx.extras.get("decode_splits")
             if splits is None:
-                splits = decode_splits(ctx.num_seqs, num_kv_heads, ctx.max_context_len)
+                splits = decode_splits(ctx.num_seqs, num_kv_heads, ctx.max_context_len, head_dim)
             return attention_decode_bf16(qkv, k_pages, v_pages, block_table, ctx.positions,
                                          num_heads, num_kv_heads, head_dim, page_size, window,
                                          scale, splits)

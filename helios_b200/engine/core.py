@@ -34,7 +34,7 @@ class _StepGraph:
         if self.decode:
             self.ctx.extras["decode_splits"] = ops.decode_splits(
                 num_seqs, max(s.num_kv_heads for s in cache.specs) if cache.specs else 1,
-                core.graph_max_context)
+                core.graph_max_context, max(s.head_dim for s in cache.specs) if cache.specs else 128)
         self.ctx.extras["tile_provider"] = self._tiles
         self._tile_buffers = {}          # (tile, longest first) -> (pinned rows, device rows)
         self._page_size = cache.page_size
