@@ -134,9 +134,9 @@ def test_a_long_portion_beside_decoded_tokens_at_the_benchmarks_sizes(graphs):
     ops.check_kernel_errors()
 
 
-@pytest.mark.parametrize("n", [128, 192])
+@pytest.mark.parametrize("n", [32, 33, 128, 192])
 def test_a_portion_on_either_side_of_the_library_boundary(n):
-    """Up to 128 tokens the products run on this package's decode kernel, from 129 to 512 the
+    """Up to 32 tokens the products run on this package's decode kernel, from 33 to 512 the
     plain ones go to the library: a request's bfloat16 numbers are not bit-equal across that
     line, but either side must match the plain model."""
     from helios_b200.engine.batch import StepEntry
