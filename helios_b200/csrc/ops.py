@@ -730,18 +730,9 @@ def sm_count(device=None) -> int:
 
 
 def _wave_splits(blocks: int, slots: int, most: int) -> int:
-    """Number of slices per block so that blocks * slices fills ``slots`` resident blocks as
-    evenly as possible: the largest count that still fits one round, or, when even one
-    slice per block overflows it, the count with the fullest last round."""
-    if blocks >= slots:
-        best, best_eff = 1, 0.0
-        for s in range(1, most + 1):
-            total = blocks * s
-            eff = total / (-(-total // slots) * slots)
-            if eff > best_eff + 0.03:
-                best, best_eff = s, eff
-        return best
-    return max(1, min(most, slots // blocks))
+    """Number of slices per block so that blocks * slices still fits one round of ``slots``
+    resident blocks (at most ``most``)."""
+    return max(1, min(most, slots // max(1, blocks)))
 
 
 def decode_splits(num_seqs: int, num_kv_heads: int, max_context: int, head_dim: int = 128) -> int:
