@@ -167,6 +167,10 @@ def run_reference(args):
     API, ``LLMEngine(EngineConfig(...))`` / ``add_request`` / ``step``, on the same model
     sizes, batch and context.  Only the model folder (random weights in its checkpoint
     layout) is written here; nothing of helios_b200 runs."""
+    if args.workload != "decode" or args.micro:
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference arm runs the decode workload only (the default run's metric)"}))
+        return 0
     ref = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref, "helios")):
         print(json.dumps({"impl": "reference", "unavailable":
