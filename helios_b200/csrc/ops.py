@@ -83,18 +83,33 @@ def _fn(lib: str, name: str, argtypes):
     return f
 
 
-def preload(dtype: torch.dtype) -> None:
-    """Compile (in parallel) and load the libraries a model of this dtype uses, so that
-    the first step does not stop at each one in turn.  float32 never needs the bfloat16
-    tensor-core kernels and the other way round."""
+def preload(names) -> None:
+    """Compile (in parallel) and load the named libraries, so that the first step does not
+    stop at each one in turn.  A library that is not named here is still compiled and loaded
+    when an op first asks for it."""
     from .build import build_all
 
-    names = ["elementwise", "attention_generic"]
-    names += ["gemm_f32"] if dtype == torch.float32 else ["attention_bf16", "attention_tc", "attention_pair",
-                                                          "gemm_bf16", "small_step"]
+    names = sorted(set(names) | {"elementwise"})
     build_all(names)
     for n in names:
         load_library(n)
+
+
+def linear_libraries(dtype: torch.dtype, width: int = 0):
+    """Libraries the matrix products of a model of this dtype and width run on."""
+    if dtype == torch.float32:
+        return ("gemm_f32",)
+    return ("gemm_bf16", "small_step") if 0 < width <= SMALL_STEP_NARROW_WIDTH else ("gemm_bf16",)
+
+
+def attention_libraries(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int):
+    """Libraries ``attention`` may choose from at these sizes (whatever the page size)."""
+    if dtype != torch.bfloat16 or head_dim not in TILED_HEAD_DIMS:
+        return ("attention_generic",)
+    names = ["attention_bf16"]
+    if ATTENTION_TCGEN05 and tc_attention_supported(num_heads, num_kv_heads, head_dim, 16):
+        names += ["attention_tc", "attention_pair"]
+    return tuple(names)
 
 
 # ------------------------------------------------------------------ embedding

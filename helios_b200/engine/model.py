@@ -43,7 +43,7 @@ class DecoderModel:
         self.dtype = dtype
         self.device = device
         from ..csrc import ops
-        ops.preload(dtype)
+        ops.preload(name for _prefix, part in plan.named_parts() for name in part.kernel_libraries(dtype))
 
     # ------------------------------------------------------------------ construction
     @classmethod

@@ -44,6 +44,10 @@ class GQAAttention(Mixer):
     def cache_spec(self) -> PagedCacheSpec:
         return PagedCacheSpec(self.num_kv_heads, self.head_dim, self.window)
 
+    def kernel_libraries(self, dtype):
+        return (ops.linear_libraries(dtype, self.width)
+                + ops.attention_libraries(dtype, self.num_heads, self.num_kv_heads, self.head_dim))
+
     # ---------------------------------------------------------------- tensors
     def weight_specs(self) -> Dict[str, WeightSpec]:
         q, kv = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim

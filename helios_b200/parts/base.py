@@ -24,7 +24,7 @@ from these alone.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, Iterable, List, Optional, Tuple
 
 import torch
 
@@ -73,6 +73,12 @@ class Part:
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         if tensors:
             raise ValueError(f"{type(self).__name__} takes no tensors")
+
+    def kernel_libraries(self, dtype: torch.dtype) -> Iterable[str]:
+        """Names of the kernel libraries (``csrc.build.LIBRARIES``) this part's ops run on
+        at its sizes, so that a model compiles them together when it is made; a library
+        that is not named is compiled when an op first asks for it."""
+        return ()
 
 
 class Norm(Part):

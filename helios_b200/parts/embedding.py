@@ -43,6 +43,9 @@ class OutputHead(Part):
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.weight = tensors["weight"].contiguous()
 
+    def kernel_libraries(self, dtype):
+        return ops.linear_libraries(dtype)
+
     def forward(self, ctx, rows: torch.Tensor) -> torch.Tensor:
         return ops.linear_logits(rows, self.weight)
 

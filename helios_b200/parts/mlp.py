@@ -24,6 +24,9 @@ class SwiGLU(FeedForward):
             "down_proj.weight": WeightSpec((self.width, self.inner)),
         }
 
+    def kernel_libraries(self, dtype):
+        return ops.linear_libraries(dtype, self.width)
+
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.w_gate_up = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]],
                                    dim=0).contiguous()

@@ -3,7 +3,7 @@ import copy
 
 import pytest
 
-from conftest import TINY_CONFIGS, TINY_LLAMA, TINY_QWEN, TINY_WINDOW
+from conftest import TINY_CONFIGS, TINY_LLAMA, TINY_QWEN, TINY_TILED, TINY_WINDOW
 from helios_b200.config import (ConfigError, DenseDecoderConfig, known_architectures,
                                 register_architecture, resolve_architecture,
                                 unregister_architecture)
@@ -128,3 +128,25 @@ def test_plan_takes_every_size_from_the_configuration():
             assert m.scale == pytest.approx(cfg.head_dim ** -0.5)
             assert block.mixer_norm.eps == cfg.rms_norm_eps
             assert block.ffn.inner == cfg.intermediate_size
+
+
+def test_a_plan_names_the_kernel_libraries_its_sizes_need():
+    """What a model compiles when it is made follows its parts' sizes and the dtype: heads of
+    16 have no tiled attention kernel, heads of 32 no tcgen05 one, float32 neither; a wide
+    model has no use for the fused few-token kernels."""
+    import torch
+    from helios_b200.csrc.build import LIBRARIES
+    from helios_b200.models import build_dense_decoder_plan
+
+    def libraries(raw, dtype):
+        plan = build_dense_decoder_plan(DenseDecoderConfig.from_hf(raw))
+        return {n for _p, part in plan.named_parts() for n in part.kernel_libraries(dtype)}
+
+    bf16, f32 = torch.bfloat16, torch.float32
+    assert libraries(TINY_LLAMA, bf16) == {"gemm_bf16", "small_step", "attention_generic"}
+    assert libraries(TINY_TILED, bf16) == {"gemm_bf16", "small_step", "attention_bf16"}
+    assert libraries(TINY_TILED, f32) == {"gemm_f32", "attention_generic"}
+    wide = dict(TINY_LLAMA, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8)
+    assert libraries(wide, bf16) == {"gemm_bf16", "attention_bf16", "attention_tc", "attention_pair"}
+    for raw in TINY_CONFIGS.values():
+        assert libraries(raw, bf16) | libraries(raw, f32) <= set(LIBRARIES)
