@@ -14,6 +14,11 @@
 // Epilogues: + bias, bfloat16 or float32 out; or SwiGLU, where the block accumulates the
 // gate tile and the up tile of the same feature range side by side and writes
 // silu(gate) * up.
+// Two more for steps of few tokens (swapped orientation), which together take the RMSNorm
+// launches out of a decode step: a product can ADD its result into the float32 residual
+// stream and leave, for the norm that follows, bfloat16(residual * norm weight) and per-token
+// partial sums of squares; and a product whose input was left that way multiplies its
+// accumulators by the token's 1 / rms (from those partial sums) before bias or SwiGLU.
 //
 // One thread issues TMA, one issues MMA, four warps run the epilogue.  Every wait on an
 // mbarrier is bounded: when it runs out the block raises an error word in global
@@ -42,7 +47,16 @@ struct GemmArgs {
   int k_splits;
   int cluster_reduce;   // the K slices of a tile form a thread-block cluster and add their
                         // partial sums through distributed shared memory (no scratch)
+  // swapped orientation only:
+  float* residual = nullptr;           // [T, N] float32: residual += result (+ bias); then, with
+  const float* norm_weight = nullptr;  // a norm weight [N], out = bfloat16(residual * weight) and
+  float* sumsq_out = nullptr;          // [T, 8 * feature tiles] partial sums of residual^2
+  const float* sumsq_in = nullptr;     // [T, slots_in]: the input rows lack the factor
+  int slots_in = 0;                    //   rsqrt(sum(slots) / width + eps), applied to the
+  float width = 1.f, eps = 0.f;        //   accumulators here
 };
+
+constexpr int SUMSQ_SLOTS = 8;   // partial sums a feature tile leaves per token (K slices or warps)
 
 constexpr uint32_t pow2_cols(int n) { return n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : n <= 256 ? 256 : 512; }
 
@@ -60,7 +74,8 @@ struct Config {
   static constexpr int MIN_BLOCKS = SWAP ? 2 : 1;
   static constexpr int ACC_COLS = BN * A_TILES;            // float32 columns of tensor memory in use
   static constexpr uint32_t TMEM_COLS = pow2_cols(ACC_COLS);
-  static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
+  static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment */ +
+                                 256 /* barriers */ + (SWAP ? BN * 4 : 0) /* token factors */;
 };
 
 // out feature / token of accumulator element (row r of the A-side tile, column c)
@@ -77,6 +92,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * Cfg::STAGES + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* last_flag = const_cast<int*>(abort_flag) + 1;
+  float* col_scale = reinterpret_cast<float*>(last_flag + 3);     // [BN], one factor per token column
 
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -200,6 +216,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     pdl_wait();                                    // nothing is written before the kernel before is done
     const int quarter = warp & 3;                  // the 32 lanes of tensor memory this warp may read
     const int r = quarter * 32 + lane;             // row of the A-side tile
+    const bool scaled = SWAP && args.sumsq_in != nullptr;
+    if (scaled) {
+      // 1 / rms of this tile's tokens, while the products run: a warp per column adds the
+      // partial sums in a fixed order
+      for (int c = quarter; c < BN; c += 4) {
+        const int t = tile_b * BN + c;
+        float ss = 0.f;
+        if (t < args.T)
+          for (int j = lane; j < args.slots_in; j += 32) ss += __ldcg(args.sumsq_in + (size_t)t * args.slots_in + j);
+        ss = warp_sum(ss);
+        if (lane == 0) col_scale[c] = t < args.T ? rsqrtf(ss / args.width + args.eps) : 0.f;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
     bool ok = true;
     if (n_kb > 0) ok = mbar_wait(acc_bar, 0, abort_flag, args.error, 3);
     if (*abort_flag) ok = false;
@@ -281,6 +311,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           float g[16], u[16];
           load_chunk(c, g);
           load_chunk(HALF + c, u);
+          if (scaled) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) { g[j] *= col_scale[c + j]; u[j] *= col_scale[c + j]; }
+          }
           float val[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) val[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
@@ -309,9 +343,35 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         for (int c = 0; c < BN; c += 16) {
           float v[16];
           load_chunk(c, v);
-          if (SWAP) {
+          if (SWAP && args.residual != nullptr) {
+            // into the residual stream; a warp holds 32 features of every token of the tile
+            const int n = tile_a * BM + r;
+            const int slots = (int)gridDim.x * SUMSQ_SLOTS;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) store(tile_b * BN + c + j, tile_a * BM + r, v[j]);
+            for (int j = 0; j < 16; ++j) {
+              const int t = tile_b * BN + c + j;
+              if (t >= args.T) break;                         // the same for the whole warp
+              float sq = 0.f;
+              if (n < args.N) {
+                float* p = args.residual + (size_t)t * args.N + n;
+                const float nv = *p + v[j] + (args.bias ? args.bias[n] : 0.f);
+                *p = nv;
+                if (args.norm_weight) {
+                  reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)t * args.ldo + n] =
+                      __float2bfloat16_rn(nv * args.norm_weight[n]);
+                  sq = nv * nv;
+                }
+              }
+              if (args.norm_weight) {
+                sq = warp_sum(sq);
+                float* dst = args.sumsq_out + (size_t)t * slots + tile_a * SUMSQ_SLOTS;
+                if (lane == 0) { dst[quarter] = sq; dst[4 + quarter] = 0.f; }
+              }
+            }
+          } else if (SWAP) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              store(tile_b * BN + c + j, tile_a * BM + r, scaled ? v[j] * col_scale[c + j] : v[j]);
           } else {
             const int t = tile_a * BM + r, n0 = tile_b * BN + c;
             if (!args.out_f32 && t < args.T && n0 + 16 <= args.N && (args.ldo & 7) == 0) {
@@ -343,7 +403,48 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     // partial sums of all slices (in slice order) from its peers' shared memory, and writes
     // the result; the second barrier keeps every block's memory alive until all have read.
     cluster_sync_all();
-    if (warp >= 2 && !*abort_flag) {
+    if (SWAP && args.residual != nullptr) {
+      // Into the residual stream: this block adds up rows [r0, r1) of the tile's 128 features
+      // for every token, a warp per token column, and leaves one partial sum of squares.
+      if (warp >= 2 && !*abort_flag) {
+        const int S = args.k_splits;
+        const int r0 = split * BM / S, r1 = (split + 1) * BM / S;
+        const int slots = (int)gridDim.x * SUMSQ_SLOTS;
+        for (int c = warp - 2; c < BN; c += 4) {
+          const int t = tile_b * BN + c;
+          if (t >= args.T) break;
+          float sq = 0.f;
+          for (int rr = r0 + lane; rr < r1; rr += 32) {
+            float pv[8];
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp)
+              pv[sp] = sp < S ? ld_peer_smem(base + (uint32_t)(c * BM + rr) * 4u, sp) : 0.f;
+            float val = 0.f;
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp) val += pv[sp];
+            const int n = tile_a * BM + rr;
+            if (n < args.N) {
+              float* p = args.residual + (size_t)t * args.N + n;
+              const float nv = *p + val + (args.bias ? args.bias[n] : 0.f);
+              *p = nv;
+              if (args.norm_weight) {
+                reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)t * args.ldo + n] =
+                    __float2bfloat16_rn(nv * args.norm_weight[n]);
+                sq += nv * nv;
+              }
+            }
+          }
+          if (args.norm_weight) {
+            sq = warp_sum(sq);
+            float* dst = args.sumsq_out + (size_t)t * slots + tile_a * SUMSQ_SLOTS;
+            if (lane == 0) {
+              dst[split] = sq;
+              if (split == 0) for (int sp = S; sp < SUMSQ_SLOTS; ++sp) dst[sp] = 0.f;
+            }
+          }
+        }
+      }
+    } else if (warp >= 2 && !*abort_flag) {
       constexpr int OUT_COLS = (EPI == EPI_GLU && !SWAP) ? BN / 2 : BN;   // columns of the result tile
       constexpr int GLU_SHIFT = (EPI == EPI_GLU) ? (SWAP ? BN : BN / 2) : 0;
       const uint32_t part_addr = base;
@@ -364,6 +465,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         float g = 0.f, u = 0.f;
 #pragma unroll
         for (int sp = 0; sp < 8; ++sp) { g += gv[sp]; u += uv[sp]; }
+        if (SWAP && args.sumsq_in != nullptr) { g *= col_scale[c]; u *= col_scale[c]; }
         float val = g;
         if (EPI == EPI_GLU) val = g / (1.f + __expf(-g)) * u;
         int t, n;
@@ -752,10 +854,11 @@ HB_EXPORT long long hb_gemm_bf16_scratch_floats(int T, int N, int swap_bn, int g
 //   that many tokens per tile.  With 1 < k_splits <= 8 and `cluster` set, the slices of a tile
 //   run as one thread-block cluster and add up through distributed shared memory; else the
 //   partial sums go through `scratch` with one ticket per tile.
-HB_EXPORT int hb_gemm_bf16(void* out, const void* x, const void* w, const float* bias, float* scratch,
-                           int* tickets, int* error, int T, int N, int K, int ldx, int ldw, int ldo,
-                           int w_rows, int glu, int glu_offset, int out_f32, int swap_bn, int k_splits,
-                           int cluster, cudaStream_t stream) {
+static int gemm_bf16_call(void* out, const void* x, const void* w, const float* bias, float* scratch,
+                          int* tickets, int* error, int T, int N, int K, int ldx, int ldw, int ldo,
+                          int w_rows, int glu, int glu_offset, int out_f32, int swap_bn, int k_splits,
+                          int cluster, float* residual, const float* norm_weight, float* sumsq_out,
+                          const float* sumsq_in, int slots_in, float eps, cudaStream_t stream) {
   if (T <= 0 || N <= 0) return HB_OK;
   if (K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || k_splits < 1) return HB_BAD_ARGUMENT;
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return HB_BAD_ARGUMENT;
@@ -763,11 +866,21 @@ HB_EXPORT int hb_gemm_bf16(void* out, const void* x, const void* w, const float*
   if (k_splits > 1 && !clustered && (scratch == nullptr || tickets == nullptr)) return HB_BAD_ARGUMENT;
   if (k_splits > (K + BK - 1) / BK) return HB_BAD_ARGUMENT;
   if (error == nullptr) return HB_BAD_ARGUMENT;
+  if (residual != nullptr || sumsq_in != nullptr) {
+    // the epilogues of few-token steps: swapped orientation, one token tile
+    if (swap_bn == 0 || T > swap_bn) return HB_BAD_ARGUMENT;
+    if (residual != nullptr && (glu || out_f32)) return HB_BAD_ARGUMENT;
+    if (norm_weight != nullptr && (residual == nullptr || out == nullptr || sumsq_out == nullptr))
+      return HB_BAD_ARGUMENT;
+    if (sumsq_in != nullptr && slots_in <= 0) return HB_BAD_ARGUMENT;
+  }
   GemmArgs a;
   a.out = out; a.bias = bias; a.scratch = scratch; a.tickets = tickets; a.error = error;
   a.T = T; a.N = N; a.K = K; a.ldo = ldo; a.glu_offset = glu_offset; a.out_f32 = out_f32;
   a.k_splits = k_splits;
   a.cluster_reduce = clustered ? 1 : 0;
+  a.residual = residual; a.norm_weight = norm_weight; a.sumsq_out = sumsq_out;
+  a.sumsq_in = sumsq_in; a.slots_in = slots_in; a.width = (float)K; a.eps = eps;
 #define HB_GEMM_CASE(BN_, SWAP_)                                                              \
   return glu ? launch<BN_, SWAP_, EPI_GLU>(x, w, a, w_rows, ldx, ldw, stream)                 \
              : launch<BN_, SWAP_, EPI_STORE>(x, w, a, w_rows, ldx, ldw, stream)
@@ -783,5 +896,32 @@ HB_EXPORT int hb_gemm_bf16(void* out, const void* x, const void* w, const float*
     default: return HB_BAD_ARGUMENT;
   }
 #undef HB_GEMM_CASE
+}
+
+HB_EXPORT int hb_gemm_bf16(void* out, const void* x, const void* w, const float* bias, float* scratch,
+                           int* tickets, int* error, int T, int N, int K, int ldx, int ldw, int ldo,
+                           int w_rows, int glu, int glu_offset, int out_f32, int swap_bn, int k_splits,
+                           int cluster, cudaStream_t stream) {
+  return gemm_bf16_call(out, x, w, bias, scratch, tickets, error, T, N, K, ldx, ldw, ldo, w_rows, glu,
+                        glu_offset, out_f32, swap_bn, k_splits, cluster, nullptr, nullptr, nullptr,
+                        nullptr, 0, 0.f, stream);
+}
+
+// The same product with the epilogues of few-token steps (swapped orientation, T <= swap_bn):
+//   residual [T, N] float32: residual += x w^T (+ bias) instead of writing the product; with
+//   norm_weight [N] also out[T, ldo] = bfloat16(residual * norm_weight) and
+//   sumsq_out[T, 8 * ceil(N / 128)] = partial sums of residual^2 over the features, so that
+//   rsqrt(sum / N + eps) is the factor that `out` still lacks to be the RMS norm;
+//   sumsq_in [T, slots_in]: x lacks such a factor over ITS width K; every accumulator of token
+//   t is multiplied by rsqrt(sum(sumsq_in[t]) / K + eps) before bias or SwiGLU.
+HB_EXPORT int hb_gemm_bf16_fused(void* out, const void* x, const void* w, const float* bias, float* scratch,
+                                 int* tickets, int* error, int T, int N, int K, int ldx, int ldw, int ldo,
+                                 int w_rows, int glu, int glu_offset, int out_f32, int swap_bn,
+                                 int k_splits, int cluster, float* residual, const float* norm_weight,
+                                 float* sumsq_out, const float* sumsq_in, int slots_in, float eps,
+                                 cudaStream_t stream) {
+  return gemm_bf16_call(out, x, w, bias, scratch, tickets, error, T, N, K, ldx, ldw, ldo, w_rows, glu,
+                        glu_offset, out_f32, swap_bn, k_splits, cluster, residual, norm_weight, sumsq_out,
+                        sumsq_in, slots_in, eps, stream);
 }
 #endif  // HB_GEMM_BF16_NO_EXPORTS

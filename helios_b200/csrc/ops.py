@@ -413,12 +413,23 @@ def tc_gemm_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
 
 def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
                 glu: bool = False, out_dtype: torch.dtype = torch.bfloat16,
-                plan=None, cluster: Optional[bool] = None, two_sm: Optional[bool] = None) -> torch.Tensor:
+                plan=None, cluster: Optional[bool] = None, two_sm: Optional[bool] = None,
+                sumsq: Optional[torch.Tensor] = None, eps: float = 0.0,
+                residual: Optional[torch.Tensor] = None, norm_weight: Optional[torch.Tensor] = None,
+                norm_out: Optional[tuple] = None):
     """y = x W^T (+ bias) on tcgen05 tensor cores; bfloat16 operands, float32 accumulate.
 
     With ``glu`` the weight is [gate rows; up rows] ([2 I, K]) and the result is
     silu(x gate^T) * (x up^T), [T, I].  ``out_dtype`` bfloat16 or float32.  K must be a
-    multiple of 8 (TMA rows are 16-byte aligned); any T and N."""
+    multiple of 8 (TMA rows are 16-byte aligned); any T and N.
+
+    Steps of at most DEFERRED_NORM_TOKENS tokens have two more epilogues.  ``sumsq``
+    (float32 [T, slots]): ``x`` is residual * norm weight without the token's 1 / rms;
+    the accumulators are multiplied by rsqrt(sum(sumsq[t]) / K + eps) before bias or SwiGLU.
+    ``residual`` (float32 [T, N]): the product is added into it and None is returned, or,
+    with ``norm_weight`` (float32 [N]), the pair (bfloat16(residual * norm_weight),
+    partial sums of squares [T, slots]) that a product with ``sumsq`` takes; ``norm_out``
+    gives that pair's tensors to write into."""
     _check(x, "x", torch.bfloat16, 2)
     _check(weight, "weight", torch.bfloat16, 2)
     T, K = x.shape
@@ -438,10 +449,44 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
             raise KernelError(f"bias has {bias.numel()} entries for {N} outputs")
     if out_dtype not in (torch.bfloat16, torch.float32):
         raise KernelError(f"out_dtype {out_dtype} is not supported")
-    out = torch.empty((T, N), dtype=out_dtype, device=x.device)
+    few = sumsq is not None or residual is not None
+    if few and T > DEFERRED_NORM_TOKENS:
+        raise KernelError(f"the residual and 1 / rms epilogues take at most {DEFERRED_NORM_TOKENS} tokens, got {T}")
+    if sumsq is not None:
+        _check(sumsq, "sumsq", torch.float32, 2)
+        if sumsq.shape[0] != T or not sumsq.is_contiguous():
+            raise KernelError(f"sumsq has shape {tuple(sumsq.shape)} for {T} tokens")
+    sumsq_out = None
+    if residual is not None:
+        _check(residual, "residual", torch.float32, 2)
+        if tuple(residual.shape) != (T, N) or not residual.is_contiguous():
+            raise KernelError(f"residual has shape {tuple(residual.shape)}, expected ({T}, {N}) contiguous")
+        if glu or out_dtype != torch.bfloat16:
+            raise KernelError("a product into the residual is a plain bfloat16 one")
+        out = None
+        if norm_weight is not None:
+            _check(norm_weight, "norm_weight", torch.float32, 1)
+            if norm_weight.numel() != N:
+                raise KernelError(f"norm weight has {norm_weight.numel()} entries for width {N}")
+            slots = 8 * -(-N // 128)
+            if norm_out is not None:
+                out, sumsq_out = norm_out
+                _check(out, "norm_out[0]", torch.bfloat16, 2)
+                _check(sumsq_out, "norm_out[1]", torch.float32, 2)
+                if tuple(out.shape) != (T, N) or tuple(sumsq_out.shape) != (T, slots):
+                    raise KernelError("norm_out tensors have the wrong shapes")
+            else:
+                out = torch.empty((T, N), dtype=torch.bfloat16, device=x.device)
+                sumsq_out = torch.empty((T, slots), dtype=torch.float32, device=x.device)
+    elif norm_weight is not None:
+        raise KernelError("norm_weight goes with residual")
+    else:
+        out = torch.empty((T, N), dtype=out_dtype, device=x.device)
     if T == 0:
-        return out
+        return out if residual is None else ((out, sumsq_out) if norm_weight is not None else None)
     bn, splits = plan if plan is not None else gemm_plan(T, N, K, glu)
+    if few and (bn == 0 or T > bn):
+        raise KernelError("the residual and 1 / rms epilogues need the swapped orientation and one token tile")
     if cluster is None:
         cluster = GEMM_CLUSTER_REDUCE
     # slices of a tile as a cluster: at most 8, and the partial sums must fit the stages
@@ -458,13 +503,36 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
         if need > scratch.numel() or tiles > tickets.numel():
             raise KernelError(f"split reduction needs {need} scratch floats and {tiles} tickets; "
                               f"the work space holds {scratch.numel()} and {tickets.numel()}")
-    f = _fn("gemm_bf16", "hb_gemm_bf16",
-            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
-    _run(f(_p(out), _p(x), _p(weight), _p(bias), _p(scratch), _p(tickets), _p(err), T, N, K, K, K, N,
-           rows, int(glu), N if glu else 0, 1 if out_dtype == torch.float32 else 0, bn, splits,
-           cluster_arg, _stream()), "gemm_bf16")
+    common = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int]
+    args = (_p(out), _p(x), _p(weight), _p(bias), _p(scratch), _p(tickets), _p(err), T, N, K, K, K, N,
+            rows, int(glu), N if glu else 0, 1 if out_dtype == torch.float32 else 0, bn, splits, cluster_arg)
+    if few:
+        f = _fn("gemm_bf16", "hb_gemm_bf16_fused",
+                common + [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p])
+        _run(f(*args, _p(residual), _p(norm_weight), _p(sumsq_out), _p(sumsq),
+               0 if sumsq is None else sumsq.shape[1], float(eps), _stream()), "gemm_bf16_fused")
+        if residual is not None:
+            return (out, sumsq_out) if norm_weight is not None else None
+        return out
+    f = _fn("gemm_bf16", "hb_gemm_bf16", common + [c_void_p])
+    _run(f(*args, _stream()), "gemm_bf16")
     return out
+
+
+#: Steps of at most this many tokens can run a layer's RMS norms inside the products around
+#: them (see ``linear_bf16``): the products of such a step run swapped, tokens on one narrow
+#: tile, on this package's kernel.
+DEFERRED_NORM_TOKENS = 32
+
+
+def deferred_norm_fits(tokens: int, *weights: torch.Tensor) -> bool:
+    """Whether a step of ``tokens`` tokens runs these products with the residual and
+    1 / rms epilogues: few tokens, and shapes the tensor-core kernel takes."""
+    if not 0 < tokens <= DEFERRED_NORM_TOKENS:
+        return False
+    return all(w.dtype == torch.bfloat16 and w.dim() == 2 and w.shape[1] % 8 == 0 and w.is_contiguous()
+               and w.data_ptr() % 16 == 0 for w in weights)
 
 
 #: Between the decode kernel's best range (up to 32 tokens: weights streamed once with the

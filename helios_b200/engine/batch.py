@@ -63,6 +63,8 @@ class StepContext:
     step_tables: dict = field(default_factory=dict)
     # per-request state of the parts of the block that runs now: id(part) -> [slots, ...]
     block_states: dict = field(default_factory=dict)
+    # the norm the block after the running one applies first (None: unknown, or the end)
+    norm_after_block: object = None
     extras: dict = field(default_factory=dict)
 
     def part_state(self, part) -> Optional[torch.Tensor]:

@@ -78,11 +78,17 @@ class DecoderModel:
         if plan.position is not None:
             residual = plan.position.embed(ctx, residual)
         delta = None
+        runs = len(plan.schedule)
         for entry, run in enumerate(plan.schedule):
             ctx.block_states = cache.part_states(entry)
+            # the norm that meets the residual stream first after this block, if the next
+            # block says so: a part may prepare it while it adds its own output
+            ctx.norm_after_block = (plan.layers[plan.schedule[entry + 1].layer].first_norm
+                                    if entry + 1 < runs else None)
             residual, delta = plan.layers[run.layer].forward(
                 ctx, residual, delta, cache.layer_cache(entry), cache.layer_state(entry))
         ctx.block_states = {}
+        ctx.norm_after_block = None
         if ctx.num_wanted == 0:
             return None
         return plan.output.forward(ctx, residual, delta)

@@ -14,7 +14,7 @@ from typing import Dict, Optional
 import torch
 
 from ..csrc import ops
-from .base import LayerCache, Mixer, PagedCacheSpec, WeightSpec, register_part
+from .base import DeferredNorm, LayerCache, Mixer, PagedCacheSpec, WeightSpec, register_part
 from .norm import RMSNorm
 
 
@@ -79,13 +79,17 @@ class GQAAttention(Mixer):
             return self.position.tables(ctx)
         return ctx.rotary_cos, ctx.rotary_sin
 
-    def forward_from_residual(self, ctx, residual: torch.Tensor, norm, cache: LayerCache, state=None) -> bool:
-        """Steps of very few tokens: norm + projection + rotation + cache write in one launch,
-        attention, output projection + residual add in one launch."""
-        if ctx.act_dtype != torch.bfloat16 or type(norm) is not RMSNorm or cache is None \
-                or self.head_dim % 8 \
-                or not ops.small_step_fits(ctx.num_tokens, self.width, self.width, self.num_heads * self.head_dim):
+    def forward_from_residual(self, ctx, residual: torch.Tensor, norm, cache: LayerCache, state=None,
+                              pre=None, then=None):
+        """Steps of few tokens.  Narrow models: norm + projection + rotation + cache write in
+        one launch, attention, output projection + residual add in one launch.  Otherwise the
+        norm launches go: q|k|v takes the 1 / rms of ``pre`` as a factor on its accumulators,
+        and the output projection adds into the residual and leaves ``then`` all but done."""
+        if ctx.act_dtype != torch.bfloat16 or type(norm) is not RMSNorm or cache is None:
             return False
+        if not ops.small_step_fits(ctx.num_tokens, self.width, self.width, self.num_heads * self.head_dim) \
+                or self.head_dim % 8:
+            return self._forward_deferred_norms(ctx, residual, norm, cache, pre, then)
         cos, sin = self._rotary_tables(ctx)
         if cos is None or cos.shape[1] * 2 != self.head_dim:
             return False
@@ -99,17 +103,32 @@ class GQAAttention(Mixer):
         ops.small_linear_residual(residual, attn, self.w_o)
         return True
 
-    def forward(self, ctx, x: torch.Tensor, cache: LayerCache, state=None) -> torch.Tensor:
-        qkv = ops.linear(x, self.w_qkv, self.b_qkv)
+    def _forward_deferred_norms(self, ctx, residual, norm, cache, pre, then):
+        if not ops.deferred_norm_fits(ctx.num_tokens, self.w_qkv, self.w_o):
+            return False
+        if pre is not None:
+            qkv = ops.linear_bf16(pre.scaled, self.w_qkv, self.b_qkv, sumsq=pre.sumsq, eps=norm.eps)
+        else:
+            qkv = ops.linear_bf16(norm.add_forward(residual, None, ctx.act_dtype), self.w_qkv, self.b_qkv)
+        attn = self._attend(ctx, qkv, cache)
+        if type(then) is RMSNorm:
+            scaled, sumsq = ops.linear_bf16(attn, self.w_o, residual=residual, norm_weight=then.weight)
+            return DeferredNorm(then, scaled, sumsq)
+        ops.linear_bf16(attn, self.w_o, residual=residual)
+        return True
+
+    def _attend(self, ctx, qkv: torch.Tensor, cache: LayerCache) -> torch.Tensor:
         table = ctx.block_tables[cache.group]
         cos, sin = self._rotary_tables(ctx)
         ops.rope_kv_write(qkv, cos, sin, ctx.positions, ctx.seq_of_token, table,
                           cache.k_pages, cache.v_pages, self.num_heads, self.num_kv_heads,
                           self.head_dim, cache.page_size, write_cache=cache.write)
-        attn = ops.attention(ctx, qkv, cache.k_pages, cache.v_pages, table, self.num_heads,
+        return ops.attention(ctx, qkv, cache.k_pages, cache.v_pages, table, self.num_heads,
                              self.num_kv_heads, self.head_dim, cache.page_size, self.window,
                              self.scale)
-        return ops.linear(attn, self.w_o)
+
+    def forward(self, ctx, x: torch.Tensor, cache: LayerCache, state=None) -> torch.Tensor:
+        return ops.linear(self._attend(ctx, ops.linear(x, self.w_qkv, self.b_qkv), cache), self.w_o)
 
 
 register_part("mixer", "gqa_attention", GQAAttention)

@@ -141,6 +141,17 @@ class OutputStage(Part):
         raise NotImplementedError
 
 
+@dataclass
+class DeferredNorm:
+    """An RMS norm of the residual stream that the part BEFORE the norm has all but done
+    while it added its output: the rows times the norm weight, and partial sums of their
+    squares, from which the part AFTER the norm takes each row's 1 / rms as a factor on its
+    first product.  Handed from one ``forward_from_residual`` to the next."""
+    norm: "Norm"                  # the norm it stands for (its weight and eps went in)
+    scaled: torch.Tensor          # compute dtype [T, width]: residual * norm weight
+    sumsq: torch.Tensor           # float32 [T, slots]: they add up to sum(residual ** 2) per row
+
+
 class Mixer(Part):
     def cache_spec(self) -> Optional[PagedCacheSpec]:
         return None
@@ -156,11 +167,16 @@ class Mixer(Part):
         raise NotImplementedError
 
     def forward_from_residual(self, ctx, residual: torch.Tensor, norm: "Norm",
-                              cache: Optional[LayerCache], state: Optional[torch.Tensor]) -> bool:
+                              cache: Optional[LayerCache], state: Optional[torch.Tensor],
+                              pre: Optional[DeferredNorm] = None, then: Optional["Norm"] = None):
         """Optional fusion with the norm before and the add after: apply ``norm`` to the
         float32 residual stream (to which nothing is pending), run, and ADD the output to
         ``residual`` in place.  Return False, having done nothing, where the part has no such
-        path for this step; the block then norms, calls ``forward`` and adds as usual."""
+        path for this step; the block then norms, calls ``forward`` and adds as usual.
+
+        ``pre``: ``norm`` of this very residual, all but done by the part before (it may be
+        ignored).  ``then``: the norm that will be applied to the residual next, if the block
+        knows it; a part that can may return a ``DeferredNorm`` for it instead of True."""
         return False
 
 
@@ -173,8 +189,10 @@ class FeedForward(Part):
     def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
-    def forward_from_residual(self, ctx, residual: torch.Tensor, norm: "Norm") -> bool:
-        """As ``Mixer.forward_from_residual``: norm, run and add in place, or return False."""
+    def forward_from_residual(self, ctx, residual: torch.Tensor, norm: "Norm",
+                              pre: Optional[DeferredNorm] = None, then: Optional["Norm"] = None):
+        """As ``Mixer.forward_from_residual``: norm, run and add in place (True, or a
+        ``DeferredNorm`` for ``then``), or return False."""
         return False
 
 
@@ -187,6 +205,13 @@ class Block:
 
     @property
     def mixer(self) -> Optional[Mixer]:
+        return None
+
+    @property
+    def first_norm(self) -> Optional["Norm"]:
+        """The norm this block applies to the residual stream before anything else, if it
+        starts that way and accepts a ``DeferredNorm`` for it in place of ``delta``; the
+        model tells the block before (``ctx.norm_after_block``)."""
         return None
 
     def state_specs(self) -> List[Tuple[Part, StateSpec]]:
@@ -204,7 +229,8 @@ class Block:
     def forward(self, ctx, residual: torch.Tensor, delta: Optional[torch.Tensor],
                 cache: Optional[LayerCache], state: Optional[torch.Tensor]):
         """Takes the float32 residual stream and the not-yet-added output of the
-        block before (or None); returns the pair for the next block."""
+        block before (or None; or, for a block with ``first_norm``, a ``DeferredNorm`` of
+        it); returns the pair for the next block."""
         raise NotImplementedError
 
 

@@ -10,7 +10,7 @@ from typing import List, Optional, Tuple
 
 import torch
 
-from .base import Block, FeedForward, LayerCache, Mixer, Norm, Part, register_part
+from .base import Block, DeferredNorm, FeedForward, LayerCache, Mixer, Norm, Part, register_part
 
 
 class PreNormBlock(Block):
@@ -34,21 +34,34 @@ class PreNormBlock(Block):
     def graph_safe(self) -> bool:
         return all(p.graph_safe for _, p in self.named_parts())
 
-    def forward(self, ctx, residual: torch.Tensor, delta: Optional[torch.Tensor],
-                cache: Optional[LayerCache], state: Optional[torch.Tensor]):
-        # a part may take the norm before it and the add after it into its own kernels (steps
-        # of very few tokens); that needs a residual stream to which nothing is pending
-        if delta is None and self._mixer.forward_from_residual(ctx, residual, self.mixer_norm, cache, state):
-            pass
-        else:
+    @property
+    def first_norm(self) -> Norm:
+        return self.mixer_norm
+
+    def forward(self, ctx, residual: torch.Tensor, delta, cache: Optional[LayerCache],
+                state: Optional[torch.Tensor]):
+        # A part may take the norm before it and the add after it into its own kernels (steps
+        # of few tokens); that needs a residual stream to which nothing is pending.  Such a
+        # part may also leave the NEXT norm all but done (a DeferredNorm) for the part after it.
+        pre = None
+        if isinstance(delta, DeferredNorm):
+            pre, delta = (delta if delta.norm is self.mixer_norm else None), None
+        done = False
+        if delta is None:
+            done = self._mixer.forward_from_residual(ctx, residual, self.mixer_norm, cache, state,
+                                                     pre=pre, then=self.ffn_norm)
+        if done is False:
             x = self.mixer_norm.add_forward(residual, delta, ctx.act_dtype)
             delta = self._mixer.forward(ctx, x, cache, state)
-        if delta is None and self.ffn.forward_from_residual(ctx, residual, self.ffn_norm):
-            pass
         else:
-            x = self.ffn_norm.add_forward(residual, delta, ctx.act_dtype)
-            delta = self.ffn.forward(ctx, x)
-        return residual, delta
+            delta = None
+            done = self.ffn.forward_from_residual(ctx, residual, self.ffn_norm,
+                                                  pre=done if isinstance(done, DeferredNorm) else None,
+                                                  then=ctx.norm_after_block)
+            if done is not False:
+                return residual, (done if isinstance(done, DeferredNorm) else None)
+        x = self.ffn_norm.add_forward(residual, delta, ctx.act_dtype)
+        return residual, self.ffn.forward(ctx, x)
 
 
 register_part("block", "pre_norm", PreNormBlock)

@@ -7,7 +7,7 @@ from typing import Dict
 import torch
 
 from ..csrc import ops
-from .base import FeedForward, WeightSpec, register_part
+from .base import DeferredNorm, FeedForward, WeightSpec, register_part
 from .norm import RMSNorm
 
 
@@ -35,14 +35,27 @@ class SwiGLU(FeedForward):
     def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
         return ops.linear(ops.linear_swiglu(x, self.w_gate_up), self.w_down)
 
-    def forward_from_residual(self, ctx, residual: torch.Tensor, norm) -> bool:
-        """Steps of very few tokens: norm + gate|up + SwiGLU in one launch, down + residual
-        add in another."""
-        if ctx.act_dtype != torch.bfloat16 or type(norm) is not RMSNorm \
-                or not ops.small_step_fits(ctx.num_tokens, self.width, self.width, self.inner):
+    def forward_from_residual(self, ctx, residual: torch.Tensor, norm, pre=None, then=None):
+        """Steps of few tokens.  Narrow models: norm + gate|up + SwiGLU in one launch, down +
+        residual add in another.  Otherwise the norm launches go: gate|up takes the 1 / rms of
+        ``pre`` as a factor on its accumulators, and the down projection adds into the
+        residual and leaves ``then`` all but done."""
+        if ctx.act_dtype != torch.bfloat16 or type(norm) is not RMSNorm:
             return False
-        h = ops.small_norm_swiglu(residual, norm.weight, norm.eps, self.w_gate_up)
-        ops.small_linear_residual(residual, h, self.w_down)
+        if ops.small_step_fits(ctx.num_tokens, self.width, self.width, self.inner):
+            h = ops.small_norm_swiglu(residual, norm.weight, norm.eps, self.w_gate_up)
+            ops.small_linear_residual(residual, h, self.w_down)
+            return True
+        if not ops.deferred_norm_fits(ctx.num_tokens, self.w_gate_up, self.w_down):
+            return False
+        if pre is not None:
+            h = ops.linear_bf16(pre.scaled, self.w_gate_up, glu=True, sumsq=pre.sumsq, eps=norm.eps)
+        else:
+            h = ops.linear_bf16(norm.add_forward(residual, None, ctx.act_dtype), self.w_gate_up, glu=True)
+        if type(then) is RMSNorm:
+            scaled, sumsq = ops.linear_bf16(h, self.w_down, residual=residual, norm_weight=then.weight)
+            return DeferredNorm(then, scaled, sumsq)
+        ops.linear_bf16(h, self.w_down, residual=residual)
         return True
 
 
