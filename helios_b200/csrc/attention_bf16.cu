@@ -4,7 +4,11 @@
 //   * decode: one query token per request.  A block takes one (request, KV head,
 //     slice of the context); the query heads that share the KV head are the rows
 //     of one MMA tile, so every key and value is read once for the whole group.
-//     Slices are merged by a second kernel (flash-decoding).
+//     Slices are merged by a second kernel (flash-decoding).  The kernel can take the
+//     step's rotary position encoding and cache write with it: every block rotates its
+//     query heads in registers, and the one warp whose tile holds the request's new
+//     token rotates that key and puts it and the value into the cache first
+//     (python/helios/exec/model.py:148-153, paged_attn.py:74-85), which saves a launch.
 //   * prefill / mixed: tiles of query tokens of one request against the keys the
 //     cache holds for it, causal by position (and a window), whatever mix of
 //     prompt portions and single tokens the batch is.
@@ -32,7 +36,12 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
                         const __nv_bfloat16* __restrict__ v_pages,
                         const int* __restrict__ block_table, int bt_stride,
                         const int* __restrict__ positions, int nh, int nkv, int page_size,
-                        int window, float scale_log2, int n_splits, int cluster_merge) {
+                        int window, float scale_log2, int n_splits, int cluster_merge,
+                        const float* __restrict__ rot_cos, const float* __restrict__ rot_sin,
+                        __nv_bfloat16* k_write, __nv_bfloat16* v_write) {
+  // rot_cos / rot_sin [requests, HD / 2]: q (and the new key) still lack their rotation.
+  // k_write / v_write (the cache again, writable): the new token's key and value are still
+  // in the q|k|v row and go into the cache here.
   pdl_launch_dependents();
   constexpr int RS = HD + 8;
   constexpr int TILE_ELEMS = DEC_TILE * RS;
@@ -99,6 +108,34 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     if (early[p]) load_tile(tp, p);
   }
   pdl_wait();
+  {
+    // the warp whose tile holds the request's own token (the last tile) writes its key and
+    // value before it fetches that tile
+    const int last_tile = tiles_total - 1;
+    if (k_write != nullptr && last_tile >= tile_begin && last_tile < tile_end &&
+        (last_tile - tile_begin) % DEC_WARPS == warp) {
+      const int page = table[pos / page_size];
+      const size_t dst = ((size_t)(page * nkv + kvh) * page_size + pos % page_size) * HD;
+      const __nv_bfloat16* k_new = q + (size_t)seq * q_stride + (size_t)(nh + kvh) * HD;
+      const __nv_bfloat16* v_new = k_new + (size_t)nkv * HD;
+      for (int j = 2 * lane; j < HD / 2; j += 64) {
+        const float2 x1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(k_new + j));
+        const float2 x2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(k_new + j + HD / 2));
+        float2 r1 = x1, r2 = x2;
+        if (rot_cos != nullptr) {
+          const float2 c = *reinterpret_cast<const float2*>(rot_cos + (size_t)seq * (HD / 2) + j);
+          const float2 sn = *reinterpret_cast<const float2*>(rot_sin + (size_t)seq * (HD / 2) + j);
+          r1 = make_float2(x1.x * c.x - x2.x * sn.x, x1.y * c.y - x2.y * sn.y);
+          r2 = make_float2(x2.x * c.x + x1.x * sn.x, x2.y * c.y + x1.y * sn.y);
+        }
+        *reinterpret_cast<__nv_bfloat162*>(k_write + dst + j) = __floats2bfloat162_rn(r1.x, r1.y);
+        *reinterpret_cast<__nv_bfloat162*>(k_write + dst + j + HD / 2) = __floats2bfloat162_rn(r2.x, r2.y);
+      }
+      for (int j = 8 * lane; j < HD; j += 256)
+        *reinterpret_cast<uint4*>(v_write + dst + j) = *reinterpret_cast<const uint4*>(v_new + j);
+      __syncwarp();           // the copies below, by other lanes, read these rows
+    }
+  }
 #pragma unroll
   for (int p = 0; p < DEC_STAGES - 1; ++p) {
     const int tp = tile + p * DEC_WARPS;
@@ -118,6 +155,26 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
         const int row = g0 + (e & 1) * 8;
         const int col = ks * 16 + c0 + (e >> 1) * 8;
         qa[ks][e] = (row < G) ? *reinterpret_cast<const uint32_t*>(qrow + (size_t)row * HD + col) : 0u;
+      }
+    }
+    if (rot_cos != nullptr) {
+      // rotate-half pairs (j, j + HD / 2): both values of a pair are in this thread's fragments
+      const float* cs = rot_cos + (size_t)seq * (HD / 2);
+      const float* sn = rot_sin + (size_t)seq * (HD / 2);
+#pragma unroll
+      for (int ks = 0; ks < HD / 32; ++ks) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int col = ks * 16 + c0 + (e >> 1) * 8;
+          const float2 c = *reinterpret_cast<const float2*>(cs + col);
+          const float2 sv = *reinterpret_cast<const float2*>(sn + col);
+          const float2 x1 = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&qa[ks][e]));
+          const float2 x2 = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&qa[ks + HD / 32][e]));
+          __nv_bfloat162 r1 = __floats2bfloat162_rn(x1.x * c.x - x2.x * sv.x, x1.y * c.y - x2.y * sv.y);
+          __nv_bfloat162 r2 = __floats2bfloat162_rn(x2.x * c.x + x1.x * sv.x, x2.y * c.y + x1.y * sv.y);
+          qa[ks][e] = *reinterpret_cast<uint32_t*>(&r1);
+          qa[ks + HD / 32][e] = *reinterpret_cast<uint32_t*>(&r2);
+        }
       }
     }
   }
@@ -418,8 +475,12 @@ template <int HD>
 int launch_decode(void* out, float* part_o, float* part_ml, const void* q, int q_stride,
                   const void* k_pages, const void* v_pages, const int* block_table, int bt_stride,
                   const int* positions, int S, int nh, int nkv, int page_size, int window,
-                  float scale, int n_splits, cudaStream_t stream) {
+                  float scale, int n_splits, const float* rot_cos, const float* rot_sin,
+                  int write_cache, cudaStream_t stream) {
   constexpr int RS = HD + 8;
+  // the new keys and values go into the very pages the kernel reads
+  __nv_bfloat16* k_write = write_cache ? (__nv_bfloat16*)const_cast<void*>(k_pages) : nullptr;
+  __nv_bfloat16* v_write = write_cache ? (__nv_bfloat16*)const_cast<void*>(v_pages) : nullptr;
   size_t smem = (size_t)DEC_WARPS * DEC_STAGES * 2 * DEC_TILE * RS * sizeof(__nv_bfloat16);
   const size_t red = (size_t)(DEC_WARPS * 16 * (HD + 2) + 16 * (HD + 2)) * sizeof(float);
   if (red > smem) smem = red;
@@ -450,13 +511,15 @@ int launch_decode(void* out, float* part_o, float* part_ml, const void* q, int q
     cfg.numAttrs = hb_pdl_enabled() ? 2 : 1;
     cudaLaunchKernelEx(&cfg, kernel, (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, q_stride,
                        (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, bt_stride,
-                       positions, nh, nkv, page_size, window, scale * LOG2E, n_splits, 1);
+                       positions, nh, nkv, page_size, window, scale * LOG2E, n_splits, 1,
+                       rot_cos, rot_sin, k_write, v_write);
     return hb_check_launch();
   }
   hb_launch(kernel, dim3(grid), dim3(DEC_WARPS * 32), smem, stream, 
       (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, q_stride,
       (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, bt_stride,
-      positions, nh, nkv, page_size, window, scale * LOG2E, n_splits, 0);
+      positions, nh, nkv, page_size, window, scale * LOG2E, n_splits, 0,
+      rot_cos, rot_sin, k_write, v_write);
   if (n_splits > 1)
     hb_launch(decode_merge_kernel<HD>, dim3(S * nh), dim3(HD < 128 ? HD : 128), 0, stream, 
         (__nv_bfloat16*)out, part_o, part_ml, n_splits);
@@ -503,17 +566,27 @@ int launch_prefill(void* out, const void* q, int q_stride, const void* k_pages, 
 // [S, nh, n_splits, 2]; both unused when n_splits == 1.  With 2..8 slices and part_o null
 // the slices run as one thread-block cluster and are merged through distributed shared
 // memory instead of a second kernel.
+//   q is a row of q|k|v per request ([nh + 2 nkv] heads, q_stride elements apart).  With
+//   rot_cos / rot_sin (float [S, hd / 2]) the query heads are rotated on the way in (rotate-half
+//   pairs (j, j + hd / 2)); with write_cache the request's key (rotated likewise) and value are
+//   taken from that row and stored at its position in the pages before the kernel attends.
+//   Without either, q must be rotated and the cache written already.
 HB_EXPORT int hb_attention_decode_bf16(void* out, float* part_o, float* part_ml, const void* q,
                                        int q_stride, const void* k_pages, const void* v_pages,
                                        const int* block_table, int bt_stride, const int* positions,
                                        int S, int nh, int nkv, int hd, int page_size, int window,
-                                       float scale, int n_splits, cudaStream_t stream) {
+                                       float scale, int n_splits, const float* rot_cos,
+                                       const float* rot_sin, int write_cache, cudaStream_t stream) {
   if (S <= 0) return HB_OK;
   if (nkv <= 0 || nh % nkv != 0 || nh / nkv > 16 || page_size <= 0 || n_splits < 1)
     return HB_BAD_ARGUMENT;
+  if ((rot_cos == nullptr) != (rot_sin == nullptr)) return HB_BAD_ARGUMENT;
+  if (write_cache && (q_stride < (nh + 2 * nkv) * hd || (q_stride & 7) || ((uintptr_t)q & 15)))
+    return HB_BAD_ARGUMENT;
   HB_DISPATCH_HD(hd, return launch_decode<HD>(out, part_o, part_ml, q, q_stride, k_pages, v_pages,
                                               block_table, bt_stride, positions, S, nh, nkv,
-                                              page_size, window, scale, n_splits, stream));
+                                              page_size, window, scale, n_splits, rot_cos, rot_sin,
+                                              write_cache, stream));
 }
 
 // Prefill / mixed: q_tiles holds (request, first local token) for every tile of

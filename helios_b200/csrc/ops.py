@@ -793,6 +793,8 @@ def linear_logits(rows: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
 TILED_HEAD_DIMS = (32, 64, 96, 128)
 #: merge the context slices of decode attention inside a thread-block cluster (up to 8 slices)
 ATTENTION_CLUSTER_MERGE = True
+#: steps of single tokens: rotary position encoding and cache write inside the decode kernel
+ATTENTION_DECODE_ROTARY = True
 #: use the tcgen05 attention kernel for batches with prompt portions where its sizes fit
 ATTENTION_TCGEN05 = True
 #: ... with two tiles of query rows per block when a request brings more than one tile of tokens
@@ -838,9 +840,16 @@ def decode_splits(num_seqs: int, num_kv_heads: int, max_context: int, head_dim: 
 def attention_decode_bf16(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                           block_table: torch.Tensor, positions: torch.Tensor, num_heads: int,
                           num_kv_heads: int, head_dim: int, page_size: int,
-                          window: Optional[int], scale: float, n_splits: int) -> torch.Tensor:
+                          window: Optional[int], scale: float, n_splits: int,
+                          rotary=None, write_cache: bool = False) -> torch.Tensor:
     """Decode attention (token i is the one new token of request i) on the tensor cores;
-    bfloat16, head_dim in TILED_HEAD_DIMS, at most 16 query heads per KV head."""
+    bfloat16, head_dim in TILED_HEAD_DIMS, at most 16 query heads per KV head.
+
+    ``rotary`` = (cos, sin), float32 [requests, head_dim / 2]: the rows of ``qkv`` are not
+    rotated yet; the kernel rotates the query heads on the way in.  ``write_cache``: the
+    requests' new keys (rotated likewise) and values are still in ``qkv`` and the kernel
+    stores them in the pages before it attends.  (Without either, ``rope_kv_write`` must have
+    run.)  ``qkv`` itself is left as it was."""
     _check(qkv, "qkv", torch.bfloat16, 2)
     _check(k_pages, "k_pages", torch.bfloat16, 4)
     _check(v_pages, "v_pages", torch.bfloat16, 4)
@@ -857,6 +866,18 @@ def attention_decode_bf16(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: tor
     S = qkv.shape[0]
     if block_table.shape[0] != S or positions.numel() != S:
         raise KernelError("decode attention needs one token per request")
+    cos = sin = None
+    if rotary is not None and rotary[0] is not None:
+        cos, sin = rotary
+        _check(cos, "cos", torch.float32, 2)
+        _check(sin, "sin", torch.float32, 2)
+        if tuple(cos.shape) != (S, head_dim // 2) or cos.shape != sin.shape \
+                or not (cos.is_contiguous() and sin.is_contiguous()):
+            raise KernelError(f"rotary tables have shape {tuple(cos.shape)}, expected ({S}, {head_dim // 2})")
+    if (cos is not None or write_cache) and (qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim
+                                             or not qkv.is_contiguous()):
+        raise KernelError(f"q|k|v rows have {qkv.shape[1]} entries for {num_heads} + 2 x {num_kv_heads} "
+                          f"heads of {head_dim}")
     out = torch.empty((S, num_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
     part_o = part_ml = None
     # slices as one cluster only while all blocks are resident at once: with several rounds
@@ -867,10 +888,12 @@ def attention_decode_bf16(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: tor
         part_ml = torch.empty((S, num_heads, n_splits, 2), dtype=torch.float32, device=qkv.device)
     f = _fn("attention_bf16", "hb_attention_decode_bf16",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
-             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p,
+             c_int, c_void_p])
     _run(f(_p(out), _p(part_o), _p(part_ml), _p(qkv), qkv.shape[1], _p(k_pages), _p(v_pages),
            _p(block_table), block_table.shape[1], _p(positions), S, num_heads, num_kv_heads,
-           head_dim, page_size, int(window or 0), float(scale), int(n_splits), _stream()),
+           head_dim, page_size, int(window or 0), float(scale), int(n_splits), _p(cos), _p(sin),
+           1 if write_cache else 0, _stream()),
          "attention_decode_bf16")
     return out
 
@@ -999,19 +1022,34 @@ def _step_tiles(ctx, tile: int, longest_first: bool, device) -> torch.Tensor:
 
 def attention(ctx, qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
               block_table: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
-              page_size: int, window: Optional[int], scale: float) -> torch.Tensor:
+              page_size: int, window: Optional[int], scale: float,
+              fresh=None) -> torch.Tensor:
     """Attention of the step's tokens over the cache; chooses the kernel by dtype, sizes
     and the shape of the batch described by ``ctx``.  bfloat16 with a tiled head size
     runs on the tensor cores (split-context decode kernel for batches of single tokens,
-    tiled kernel otherwise); everything else, and float32, on the generic kernel."""
+    tiled kernel otherwise); everything else, and float32, on the generic kernel.
+
+    ``fresh`` = (cos, sin, write_cache): ``qkv`` comes straight from the projection; q and k
+    are rotated (tables None: no rotation) and, with ``write_cache``, k and v stored in the
+    pages first: inside the decode kernel where that one runs, else by ``rope_kv_write``."""
+    decode = (qkv.dtype == torch.bfloat16 and head_dim in TILED_HEAD_DIMS and ctx.decode_only
+              and num_heads // num_kv_heads <= 16)
+    rotary, write_cache = None, False
+    if fresh is not None:
+        cos, sin, write = fresh
+        if decode and ATTENTION_DECODE_ROTARY and (cos is None or cos.shape[1] * 2 == head_dim):
+            rotary, write_cache = (cos, sin), bool(write)
+        else:
+            rope_kv_write(qkv, cos, sin, ctx.positions, ctx.seq_of_token, block_table, k_pages, v_pages,
+                          num_heads, num_kv_heads, head_dim, page_size, write_cache=write)
     if qkv.dtype == torch.bfloat16 and head_dim in TILED_HEAD_DIMS:
-        if ctx.decode_only and num_heads // num_kv_heads <= 16:
+        if decode:
             splits = ctx.extras.get("decode_splits")
             if splits is None:
                 splits = decode_splits(ctx.num_seqs, num_kv_heads, ctx.max_context_len, head_dim)
             return attention_decode_bf16(qkv, k_pages, v_pages, block_table, ctx.positions,
                                          num_heads, num_kv_heads, head_dim, page_size, window,
-                                         scale, splits)
+                                         scale, splits, rotary, write_cache)
         if (ATTENTION_TCGEN05 and ctx.max_tokens_per_seq >= 16
                 and tc_attention_supported(num_heads, num_kv_heads, head_dim, page_size)):
             tile = 128 // (num_heads // num_kv_heads)

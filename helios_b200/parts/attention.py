@@ -120,12 +120,9 @@ class GQAAttention(Mixer):
     def _attend(self, ctx, qkv: torch.Tensor, cache: LayerCache) -> torch.Tensor:
         table = ctx.block_tables[cache.group]
         cos, sin = self._rotary_tables(ctx)
-        ops.rope_kv_write(qkv, cos, sin, ctx.positions, ctx.seq_of_token, table,
-                          cache.k_pages, cache.v_pages, self.num_heads, self.num_kv_heads,
-                          self.head_dim, cache.page_size, write_cache=cache.write)
         return ops.attention(ctx, qkv, cache.k_pages, cache.v_pages, table, self.num_heads,
                              self.num_kv_heads, self.head_dim, cache.page_size, self.window,
-                             self.scale)
+                             self.scale, fresh=(cos, sin, cache.write))
 
     def forward(self, ctx, x: torch.Tensor, cache: LayerCache, state=None) -> torch.Tensor:
         return ops.linear(self._attend(ctx, ops.linear(x, self.w_qkv, self.b_qkv), cache), self.w_o)

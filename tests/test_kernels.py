@@ -165,6 +165,60 @@ def test_decode_attention_bf16(nh, nkv, hd, page, window, splits, cluster, monke
 
 
 @pytest.mark.parametrize("nh,nkv,hd,page", [(32, 8, 128, 16), (28, 4, 128, 16), (14, 2, 64, 8), (6, 6, 96, 64),
+                                            (16, 1, 32, 16), (7, 1, 64, 3)])
+@pytest.mark.parametrize("window", [None, 100])
+@pytest.mark.parametrize("splits,cluster", [(1, True), (3, True), (8, True), (5, False), (13, True)])
+@pytest.mark.parametrize("rotate", [True, False])
+def test_decode_attention_rotates_and_writes_the_new_token_itself(nh, nkv, hd, page, window, splits, cluster,
+                                                                  rotate, monkeypatch):
+    """The q|k|v rows come straight from the projection: the kernel rotates the query heads,
+    and stores the new token's rotated key and its value at its place in the pages (which hold
+    NaN there before) and nowhere else, before it attends."""
+    monkeypatch.setattr(ops(), "ATTENTION_CLUSTER_MERGE", cluster)
+    seqs = [(n, 1) for n in (0, 1, 15, 16, 17, 31, 32, 33, 127, 128, 129, 255, 256, 1000, 2049)]
+    case = make_paged_case(seqs, nh, nkv, hd, page, torch.bfloat16, DEV, seed=nh + hd + 1)
+    S = len(seqs)
+    g = torch.Generator().manual_seed(hd)
+    raw = torch.randn(S, (nh + 2 * nkv) * hd, generator=g).to(torch.bfloat16)
+    positions = case.positions.cpu()
+    inv = plain_model.rope_inv_freq(hd, 10000.0, None)
+    q = raw[:, : nh * hd].view(S, nh, hd).double()
+    k = raw[:, nh * hd:(nh + nkv) * hd].view(S, nkv, hd).double()
+    v = raw[:, (nh + nkv) * hd:].view(S, nkv, hd).double()
+    cos = sin = None
+    if rotate:
+        cos, sin = ops().rotary_table(case.positions, inv.to(DEV))
+        q, k = plain_model.apply_rope(q, positions, inv), plain_model.apply_rope(k, positions, inv)
+    q, k = q.to(torch.bfloat16).double(), k.to(torch.bfloat16).double()
+    before_k, before_v = case.k_pages.clone(), case.v_pages.clone()
+    for i, (a, _n) in enumerate(seqs):
+        dq, dk, dv, da = case.dense[i]
+        dk, dv = dk.clone(), dv.clone()
+        dk[a], dv[a] = k[i], v[i]
+        case.dense[i] = (q[i:i + 1], dk, dv, da)
+        pg, slot = int(case.table[i, a // page]), a % page
+        case.k_pages[pg, :, slot] = float("nan")
+        case.v_pages[pg, :, slot] = float("nan")
+    scale = 1.0 / math.sqrt(hd)
+    x = raw.to(DEV)
+    out = ops().attention_decode_bf16(x, case.k_pages, case.v_pages, case.table, case.positions, nh, nkv, hd,
+                                      page, window, scale, splits, rotary=(cos, sin) if rotate else None,
+                                      write_cache=True)
+    torch.testing.assert_close(out.cpu().double(), dense_attention(case, scale, window), atol=2e-2, rtol=2e-2)
+    assert torch.equal(x.cpu(), raw)
+    kp, vp = case.k_pages.cpu(), case.v_pages.cpu()
+    same = torch.ones_like(kp, dtype=torch.bool)
+    for i, (a, _n) in enumerate(seqs):
+        pg, slot = int(case.table[i, a // page]), a % page
+        same[pg, :, slot] = False
+        torch.testing.assert_close(kp[pg, :, slot].double(), k[i], atol=1e-2, rtol=1e-2)
+        assert torch.equal(vp[pg, :, slot].double(), v[i])
+    bk, bv = before_k.cpu(), before_v.cpu()
+    assert torch.equal(kp[same].nan_to_num(7.0), bk[same].nan_to_num(7.0))
+    assert torch.equal(vp[same].nan_to_num(7.0), bv[same].nan_to_num(7.0))
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page", [(32, 8, 128, 16), (28, 4, 128, 16), (14, 2, 64, 8), (6, 6, 96, 64),
                                             (16, 1, 32, 16), (3, 1, 64, 3)])
 @pytest.mark.parametrize("window", [None, 100])
 def test_prefill_attention_bf16(nh, nkv, hd, page, window):
