@@ -1,4 +1,4 @@
-from .base import (Block, FeedForward, InputStage, LayerCache, Mixer, Norm, OutputStage, PagedCacheSpec, Part,
+from .base import (Block, DeferredNorm, FeedForward, InputStage, LayerCache, Mixer, Norm, OutputStage, PagedCacheSpec, Part,
                    PositionEncoding, StateSpec, WeightSpec, known_parts, part_class,
                    register_part)
 from .norm import RMSNorm
@@ -9,7 +9,7 @@ from .embedding import NormedHead, OutputHead, TokenEmbedding
 from .block import PreNormBlock
 from .plan import ModelPlan, Run
 
-__all__ = ["Block", "FeedForward", "InputStage", "OutputStage", "NormedHead", "LayerCache", "Mixer", "Norm", "PagedCacheSpec", "Part",
+__all__ = ["Block", "DeferredNorm", "FeedForward", "InputStage", "OutputStage", "NormedHead", "LayerCache", "Mixer", "Norm", "PagedCacheSpec", "Part",
            "PositionEncoding", "StateSpec", "WeightSpec", "known_parts", "part_class",
            "register_part", "RMSNorm", "RotaryEncoding", "rotary_frequencies", "GQAAttention",
            "SwiGLU", "OutputHead", "TokenEmbedding", "PreNormBlock", "ModelPlan", "Run"]

@@ -139,6 +139,68 @@ def test_embedding_and_head_parts():
 
 
 # ---------------------------------------------------------------------- the schedule is data
+@pytest.mark.parametrize("lens", [[20], [1, 1, 1, 1, 1, 1, 1], [9, 1, 12]])
+@pytest.mark.parametrize("bias", [False, True])
+def test_the_parts_hand_a_norm_to_one_another(lens, bias):
+    """Steps of few tokens in bfloat16: the attention part adds its output into the residual
+    and leaves the feed-forward's norm all but done (a DeferredNorm: rows times the norm
+    weight, partial sums of squares); the feed-forward takes it, applies 1 / rms inside its
+    first product and adds into the residual too.  Against the plain functions."""
+    from helios_b200.parts import DeferredNorm, GQAAttention, LayerCache, RMSNorm, RotaryEncoding, SwiGLU
+
+    H, I, nh, nkv, hd, page, eps = 2304, 640, 6, 2, 64, 8, 1e-5     # wider than the narrow-model kernels take
+    g = torch.Generator().manual_seed(len(lens) + bias)
+    attn, ffn = GQAAttention(H, nh, nkv, hd, 1 / math.sqrt(hd), bias), SwiGLU(H, I)
+    norm1, norm2 = RMSNorm(H, eps), RMSNorm(H, eps)
+    t = {}
+    for name, part in (("a.", attn), ("f.", ffn), ("n1.", norm1), ("n2.", norm2)):
+        w = {k: (torch.randn(sp.shape, generator=g) * 0.03 if len(sp.shape) == 2
+                 else 1.0 + 0.2 * torch.randn(sp.shape, generator=g)) for k, sp in part.weight_specs().items()}
+        w = {k: (v.to(torch.bfloat16).float() if v.dim() == 2 else v) for k, v in w.items()}
+        part.bind({k: v.to(DEV, torch.bfloat16 if v.dim() == 2 else torch.float32) for k, v in w.items()})
+        t.update({name + k: v.double() for k, v in w.items()})
+    ctx, _lay = _ctx([[0] * n for n in lens], torch.bfloat16, page_size=page)
+    RotaryEncoding(hd, 10000.0).prepare(ctx)
+    T = sum(lens)
+    res0 = torch.randn(T, H, generator=g) * 2.0
+    residual = res0.to(DEV).clone()
+    k_pages = torch.full((64, nkv, page, hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    cache = LayerCache(k_pages, k_pages.clone(), group=0, page_size=page)
+
+    handed = attn.forward_from_residual(ctx, residual, norm1, cache, None, pre=None, then=norm2)
+    assert isinstance(handed, DeferredNorm) and handed.norm is norm2
+    inv = plain_model.rope_inv_freq(hd, 10000.0, None)
+    want, off = [], 0
+    for n in lens:
+        xs = plain_model.rms_norm(res0[off:off + n].double(), t["n1.weight"], eps)
+        q = xs @ t["a.q_proj.weight"].T + (t["a.q_proj.bias"] if bias else 0)
+        k = xs @ t["a.k_proj.weight"].T + (t["a.k_proj.bias"] if bias else 0)
+        v = xs @ t["a.v_proj.weight"].T + (t["a.v_proj.bias"] if bias else 0)
+        pos = torch.arange(n)
+        a = plain_model.causal_attention(plain_model.apply_rope(q.view(n, nh, hd), pos, inv),
+                                         plain_model.apply_rope(k.view(n, nkv, hd), pos, inv),
+                                         v.view(n, nkv, hd), 1 / math.sqrt(hd), None)
+        want.append(res0[off:off + n].double() + a.reshape(n, nh * hd) @ t["a.o_proj.weight"].T)
+        off += n
+    after_attn = torch.cat(want)
+    torch.testing.assert_close(residual.cpu().double(), after_attn, atol=3e-2, rtol=3e-2)
+    got = residual.cpu()
+    assert torch.equal(handed.scaled.cpu(), (got * t["n2.weight"].float()).to(torch.bfloat16))
+    torch.testing.assert_close(handed.sumsq.cpu().double().sum(1), (got.double() ** 2).sum(1), rtol=1e-5, atol=0)
+
+    assert ffn.forward_from_residual(ctx, residual, norm2, pre=handed, then=None) is True
+    xs = plain_model.rms_norm(got.double(), t["n2.weight"], eps)
+    want = got.double() + plain_model.swiglu(xs, t["f.gate_proj.weight"], t["f.up_proj.weight"],
+                                             t["f.down_proj.weight"])
+    torch.testing.assert_close(residual.cpu().double(), want, atol=3e-2, rtol=3e-2)
+    # without anything handed over the feed-forward norms by itself, to the same result
+    again = got.to(DEV).clone()
+    assert ffn.forward_from_residual(ctx, again, norm2, pre=None, then=None) is True
+    torch.testing.assert_close(again.cpu().double(), want, atol=3e-2, rtol=3e-2)
+    # a norm of another kind next: nothing is prepared for it
+    assert attn.forward_from_residual(ctx, res0.to(DEV).clone(), norm1, cache, None, pre=None, then=object()) is True
+
+
 def _toy_plan(schedule, layers=2):
     from helios_b200.config import DenseDecoderConfig
     from helios_b200.models import build_dense_decoder_plan
