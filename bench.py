@@ -17,6 +17,8 @@ Qwen2.5-0.5B sizes (decode at batch 1, 64 and 256 from 512 to 1,024 tokens, pref
 workload through ``LLMEngine`` and reports wall time, tokens a second, the steps by size
 and the pages' high-water mark; ``--micro`` times single kernels as chains in a captured
 graph (the tables under ``profiles/``).  Synthetic token ids, uniform from a seed.
+A decode measurement fills the requests' contexts (prompt steps), runs 64 untimed decode
+steps, then the W warm-up steps, then exactly K timed steps.
 """
 from __future__ import annotations
 
@@ -63,6 +65,9 @@ MODEL_NAMES = {"llama8b": "Llama-3.1-8B sizes", "qwen7b": "Qwen2.5-7B sizes",
                "qwen0.5b": "Qwen2.5-0.5B sizes"}
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
+#: untimed decode steps between the prompt fill and the W warm-up steps of a decode measurement
+#: (named in ``config``): they take the device out of the power state the fill left it in
+SETTLE_STEPS = 64
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
@@ -255,16 +260,16 @@ def run_reference(args):
                                  / (load_peaks()["bf16_tflops"] * 1e12), 4)}
 
     steps, warmup = args.steps, max(3, args.warmup)
-    ctx0 = args.context - steps - warmup - 64
+    ctx0 = args.context - steps - warmup - SETTLE_STEPS - 64
     for b in range(args.batch):
-        engine.add_request(f"e{b}", tokens(ctx0), SamplingParams(max_tokens=steps + warmup + 64))
+        engine.add_request(f"e{b}", tokens(ctx0), SamplingParams(max_tokens=steps + warmup + SETTLE_STEPS + 64))
     guard = 0
     while engine.scheduler.waiting or any(not s.is_prefill_done for s in engine.scheduler.running):
         engine.step()
         guard += 1
         if guard > 10000:
             break
-    for _ in range(warmup):
+    for _ in range(SETTLE_STEPS + warmup):     # the same untimed decode steps as the other arm
         engine.step()
     sampler = ClockSampler()
     sampler.start()
@@ -295,7 +300,8 @@ def run_reference(args):
                    "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
                    "global_batch": args.batch, "live_requests": running,
                    "seq_len": args.context, "page_size": page, "parallelism": "single GPU",
-                   "api": "helios.engine.LLMEngine.step", "setup_s": round(setup_s, 1)},
+                   "api": "helios.engine.LLMEngine.step", "setup_s": round(setup_s, 1),
+                   "settle_steps": SETTLE_STEPS},
         "clocks": sampler.summary(t0, t1), "gpu_launches": 0, "prefill": prefill,
         "e2e": {"value": round(running / wall, 1), "unit": "tokens/s",
                 "h2d_bytes_per_step": 16 * args.batch, "d2h_bytes_per_step": 8 * args.batch},
@@ -563,7 +569,7 @@ def main():
     def measure_decode(core, cfg, batch, ctx_end, steps, warmup):
         """``steps`` decode steps of ``batch`` requests that end at context ``ctx_end``."""
         vocab = cfg["vocab_size"]
-        ctx0 = ctx_end - steps - warmup
+        ctx0 = ctx_end - steps - warmup - SETTLE_STEPS
         for b in range(batch):
             left = ctx0
             while left > 0:
@@ -575,6 +581,12 @@ def main():
         def one():
             core.step([StepEntry(f"d{b}", [last[b]], [0]) for b in range(batch)])
 
+        # the prompt fill above is a burst of tensor-core work that leaves the device under its
+        # power cap at lowered SM clocks for some 100 ms; untimed decode steps first, so that the
+        # timed ones run in the state of a device that is decoding, as a server's do
+        for _ in range(SETTLE_STEPS):
+            one()
+        torch.cuda.synchronize()
         for _ in range(warmup):
             one()
         before = ops.launch_count
@@ -582,7 +594,7 @@ def main():
         launches = ops.launch_count - before
         for b in range(batch):
             core.end(f"d{b}")
-        mean_ctx = ctx0 + warmup + steps // 2
+        mean_ctx = ctx0 + SETTLE_STEPS + warmup + steps // 2
         need = decode_bytes(cfg, cfg["num_hidden_layers"], batch, mean_ctx)
         return {"ms": mean, "ms_median": median, "launches": launches, "mean_ctx": mean_ctx,
                 "tokens_per_s": batch / mean * 1e3, "gbs": need / (mean * 1e-3) / 1e9}
@@ -615,7 +627,7 @@ def main():
               "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
               "global_batch": args.batch, "seq_len": args.context, "page_size": page,
               "parallelism": "single GPU", "l2": "inputs (weights + cache) larger than L2",
-              "seed": args.seed, "workload": args.workload}
+              "seed": args.seed, "workload": args.workload, "settle_steps": SETTLE_STEPS}
 
     if args.workload == "mixed":
         t0 = time.time()
@@ -671,13 +683,16 @@ def main():
             max_num_batched_tokens=PREFILL_TOKENS, max_model_len=args.context + 8,
             num_blocks=args.batch * (args.context // page + 2) + 8, watermark=0.0,
             run_ahead=not args.no_run_ahead), model=model)
-        ctx0 = args.context - args.steps - args.warmup
+        ctx0 = args.context - args.steps - args.warmup - SETTLE_STEPS
         # every request must still be decoding when the timed steps end, whenever its
         # prompt was finished
         for b in range(args.batch):
             toks = torch.randint(0, cfg["vocab_size"], (ctx0 - 64,), generator=gen).tolist()
-            engine.add_request(f"e{b}", toks, SamplingParams(max_tokens=args.steps + args.warmup + 64))
+            engine.add_request(f"e{b}", toks,
+                               SamplingParams(max_tokens=args.steps + args.warmup + SETTLE_STEPS + 64))
         while any(s.num_pending_tokens > 1 for s in engine.scheduler.running) or engine.scheduler.waiting:
+            engine.step()
+        for _ in range(SETTLE_STEPS):        # as in measure_decode: out of the prompt fill's power state
             engine.step()
         for _ in range(args.warmup):
             engine.step()
