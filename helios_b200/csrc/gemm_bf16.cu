@@ -220,14 +220,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if (scaled) {
       // 1 / rms of this tile's tokens, while the products run: a warp per column adds the
       // partial sums in a fixed order
-      for (int c = quarter; c < BN; c += 4) {
-        const int t = tile_b * BN + c;
-        float ss = 0.f;
-        if (t < args.T)
-          for (int j = lane; j < args.slots_in; j += 32) ss += __ldcg(args.sumsq_in + (size_t)t * args.slots_in + j);
-        ss = warp_sum(ss);
-        if (lane == 0) col_scale[c] = t < args.T ? rsqrtf(ss / args.width + args.eps) : 0.f;
+      // (all columns at once: 128 / BN consecutive lanes share a column's partial sums)
+      constexpr int PER_COL = BN <= 128 ? 128 / BN : 1;
+      const int et = (int)threadIdx.x - 64;
+      const int c = et / PER_COL, q = et % PER_COL;
+      const int t = tile_b * BN + c;
+      float ss = 0.f;
+      if (t < args.T) {
+        const float* src = args.sumsq_in + (size_t)t * args.slots_in;
+#pragma unroll 8
+        for (int j = q; j < args.slots_in; j += PER_COL) ss += __ldcg(src + j);
       }
+#pragma unroll
+      for (int o = PER_COL / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (q == 0) col_scale[c] = t < args.T ? rsqrtf(ss / args.width + args.eps) : 0.f;
       asm volatile("bar.sync 1, 128;" ::: "memory");
     }
     bool ok = true;
@@ -347,25 +353,31 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             // into the residual stream; a warp holds 32 features of every token of the tile
             const int n = tile_a * BM + r;
             const int slots = (int)gridDim.x * SUMSQ_SLOTS;
+            const bool mine = n < args.N;
+            const float bias_n = (mine && args.bias) ? args.bias[n] : 0.f;
+            const float weight_n = (mine && args.norm_weight) ? args.norm_weight[n] : 0.f;
+            float old[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {                    // the 16 loads in one trip
+              const int t = tile_b * BN + c + j;
+              old[j] = (mine && t < args.T) ? args.residual[(size_t)t * args.N + n] : 0.f;
+            }
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int t = tile_b * BN + c + j;
-              if (t >= args.T) break;                         // the same for the whole warp
-              float sq = 0.f;
-              if (n < args.N) {
-                float* p = args.residual + (size_t)t * args.N + n;
-                const float nv = *p + v[j] + (args.bias ? args.bias[n] : 0.f);
-                *p = nv;
-                if (args.norm_weight) {
-                  reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)t * args.ldo + n] =
-                      __float2bfloat16_rn(nv * args.norm_weight[n]);
-                  sq = nv * nv;
+              if (t < args.T) {                               // the same for the whole warp
+                const float nv = old[j] + v[j] + bias_n;
+                if (mine) {
+                  args.residual[(size_t)t * args.N + n] = nv;
+                  if (args.norm_weight)
+                    reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)t * args.ldo + n] =
+                        __float2bfloat16_rn(nv * weight_n);
                 }
-              }
-              if (args.norm_weight) {
-                sq = warp_sum(sq);
-                float* dst = args.sumsq_out + (size_t)t * slots + tile_a * SUMSQ_SLOTS;
-                if (lane == 0) { dst[quarter] = sq; dst[4 + quarter] = 0.f; }
+                if (args.norm_weight) {
+                  const float sq = warp_sum(mine ? nv * nv : 0.f);
+                  float* dst = args.sumsq_out + (size_t)t * slots + tile_a * SUMSQ_SLOTS;
+                  if (lane == 0) { dst[quarter] = sq; dst[4 + quarter] = 0.f; }
+                }
               }
             }
           } else if (SWAP) {
@@ -405,42 +417,50 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     cluster_sync_all();
     if (SWAP && args.residual != nullptr) {
       // Into the residual stream: this block adds up rows [r0, r1) of the tile's 128 features
-      // for every token, a warp per token column, and leaves one partial sum of squares.
+      // for every token of the tile, an element a thread; the squares go through shared
+      // memory (behind the partial sums), where four lanes add up a token's in a fixed order.
       if (warp >= 2 && !*abort_flag) {
         const int S = args.k_splits;
-        const int r0 = split * BM / S, r1 = (split + 1) * BM / S;
+        const int r0 = split * BM / S, r1 = (split + 1) * BM / S, nrows = r1 - r0;
+        const int ncols = min(BN, args.T - tile_b * BN);
+        const int total = ncols * nrows;
         const int slots = (int)gridDim.x * SUMSQ_SLOTS;
-        for (int c = warp - 2; c < BN; c += 4) {
-          const int t = tile_b * BN + c;
-          if (t >= args.T) break;
-          float sq = 0.f;
-          for (int rr = r0 + lane; rr < r1; rr += 32) {
-            float pv[8];
+        const int et = (int)threadIdx.x - 64;
+        float* squares = reinterpret_cast<float*>(aligned) + Cfg::ACC_COLS * BM;     // [ncols][nrows]
+        for (int e = et; e < total; e += 128) {
+          const int c = e / nrows, rr = r0 + (e - c * nrows);
+          const int t = tile_b * BN + c, n = tile_a * BM + rr;
+          const bool mine = n < args.N;
+          const float old = mine ? args.residual[(size_t)t * args.N + n] : 0.f;
+          const float weight_n = (mine && args.norm_weight) ? args.norm_weight[n] : 0.f;
+          const float bias_n = (mine && args.bias) ? args.bias[n] : 0.f;
+          float pv[8];
 #pragma unroll
-            for (int sp = 0; sp < 8; ++sp)
-              pv[sp] = sp < S ? ld_peer_smem(base + (uint32_t)(c * BM + rr) * 4u, sp) : 0.f;
-            float val = 0.f;
+          for (int sp = 0; sp < 8; ++sp)
+            pv[sp] = sp < S ? ld_peer_smem(base + (uint32_t)(c * BM + rr) * 4u, sp) : 0.f;
+          float val = 0.f;
 #pragma unroll
-            for (int sp = 0; sp < 8; ++sp) val += pv[sp];
-            const int n = tile_a * BM + rr;
-            if (n < args.N) {
-              float* p = args.residual + (size_t)t * args.N + n;
-              const float nv = *p + val + (args.bias ? args.bias[n] : 0.f);
-              *p = nv;
-              if (args.norm_weight) {
-                reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)t * args.ldo + n] =
-                    __float2bfloat16_rn(nv * args.norm_weight[n]);
-                sq += nv * nv;
-              }
-            }
+          for (int sp = 0; sp < 8; ++sp) val += pv[sp];
+          const float nv = old + val + bias_n;
+          if (mine) {
+            args.residual[(size_t)t * args.N + n] = nv;
+            if (args.norm_weight)
+              reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)t * args.ldo + n] = __float2bfloat16_rn(nv * weight_n);
           }
-          if (args.norm_weight) {
-            sq = warp_sum(sq);
-            float* dst = args.sumsq_out + (size_t)t * slots + tile_a * SUMSQ_SLOTS;
-            if (lane == 0) {
-              dst[split] = sq;
-              if (split == 0) for (int sp = S; sp < SUMSQ_SLOTS; ++sp) dst[sp] = 0.f;
-            }
+          squares[e] = mine ? nv * nv : 0.f;
+        }
+        if (args.norm_weight) {
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          const int c = et >> 2, q = et & 3;                   // at most 32 token columns (checked at launch)
+          float sq = 0.f;
+          if (c < ncols)
+            for (int i = q; i < nrows; i += 4) sq += squares[c * nrows + i];
+          sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+          sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+          if (c < ncols && q == 0) {
+            float* dst = args.sumsq_out + (size_t)(tile_b * BN + c) * slots + tile_a * SUMSQ_SLOTS;
+            dst[split] = sq;
+            if (split == 0) for (int sp = S; sp < SUMSQ_SLOTS; ++sp) dst[sp] = 0.f;
           }
         }
       }
@@ -869,6 +889,7 @@ static int gemm_bf16_call(void* out, const void* x, const void* w, const float* 
   if (residual != nullptr || sumsq_in != nullptr) {
     // the epilogues of few-token steps: swapped orientation, one token tile
     if (swap_bn == 0 || T > swap_bn) return HB_BAD_ARGUMENT;
+    if (residual != nullptr && swap_bn > 32) return HB_BAD_ARGUMENT;   // room for the squares, four lanes a token
     if (residual != nullptr && (glu || out_f32)) return HB_BAD_ARGUMENT;
     if (norm_weight != nullptr && (residual == nullptr || out == nullptr || sumsq_out == nullptr))
       return HB_BAD_ARGUMENT;

@@ -423,7 +423,7 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
     silu(x gate^T) * (x up^T), [T, I].  ``out_dtype`` bfloat16 or float32.  K must be a
     multiple of 8 (TMA rows are 16-byte aligned); any T and N.
 
-    Steps of at most DEFERRED_NORM_TOKENS tokens have two more epilogues.  ``sumsq``
+    Up to DEFERRED_NORM_MOST tokens there are two more epilogues.  ``sumsq``
     (float32 [T, slots]): ``x`` is residual * norm weight without the token's 1 / rms;
     the accumulators are multiplied by rsqrt(sum(sumsq[t]) / K + eps) before bias or SwiGLU.
     ``residual`` (float32 [T, N]): the product is added into it and None is returned, or,
@@ -450,8 +450,8 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
     if out_dtype not in (torch.bfloat16, torch.float32):
         raise KernelError(f"out_dtype {out_dtype} is not supported")
     few = sumsq is not None or residual is not None
-    if few and T > DEFERRED_NORM_TOKENS:
-        raise KernelError(f"the residual and 1 / rms epilogues take at most {DEFERRED_NORM_TOKENS} tokens, got {T}")
+    if few and T > DEFERRED_NORM_MOST:
+        raise KernelError(f"the residual and 1 / rms epilogues take at most {DEFERRED_NORM_MOST} tokens, got {T}")
     if sumsq is not None:
         _check(sumsq, "sumsq", torch.float32, 2)
         if sumsq.shape[0] != T or not sumsq.is_contiguous():
@@ -520,10 +520,15 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
     return out
 
 
-#: Steps of at most this many tokens can run a layer's RMS norms inside the products around
-#: them (see ``linear_bf16``): the products of such a step run swapped, tokens on one narrow
-#: tile, on this package's kernel.
-DEFERRED_NORM_TOKENS = 32
+#: Steps of at most this many tokens run a layer's RMS norms inside the products around them
+#: (see ``linear_bf16``): the products of such a step run swapped, tokens on one narrow tile,
+#: on this package's kernel.  The epilogues take up to DEFERRED_NORM_MOST tokens, but their
+#: cost grows with the tokens while a norm launch's does not.  Measured, milliseconds a
+#: decode step with the norm launches against without: Llama-3.1-8B sizes 4.01 / 3.89 at 8
+#: requests, 4.87 / 4.86 at 16, 5.83 / 5.73 at 24, 6.70 / 6.88 at 32; Qwen2.5-7B sizes 3.38 /
+#: 3.22 at 8, 4.52 / 4.58 at 32; Qwen2.5-0.5B sizes 1.06 / 1.08 at 24, 1.12 / 1.14 at 32.
+DEFERRED_NORM_TOKENS = 16
+DEFERRED_NORM_MOST = 32
 
 
 def deferred_norm_fits(tokens: int, *weights: torch.Tensor) -> bool:

@@ -202,6 +202,7 @@ def test_two_products_with_the_norm_between_them_folded_in():
     normed = new * torch.rsqrt((new ** 2).mean(1, keepdim=True) + eps) * norm_w.double()
     gate, up = normed @ wgu.double()[:I].T, normed @ wgu.double()[I:].T
     _close(got, gate * torch.sigmoid(gate) * up, scale=2.0)
+    assert ops().DEFERRED_NORM_TOKENS <= ops().DEFERRED_NORM_MOST == 32
     with pytest.raises(ops().KernelError):
         ops().linear_bf16(torch.zeros(40, H, dtype=torch.bfloat16, device=DEV), wo.to(DEV),
                           residual=torch.zeros(40, H, device=DEV))

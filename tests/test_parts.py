@@ -141,13 +141,15 @@ def test_embedding_and_head_parts():
 # ---------------------------------------------------------------------- the schedule is data
 @pytest.mark.parametrize("lens", [[20], [1, 1, 1, 1, 1, 1, 1], [9, 1, 12]])
 @pytest.mark.parametrize("bias", [False, True])
-def test_the_parts_hand_a_norm_to_one_another(lens, bias):
+def test_the_parts_hand_a_norm_to_one_another(lens, bias, monkeypatch):
     """Steps of few tokens in bfloat16: the attention part adds its output into the residual
     and leaves the feed-forward's norm all but done (a DeferredNorm: rows times the norm
     weight, partial sums of squares); the feed-forward takes it, applies 1 / rms inside its
     first product and adds into the residual too.  Against the plain functions."""
+    from helios_b200.csrc import ops
     from helios_b200.parts import DeferredNorm, GQAAttention, LayerCache, RMSNorm, RotaryEncoding, SwiGLU
 
+    monkeypatch.setattr(ops, "DEFERRED_NORM_TOKENS", ops.DEFERRED_NORM_MOST)   # also the 32-token tile
     H, I, nh, nkv, hd, page, eps = 2304, 640, 6, 2, 64, 8, 1e-5     # wider than the narrow-model kernels take
     g = torch.Generator().manual_seed(len(lens) + bias)
     attn, ffn = GQAAttention(H, nh, nkv, hd, 1 / math.sqrt(hd), bias), SwiGLU(H, I)
