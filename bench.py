@@ -416,15 +416,29 @@ def run_micro(args):
 
     if args.micro == "gemm":
         shapes = {"gate_up": (2 * I, H), "down": (H, I), "qkv": ((nh + 2 * nkv) * hd, H), "o": (H, nh * hd)}
+        token_counts = [int(t) for t in args.micro_tokens.split(",")] if args.micro_tokens else (8, 16, 32, 64, 128)
         for name, (rows, cols) in shapes.items():
+            if args.micro_case and args.micro_case != name:
+                continue
             w = weights(rows, cols)
-            for T in (8, 16, 32, 64, 128):
+            for T in token_counts:
                 x = torch.randn(T, cols, device=dev).bfloat16()
                 if name == "gate_up":
                     us = chain_us(lambda i: ops.linear_swiglu(x, w[i % len(w)]))
                 else:
                     us = chain_us(lambda i: ops.linear(x, w[i % len(w)]))
                 report(name, us, rows * cols * 2, tokens=T)
+                if T <= ops.DEFERRED_NORM_MOST:
+                    # the epilogues that replace the norm launches in steps of few tokens
+                    if name in ("o", "down"):
+                        res, nw = torch.randn(T, rows, device=dev), torch.ones(rows, device=dev)
+                        us = chain_us(lambda i: ops.linear_bf16(x, w[i % len(w)], residual=res, norm_weight=nw))
+                        report(name + "_into_residual_with_next_norm", us, rows * cols * 2, tokens=T)
+                    else:
+                        ss = torch.rand(T, 8 * -(-cols // 128), device=dev)
+                        us = chain_us(lambda i: ops.linear_bf16(x, w[i % len(w)], glu=name == "gate_up",
+                                                                sumsq=ss, eps=1e-5))
+                        report(name + "_with_rms_factor", us, rows * cols * 2, tokens=T)
             del w
     elif args.micro == "small_step":
         T = args.batch
@@ -497,6 +511,8 @@ def main():
     ap.add_argument("--micro", default=None, choices=["gemm", "small_step", "attention_decode"],
                     help="time one kind of kernel as a chain in a captured graph instead of the step "
                          "(sizes of --model; --batch tokens or requests, --context keys)")
+    ap.add_argument("--micro-case", default=None, help="--micro gemm: one of gate_up, down, qkv, o")
+    ap.add_argument("--micro-tokens", default=None, help="--micro gemm: token counts, e.g. 8,16")
     ap.add_argument("--micro-launches", type=int, default=48,
                     help="launches in the chain; below 8 they run plainly, for a profiler")
     args = ap.parse_args()
