@@ -526,6 +526,34 @@ int launch_decode(void* out, float* part_o, float* part_ml, const void* q, int q
   return hb_check_launch();
 }
 
+// Clusters of `cluster_size` decode blocks the device keeps resident at once (-1 if the
+// query fails): whole clusters are placed inside a GPC, so this can be fewer than the blocks
+// that would fit one by one.
+template <int HD>
+int decode_max_clusters(int cluster_size) {
+  constexpr int RS = HD + 8;
+  size_t smem = (size_t)DEC_WARPS * DEC_STAGES * 2 * DEC_TILE * RS * sizeof(__nv_bfloat16);
+  const size_t red = (size_t)(DEC_WARPS * 16 * (HD + 2) + 16 * (HD + 2)) * sizeof(float);
+  if (red > smem) smem = red;
+  auto kernel = decode_attention_kernel<HD>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    return -1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(cluster_size, 1, 1);
+  cfg.blockDim = dim3(DEC_WARPS * 32);
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster_size;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) return -1;
+  return n;
+}
+
 template <int HD>
 int launch_prefill(void* out, const void* q, int q_stride, const void* k_pages, const void* v_pages,
                    const int* block_table, int bt_stride, const int* q_tiles, int n_tiles,
@@ -587,6 +615,11 @@ HB_EXPORT int hb_attention_decode_bf16(void* out, float* part_o, float* part_ml,
                                               block_table, bt_stride, positions, S, nh, nkv,
                                               page_size, window, scale, n_splits, rot_cos, rot_sin,
                                               write_cache, stream));
+}
+
+HB_EXPORT int hb_attention_decode_max_clusters(int hd, int cluster_size) {
+  if (cluster_size < 1 || cluster_size > 8) return -1;
+  HB_DISPATCH_HD(hd, return decode_max_clusters<HD>(cluster_size));
 }
 
 // Prefill / mixed: q_tiles holds (request, first local token) for every tile of

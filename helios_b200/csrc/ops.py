@@ -825,6 +825,22 @@ def _wave_splits(blocks: int, slots: int, most: int) -> int:
     return max(1, min(most, slots // max(1, blocks)))
 
 
+_decode_clusters = {}
+
+
+def decode_cluster_capacity(head_dim: int, size: int) -> int:
+    """Clusters of ``size`` decode-attention blocks the device keeps resident at once (the
+    occupancy calculator knows how the SMs are spread over the GPCs, which bounds whole
+    clusters: 71 clusters of 4 on a B200 where 74 would fit block by block)."""
+    key = (head_dim, size)
+    if key not in _decode_clusters:
+        n = -1
+        if torch.cuda.is_available() and head_dim in TILED_HEAD_DIMS and 1 <= size <= 8:
+            n = int(load_library("attention_bf16").hb_attention_decode_max_clusters(head_dim, size))
+        _decode_clusters[key] = n if n > 0 else (2 * sm_count()) // size
+    return _decode_clusters[key]
+
+
 def decode_splits(num_seqs: int, num_kv_heads: int, max_context: int, head_dim: int = 128) -> int:
     """Slices of the context per (request, KV head) of the decode attention kernel, by a cost
     model fitted to measurements (64 requests x 8 KV heads of 128 at contexts 1,024 and 4,096;
@@ -836,7 +852,10 @@ def decode_splits(num_seqs: int, num_kv_heads: int, max_context: int, head_dim: 
     fixed = 176.0 * 128.0 / max(1, head_dim)
     best, best_cost = 1, None
     for s in range(1, max(1, min(32, max_context // 128)) + 1):
-        cost = -(-blocks * s // slots) * (max_context / s + fixed)
+        # 2 to 8 slices run as one cluster per (request, KV head) while all clusters are
+        # resident at once; otherwise block by block, with a merge kernel
+        rounds = 1 if (1 < s <= 8 and blocks <= decode_cluster_capacity(head_dim, s)) else -(-blocks * s // slots)
+        cost = rounds * (max_context / s + fixed)
         if best_cost is None or cost < best_cost * 0.94:      # fewer slices unless clearly better
             best, best_cost = s, cost
     return best
@@ -887,7 +906,7 @@ def attention_decode_bf16(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: tor
     part_o = part_ml = None
     # slices as one cluster only while all blocks are resident at once: with several rounds
     # of blocks, clusters (whose blocks must start together) cost more than the merge kernel
-    one_round = S * num_kv_heads * n_splits <= 2 * sm_count()
+    one_round = n_splits <= 8 and S * num_kv_heads <= decode_cluster_capacity(head_dim, n_splits)
     if n_splits > 8 or (n_splits > 1 and not (ATTENTION_CLUSTER_MERGE and one_round)):
         part_o = torch.empty((S, num_heads, n_splits, head_dim), dtype=torch.float32, device=qkv.device)
         part_ml = torch.empty((S, num_heads, n_splits, 2), dtype=torch.float32, device=qkv.device)
