@@ -314,6 +314,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       if (EPI == EPI_GLU) {
         constexpr int HALF = SWAP ? BN : BN / 2;   // columns of the gate accumulator
         for (int c = 0; c < HALF; c += 16) {
+          if (SWAP && tile_b * BN + c >= args.T) break;           // columns without tokens
           float g[16], u[16];
           load_chunk(c, g);
           load_chunk(HALF + c, u);
@@ -322,8 +323,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             for (int j = 0; j < 16; ++j) { g[j] *= col_scale[c + j]; u[j] *= col_scale[c + j]; }
           }
           float val[16];
+          // (a row or column beyond the last token holds zeros, and 0 / x takes the division's
+          // slow path: the whole warp would wait for it)
+          const bool idle_row = !SWAP && tile_a * BM + r >= args.T;
 #pragma unroll
-          for (int j = 0; j < 16; ++j) val[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
+          for (int j = 0; j < 16; ++j) {
+            const bool idle = SWAP ? tile_b * BN + c + j >= args.T : idle_row;
+            val[j] = idle ? 0.f : g[j] / (1.f + __expf(-g[j])) * u[j];
+          }
           if (SWAP) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) store(tile_b * BN + c + j, tile_a * BM + r, val[j]);
@@ -469,11 +476,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       constexpr int GLU_SHIFT = (EPI == EPI_GLU) ? (SWAP ? BN : BN / 2) : 0;
       const uint32_t part_addr = base;
       const int S = args.k_splits;
-      const int total = OUT_COLS * BM;
+      // swapped: only the columns that hold tokens are shared out (the others are padding of
+      // the MMA's N axis; sums of zeros, whose SwiGLU would also take the slow path of the
+      // division)
+      const int cols = SWAP ? max(0, min(OUT_COLS, args.T - tile_b * BN)) : OUT_COLS;
+      const int total = cols * BM;
       const int per = (total + S - 1) / S;
       const int e_begin = split * per, e_end = min(total, e_begin + per);
       for (int e = e_begin + (int)threadIdx.x - 64; e < e_end; e += 128) {
         const int c = e / BM, rr = e - c * BM;
+        if (!SWAP && tile_a * BM + rr >= args.T) continue;        // a row beyond the last token
         // all loads first (a cluster has at most 8 blocks), then the sum in slice order
         float gv[8], uv[8];
 #pragma unroll
@@ -655,8 +667,10 @@ gemm_bf16_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           float g[16], u[16];
           tmem_ld16(taddr + c, g);
           tmem_ld16(taddr + 128 + c, u);
+          if (t < args.T) {       // rows beyond the last token hold zeros: 0 / x is the division's slow path
 #pragma unroll
-          for (int i = 0; i < 16; ++i) val[i] = g[i] / (1.f + __expf(-g[i])) * u[i];
+            for (int i = 0; i < 16; ++i) val[i] = g[i] / (1.f + __expf(-g[i])) * u[i];
+          }
         } else {
           tmem_ld16(taddr + c, val);
         }

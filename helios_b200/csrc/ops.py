@@ -542,17 +542,25 @@ def deferred_norm_fits(tokens: int, *weights: torch.Tensor) -> bool:
 
 #: Between the decode kernel's best range (up to 32 tokens: weights streamed once with the
 #: tokens on a narrow MMA N axis, a deep ring of weight stages) and the prefill kernel's (pairs
-#: of SMs on 256x256 tiles; on a par with the library above 512 tokens) plain products (no
+#: of SMs on 256x256 tiles, which need a few hundred tiles to fill 74 pairs) plain products (no
 #: bias, bfloat16 out) go to the library (cuBLAS through torch), which the reference uses for
-#: every product (python/helios/exec/model.py:170-181): from 33 tokens on a stage of the decode
+#: every product (python/helios/exec/model.py:170-181).  From 33 tokens on a stage of the decode
 #: kernel holds 8-16 KB of tokens beside its 16 KB of weights, the ring gets shallow, and the
 #: library is ahead (Llama-3.1-8B sizes at 64 tokens, microseconds in a chain: q|k|v 15.2
-#: against 11.5, O 11.1 against 10.0, down 24.3 against 24.2, gate|up + SwiGLU 54.1 against
-#: 46.9 with the gate as a kernel of its own; a decode step of 64 requests 6,300-6,460 against
-#: 6,690 tokens/s); from 129 to 512 tokens most SMs of the two-SM kernel have no tile.
-#: Products with a bias or float32 logits, SwiGLU from 384 tokens up, and everything up to 32
-#: tokens always run on this package's kernels.  (0, 0) turns the library off.
-GEMM_LIBRARY_TOKEN_RANGE = (33, 512)
+#: against 11.5, O 11.1 against 10.0, down 24.3 against 24.2; a decode step of 64 requests
+#: 6,300-6,460 against 6,690 tokens/s); from 129 tokens on the two-SM kernel has too few tiles
+#: (same sizes, this package's kernel against the library: down 88 / 61 at 513 tokens, 82 / 69
+#: at 768, 86 / 83 at 1,024, 171 / 120 at 1,536 with 80 tiles on 74 pairs, 168 / 156 at 2,048,
+#: 263 / 271 at 3,072; O 28 / 22, 29 / 22, 30 / 27, 54 / 43, 53 / 50, 84 / 82).  Products with
+#: a bias or float32 logits, and everything up to 32 tokens, always run on this package's
+#: kernels.  (0, 0) turns the library off.
+GEMM_LIBRARY_TOKEN_RANGE = (33, 1536)
+#: gate|up with SwiGLU runs fused on this package's kernels except in these token ranges,
+#: where the library's plain product and a gate kernel are ahead (Llama-3.1-8B sizes, fused
+#: against library + gate: 73 / 59 at 96 tokens, 82 / 57 at 128; 59 / 67 at 160, 66 / 76 at
+#: 256: one full tile of the two-SM kernel; 110 / 93 at 320, 110 / 104 at 384: a second tile
+#: that is mostly empty; 111 / 129 at 448, 112 / 141 at 512, 150 / 188 at 640)
+GEMM_LIBRARY_GLU_TOKENS = ((33, 128), (257, 383))
 #: The library chooses its kernel per shape, which takes about a millisecond of host time
 #: the first time a shape is seen; token counts are rounded up to a multiple of this (on a
 #: padded copy of the rows) so that a serving run meets a handful of shapes, not hundreds.
@@ -560,15 +568,18 @@ GEMM_LIBRARY_TOKEN_STEP = 64
 #: Weight matrices of at most this many bytes (the products of models about 1,000 wide: 2 to
 #: 17 MB) go to the library from GEMM_LIBRARY_SMALL_TOKENS[0] tokens on: a product that short
 #: is bound by the kernel's own latency, where the tensor-memory kernels (set-up, a cluster for
-#: the split reduction) lose to the library's plain ones.  Measured at Qwen2.5-0.5B sizes,
-#: microseconds a launch in a chain, this package's kernel against the library, at 24 / 64 /
-#: 256 tokens: q|k|v 5.0 / 7.2 / 10.9 against 4.0 / 3.9 / 4.2; down 6.8 / 8.5 / 29.7 against
-#: 9.4 / 8.6 / 8.8; gate|up with SwiGLU 14.4 / 18.9 / 16.5 against 8.6 / 8.7 / 12.8 (library
-#: product + gate kernel).  Up to 32 tokens this package's kernels win as a whole (a step of
-#: 32 requests: 28,300 against 25,900 tokens/s), up to 16 the fused few-token kernels run.
-#: 0 bytes turns it off.
+#: the split reduction) lose to the library's plain ones, and with 896 output features the
+#: two-SM kernel has 4 tiles a 256 tokens.  Measured at Qwen2.5-0.5B sizes, microseconds a
+#: launch in a chain, this package's kernel against the library, at 24 / 64 / 256 tokens: q|k|v
+#: 5.0 / 7.2 / 10.9 against 4.0 / 3.9 / 4.2; down 6.8 / 8.5 / 29.7 against 9.4 / 8.6 / 8.8 (and
+#: 30 / 10 at 1,024, 31 / 15 at 2,048, 32 / 27 at 4,096, 64 / 64 at 8,192); gate|up with SwiGLU
+#: 14.4 / 18.9 / 16.5 against 8.6 / 8.7 / 12.8 (library product + gate kernel; 26 / 26 at 768,
+#: 56 / 58 at 2,048, 96 / 117 at 4,096: GEMM_LIBRARY_SMALL_GLU_TOKENS).  Up to 32 tokens this
+#: package's kernels win as a whole (a step of 32 requests: 28,300 against 25,900 tokens/s),
+#: up to 16 the fused few-token kernels run.  0 bytes turns it off.
 GEMM_LIBRARY_SMALL_WEIGHT_BYTES = 20 * 1024 * 1024
-GEMM_LIBRARY_SMALL_TOKENS = (33, 512)
+GEMM_LIBRARY_SMALL_TOKENS = (33, 4096)
+GEMM_LIBRARY_SMALL_GLU_TOKENS = (33, 512)
 
 
 def _library_range(tokens: int) -> bool:
@@ -576,8 +587,8 @@ def _library_range(tokens: int) -> bool:
     return lo <= tokens <= hi
 
 
-def _small_weight_library(tokens: int, weight: torch.Tensor) -> bool:
-    lo, hi = GEMM_LIBRARY_SMALL_TOKENS
+def _small_weight_library(tokens: int, weight: torch.Tensor, glu: bool = False) -> bool:
+    lo, hi = GEMM_LIBRARY_SMALL_GLU_TOKENS if glu else GEMM_LIBRARY_SMALL_TOKENS
     return lo <= tokens <= hi and \
         weight.numel() * weight.element_size() <= GEMM_LIBRARY_SMALL_WEIGHT_BYTES
 
@@ -615,10 +626,10 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     product's epilogue in bfloat16, two kernels otherwise."""
     if x.dtype == torch.bfloat16 and tc_gemm_supported(x, w_gate_up):
         T = x.shape[0]
-        if _small_weight_library(T, w_gate_up):
+        if _small_weight_library(T, w_gate_up, glu=True) or \
+                any(lo <= T <= hi for lo, hi in GEMM_LIBRARY_GLU_TOKENS):
             return silu_mul(_library_linear(x, w_gate_up, None))
-        if not (_library_range(T) and T < 384):
-            return linear_bf16(x, w_gate_up, glu=True)
+        return linear_bf16(x, w_gate_up, glu=True)
     return silu_mul(linear(x, w_gate_up))
 
 

@@ -134,11 +134,12 @@ def test_a_long_portion_beside_decoded_tokens_at_the_benchmarks_sizes(graphs):
     ops.check_kernel_errors()
 
 
-@pytest.mark.parametrize("n", [32, 33, 128, 192])
+@pytest.mark.parametrize("n", [32, 33, 128, 192, 257, 400])
 def test_a_portion_on_either_side_of_the_library_boundary(n):
-    """Up to 32 tokens the products run on this package's decode kernel, from 33 to 512 the
+    """Up to 32 tokens the products run on this package's decode kernel, from 33 to 1,536 the
     plain ones go to the library: a request's bfloat16 numbers are not bit-equal across that
-    line, but either side must match the plain model."""
+    line, but either side must match the plain model.  (The SwiGLU product changes sides at
+    129, 257 and 384 tokens.)"""
     from helios_b200.engine.batch import StepEntry
     from helios_b200.engine.core import EngineCore
     from helios_b200.engine.model import DecoderModel
