@@ -483,30 +483,43 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       const int total = cols * BM;
       const int per = (total + S - 1) / S;
       const int e_begin = split * per, e_end = min(total, e_begin + per);
-      for (int e = e_begin + (int)threadIdx.x - 64; e < e_end; e += 128) {
-        const int c = e / BM, rr = e - c * BM;
-        if (!SWAP && tile_a * BM + rr >= args.T) continue;        // a row beyond the last token
-        // all loads first (a cluster has at most 8 blocks), then the sum in slice order
-        float gv[8], uv[8];
+      // two elements a thread and pass: the loads of both (from up to 8 peers each) go out
+      // before either sum is used
+      for (int e0 = e_begin + (int)threadIdx.x - 64; e0 < e_end; e0 += 256) {
+        float gv[2][8], uv[2][8];
+        bool live[2];
 #pragma unroll
-        for (int sp = 0; sp < 8; ++sp) {
-          gv[sp] = sp < S ? ld_peer_smem(part_addr + (uint32_t)(c * BM + rr) * 4u, sp) : 0.f;
-          uv[sp] = (EPI == EPI_GLU && sp < S)
-                       ? ld_peer_smem(part_addr + (uint32_t)((GLU_SHIFT + c) * BM + rr) * 4u, sp) : 0.f;
+        for (int k = 0; k < 2; ++k) {
+          const int e = e0 + k * 128;
+          const int c = e / BM, rr = e - c * BM;
+          live[k] = e < e_end && (SWAP || tile_a * BM + rr < args.T);     // not a row beyond the last token
+#pragma unroll
+          for (int sp = 0; sp < 8; ++sp) {
+            const bool on = live[k] && sp < S;
+            gv[k][sp] = on ? ld_peer_smem(part_addr + (uint32_t)(c * BM + rr) * 4u, sp) : 0.f;
+            uv[k][sp] = (EPI == EPI_GLU && on)
+                            ? ld_peer_smem(part_addr + (uint32_t)((GLU_SHIFT + c) * BM + rr) * 4u, sp) : 0.f;
+          }
         }
-        float g = 0.f, u = 0.f;
 #pragma unroll
-        for (int sp = 0; sp < 8; ++sp) { g += gv[sp]; u += uv[sp]; }
-        if (SWAP && args.sumsq_in != nullptr) { g *= col_scale[c]; u *= col_scale[c]; }
-        float val = g;
-        if (EPI == EPI_GLU) val = g / (1.f + __expf(-g)) * u;
-        int t, n;
-        if (SWAP) { t = tile_b * BN + c; n = tile_a * BM + rr; }
-        else { t = tile_a * BM + rr; n = tile_b * OUT_COLS + c; }
-        if (t < args.T && n < args.N) {
-          if (args.bias) val += args.bias[n];
-          if (args.out_f32) reinterpret_cast<float*>(args.out)[(size_t)t * args.ldo + n] = val;
-          else reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)t * args.ldo + n] = __float2bfloat16_rn(val);
+        for (int k = 0; k < 2; ++k) {
+          if (!live[k]) continue;
+          const int e = e0 + k * 128;
+          const int c = e / BM, rr = e - c * BM;
+          float g = 0.f, u = 0.f;                       // the sum in slice order
+#pragma unroll
+          for (int sp = 0; sp < 8; ++sp) { g += gv[k][sp]; u += uv[k][sp]; }
+          if (SWAP && args.sumsq_in != nullptr) { g *= col_scale[c]; u *= col_scale[c]; }
+          float val = g;
+          if (EPI == EPI_GLU) val = g / (1.f + __expf(-g)) * u;
+          int t, n;
+          if (SWAP) { t = tile_b * BN + c; n = tile_a * BM + rr; }
+          else { t = tile_a * BM + rr; n = tile_b * OUT_COLS + c; }
+          if (t < args.T && n < args.N) {
+            if (args.bias) val += args.bias[n];
+            if (args.out_f32) reinterpret_cast<float*>(args.out)[(size_t)t * args.ldo + n] = val;
+            else reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)t * args.ldo + n] = __float2bfloat16_rn(val);
+          }
         }
       }
     }
