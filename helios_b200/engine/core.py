@@ -13,6 +13,13 @@ from .batch import MetaLayout, SeqSlice, StepEntry, build_context, context_from_
 from .model import DecoderModel
 
 
+def _numel(shape) -> int:
+    n = 1
+    for d in shape:
+        n *= int(d)
+    return n
+
+
 class _StepGraph:
     """A captured step for a fixed number of requests and tokens (both padded) and fixed
     block-table widths: static inputs, one CUDA graph, static logits (one row a request).
@@ -130,6 +137,12 @@ class EngineCore:
     #: ... except steps that fill one of these counts to seven eighths or more: the full
     #: portions of a long prompt under the usual token budgets, which come many times in a row
     GRAPH_FULL_TOKEN_BUCKETS = (1024, 2048, 4096, 8192)
+    #: A small model's steps of some hundred tokens are over on the device before the host has
+    #: launched them kernel by kernel (Qwen2.5-0.5B sizes, 768 tokens: 3.4 ms against 1.5 ms at
+    #: 512 as a graph), and padding them costs little: models of at most this many parameters
+    #: take these token counts too.
+    SMALL_MODEL_PARAMETERS = 2_000_000_000
+    SMALL_MODEL_TOKEN_BUCKETS = (640, 768, 896, 1024, 1280, 1536, 1792, 2048)
     MAX_FULL_GRAPHS = 8
     FULL_GRAPH_EAGER_RUNS = 6
 
@@ -162,6 +175,10 @@ class EngineCore:
         self.graph_table_widths = [-(-self.graph_max_context // page_size)] * len(self.cache.groups)
         self._graphs = {}
         self._bucket_seen = {}
+        parameters = sum(_numel(spec.shape) for _prefix, part in model.plan.named_parts()
+                         for spec in part.weight_specs().values())
+        self.graph_token_buckets = self.GRAPH_TOKEN_BUCKETS + (
+            self.SMALL_MODEL_TOKEN_BUCKETS if parameters <= self.SMALL_MODEL_PARAMETERS else ())
 
     @staticmethod
     def padded_requests(n: int) -> int:
@@ -290,9 +307,9 @@ class EngineCore:
         else:
             if token_feed is not None:
                 return False, None
-            if num_seqs == S and T not in self.GRAPH_TOKEN_BUCKETS:
+            if num_seqs == S and T not in self.graph_token_buckets:
                 num_seqs = self.padded_requests(S + 1)   # a padding request has to take the spare tokens
-            fits = [b for b in self.GRAPH_TOKEN_BUCKETS if b >= T + (num_seqs - S)]
+            fits = [b for b in self.graph_token_buckets if b >= T + (num_seqs - S)]
             if not fits:
                 # a full portion: the requests as they are, and one padding request only if
                 # tokens are to spare (such steps come with the same number of requests many
@@ -301,7 +318,7 @@ class EngineCore:
                 if fits:
                     num_seqs = S if fits[0] == T else S + 1
                     if (num_seqs, fits[0]) not in self._graphs and \
-                            sum(t > self.GRAPH_TOKEN_BUCKETS[-1] for _s, t in self._graphs) >= self.MAX_FULL_GRAPHS:
+                            sum(t > self.graph_token_buckets[-1] for _s, t in self._graphs) >= self.MAX_FULL_GRAPHS:
                         return False, None
             if not fits or fits[0] > self.graph_max_context:
                 return False, None
@@ -314,7 +331,7 @@ class EngineCore:
             # first time: run eagerly (also warms everything up).  Capturing a step of
             # thousands of tokens costs as much as it saves in a hundred replays: only a
             # shape that keeps coming is worth it.
-            eager_runs = 1 if num_tokens <= self.GRAPH_TOKEN_BUCKETS[-1] else self.FULL_GRAPH_EAGER_RUNS
+            eager_runs = 1 if num_tokens <= self.graph_token_buckets[-1] else self.FULL_GRAPH_EAGER_RUNS
             if seen < eager_runs:
                 return False, None
             g = self._graphs[key] = _StepGraph(self, num_seqs, num_tokens)
