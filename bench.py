@@ -440,21 +440,6 @@ def run_micro(args):
                                                                 sumsq=ss, eps=1e-5))
                         report(name + "_with_rms_factor", us, rows * cols * 2, tokens=T)
             del w
-    elif args.micro == "small_step":
-        T = args.batch
-        res, nw = torch.randn(T, H, device=dev), torch.ones(H, device=dev)
-        cases = {"o_into_residual": (H, nh * hd), "down_into_residual": (H, I), "norm_gate_up_swiglu": (2 * I, H)}
-        for name, (rows, cols) in cases.items():
-            w = weights(rows, cols)
-            x = torch.randn(T, cols, device=dev).bfloat16()
-            if name == "norm_gate_up_swiglu":
-                us = chain_us(lambda i: ops.small_norm_swiglu(res, nw, 1e-6, w[i % len(w)]))
-            else:
-                us = chain_us(lambda i: ops.small_linear_residual(res, x, w[i % len(w)]))
-            report(name, us, rows * cols * 2, tokens=T)
-            del w
-        delta = torch.randn(T, H, device=dev).bfloat16()
-        report("add_rmsnorm", chain_us(lambda i: ops.add_rmsnorm(res, delta, nw, 1e-6, torch.bfloat16)), 0, tokens=T)
     else:
         B, ctx, page = args.batch, args.context, 16
         pages = B * (ctx // page)
@@ -508,7 +493,7 @@ def main():
     ap.add_argument("--max-prompt", type=int, default=4096)
     ap.add_argument("--budget", type=int, default=2048, help="tokens a step (chunked prefill)")
     ap.add_argument("--new-tokens", type=int, default=256)
-    ap.add_argument("--micro", default=None, choices=["gemm", "small_step", "attention_decode"],
+    ap.add_argument("--micro", default=None, choices=["gemm", "attention_decode"],
                     help="time one kind of kernel as a chain in a captured graph instead of the step "
                          "(sizes of --model; --batch tokens or requests, --context keys)")
     ap.add_argument("--micro-case", default=None, help="--micro gemm: one of gate_up, down, qkv, o")

@@ -38,7 +38,6 @@ LIBRARIES: Dict[str, str] = {
     "gemm_f32": "gemm_f32.cu",
     "gemm_bf16": "gemm_bf16.cu",
     "gemm_bf16_noalloc": "gemm_bf16_noalloc.cu",
-    "small_step": "small_step.cu",
     "sampling": "sampling.cu",
 }
 _HEADERS = ["common.cuh", "tcgen05.cuh"]

@@ -99,7 +99,7 @@ def linear_libraries(dtype: torch.dtype, width: int = 0):
     """Libraries the matrix products of a model of this dtype and width run on."""
     if dtype == torch.float32:
         return ("gemm_f32",)
-    return ("gemm_bf16", "small_step") if 0 < width <= SMALL_STEP_NARROW_WIDTH else ("gemm_bf16",)
+    return ("gemm_bf16",)
 
 
 def attention_libraries(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int):
@@ -637,134 +637,6 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
             return silu_mul(_library_linear(x, w_gate_up, None))
         return linear_bf16(x, w_gate_up, glu=True)
     return silu_mul(linear(x, w_gate_up))
-
-
-# ------------------------------------------------------------------ steps of very few tokens
-#: Steps of at most SMALL_STEP_TOKENS_NARROW tokens run a layer as five fused launches
-#: (``small_step.cu``) instead of eight where the residual stream is at most
-#: SMALL_STEP_NARROW_WIDTH wide: there a step is bound by the number of dependent launches.
-#: Wider models stream their weights faster through the tcgen05 products (measured at
-#: Llama-3.1-8B sizes, one token: 6.3 against 3.4 ms a step), so for them the limit,
-#: SMALL_STEP_TOKENS, is 0: never.
-SMALL_STEP_TOKENS = 0
-SMALL_STEP_TOKENS_NARROW = 16
-SMALL_STEP_NARROW_WIDTH = 2048
-
-
-def small_step_fits(tokens: int, width: int, *ks: int) -> bool:
-    """Whether a step of ``tokens`` tokens of a model ``width`` wide takes the fused
-    few-token kernels; ``ks`` are the reduction lengths of its products."""
-    limit = SMALL_STEP_TOKENS_NARROW if width <= SMALL_STEP_NARROW_WIDTH else SMALL_STEP_TOKENS
-    if not 0 < tokens <= min(limit, 16):
-        return False
-    # the step's activations must fit a block's shared memory as bfloat16 rows
-    most = _small_max_k.get(tokens)
-    if most is None:
-        lib = load_library("small_step")
-        most = _small_max_k[tokens] = int(lib.hb_small_step_max_k(int(tokens)))
-    return all(k % 8 == 0 and k <= most for k in ks)
-
-
-_small_max_k = {}
-
-
-def _small_tiles_per_block(tiles: int) -> int:
-    """Tiles of 8 weight rows a block takes (1, 2 or 4): the fewest that give the fewest
-    rounds of blocks, two blocks being resident per SM."""
-    resident = 2 * sm_count()
-    rounds = {nt: -(-(-(-tiles // nt)) // resident) for nt in (1, 2, 4)}
-    return min((1, 2, 4), key=lambda nt: (rounds[nt], nt))
-
-
-def small_linear_residual(residual: torch.Tensor, x: torch.Tensor, weight: torch.Tensor) -> None:
-    """residual [T, N] (float32, in place) += x [T, K] weight[N, K]^T for at most 16 tokens."""
-    _check(residual, "residual", torch.float32, 2)
-    _check(x, "x", torch.bfloat16, 2)
-    _check(weight, "weight", torch.bfloat16, 2)
-    T, K = x.shape
-    N = weight.shape[0]
-    if weight.shape[1] != K or tuple(residual.shape) != (T, N):
-        raise KernelError(f"residual {tuple(residual.shape)}, x {tuple(x.shape)} and weight "
-                          f"{tuple(weight.shape)} do not fit")
-    if T > 16 or K % 8:
-        raise KernelError(f"the few-token product takes at most 16 tokens and K % 8 == 0, got {T}, {K}")
-    f = _fn("small_step", "hb_small_linear_residual",
-            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
-    _run(f(_p(residual), _p(x), _p(weight), T, N, K, _small_tiles_per_block(-(-N // 8)), _stream()),
-         "small_linear_residual")
-
-
-def small_norm_swiglu(residual: torch.Tensor, norm_weight: torch.Tensor, eps: float,
-                      w_gate_up: torch.Tensor) -> torch.Tensor:
-    """silu(h gate^T) * (h up^T) with h = RMSNorm(residual) (float32 [T, K], at most 16 tokens)
-    and ``w_gate_up`` = [gate rows; up rows]; bfloat16 [T, I]."""
-    _check(residual, "residual", torch.float32, 2)
-    _check(norm_weight, "norm_weight", torch.float32, 1)
-    _check(w_gate_up, "w_gate_up", torch.bfloat16, 2)
-    T, K = residual.shape
-    rows = w_gate_up.shape[0]
-    if w_gate_up.shape[1] != K or norm_weight.numel() != K or rows % 2:
-        raise KernelError(f"residual {tuple(residual.shape)}, norm weight {norm_weight.numel()} and "
-                          f"w_gate_up {tuple(w_gate_up.shape)} do not fit")
-    if T > 16 or K % 8:
-        raise KernelError(f"the few-token product takes at most 16 tokens and K % 8 == 0, got {T}, {K}")
-    inner = rows // 2
-    out = torch.empty((T, inner), dtype=torch.bfloat16, device=residual.device)
-    f = _fn("small_step", "hb_small_norm_swiglu",
-            [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
-    _run(f(_p(out), _p(residual), _p(norm_weight), float(eps), _p(w_gate_up), T, inner, K, inner,
-           _small_tiles_per_block(-(-inner // 4)), _stream()), "small_norm_swiglu")
-    return out
-
-
-def small_norm_qkv_rope(residual: torch.Tensor, norm_weight: torch.Tensor, eps: float,
-                        w_qkv: torch.Tensor, b_qkv: Optional[torch.Tensor], cos: torch.Tensor,
-                        sin: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
-                        block_table: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
-                        num_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
-                        write_cache: bool = True) -> torch.Tensor:
-    """RMSNorm of the residual rows, the fused q|k|v projection (+ bias), the rotation of q
-    and k, and the write of k and v into the tokens' cache slots, for at most 16 tokens.
-    Returns [T, (nh + 2 nkv) hd] of which the q columns are filled (and the k and v columns
-    when nothing is written to the cache)."""
-    _check(residual, "residual", torch.float32, 2)
-    _check(norm_weight, "norm_weight", torch.float32, 1)
-    _check(w_qkv, "w_qkv", torch.bfloat16, 2)
-    T, K = residual.shape
-    width = (num_heads + 2 * num_kv_heads) * head_dim
-    if tuple(w_qkv.shape) != (width, K) or norm_weight.numel() != K:
-        raise KernelError(f"w_qkv {tuple(w_qkv.shape)} is not [(nh + 2 nkv) hd, K] = [{width}, {K}]")
-    if T > 16 or K % 8 or head_dim % 8:
-        raise KernelError("the few-token projection takes at most 16 tokens, K % 8 == 0 and head_dim % 8 == 0")
-    if b_qkv is not None:
-        _check(b_qkv, "b_qkv", torch.float32, 1)
-        if b_qkv.numel() != width:
-            raise KernelError(f"bias has {b_qkv.numel()} entries for {width} outputs")
-    _check(cos, "cos", torch.float32, 2)
-    _check(sin, "sin", torch.float32, 2)
-    if tuple(cos.shape) != (T, head_dim // 2) or cos.shape != sin.shape:
-        raise KernelError(f"cos/sin tables {tuple(cos.shape)} are not [{T}, {head_dim // 2}]")
-    _check(positions, "positions", torch.int32, 1)
-    _check(seq_of_token, "seq_of_token", torch.int32, 1)
-    _check(block_table, "block_table", torch.int32, 2)
-    if write_cache:
-        for name, pages in (("k_pages", k_pages), ("v_pages", v_pages)):
-            _check(pages, name, torch.bfloat16, 4)
-            if tuple(pages.shape[1:]) != (num_kv_heads, page_size, head_dim):
-                raise KernelError(f"{name} has shape {tuple(pages.shape)}, expected "
-                                  f"[pages, {num_kv_heads}, {page_size}, {head_dim}]")
-    qkv = torch.empty((T, width), dtype=torch.bfloat16, device=residual.device)
-    f = _fn("small_step", "hb_small_norm_qkv_rope",
-            [c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-             c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-             c_int, c_void_p])
-    tiles = (num_heads + 2 * num_kv_heads) * (head_dim // 8)
-    _run(f(_p(qkv), width, _p(residual), _p(norm_weight), float(eps), _p(w_qkv), _p(b_qkv), _p(cos), _p(sin),
-           _p(positions), _p(seq_of_token), _p(block_table), block_table.shape[1],
-           _p(k_pages) if write_cache else 0, _p(v_pages) if write_cache else 0, T, K, num_heads,
-           num_kv_heads, head_dim, page_size, 1 if write_cache else 0, _small_tiles_per_block(tiles),
-           _stream()), "small_norm_qkv_rope")
-    return qkv
 
 
 # ------------------------------------------------------------------ sampling

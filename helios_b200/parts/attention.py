@@ -81,30 +81,11 @@ class GQAAttention(Mixer):
 
     def forward_from_residual(self, ctx, residual: torch.Tensor, norm, cache: LayerCache, state=None,
                               pre=None, then=None):
-        """Steps of few tokens.  Narrow models: norm + projection + rotation + cache write in
-        one launch, attention, output projection + residual add in one launch.  Otherwise the
-        norm launches go: q|k|v takes the 1 / rms of ``pre`` as a factor on its accumulators,
+        """Steps of few tokens run without norm launches: q|k|v takes the 1 / rms of ``pre``
+        as a factor on its accumulators (the norm kernel runs where nothing was handed over),
         and the output projection adds into the residual and leaves ``then`` all but done."""
-        if ctx.act_dtype != torch.bfloat16 or type(norm) is not RMSNorm or cache is None:
-            return False
-        if not ops.small_step_fits(ctx.num_tokens, self.width, self.width, self.num_heads * self.head_dim) \
-                or self.head_dim % 8:
-            return self._forward_deferred_norms(ctx, residual, norm, cache, pre, then)
-        cos, sin = self._rotary_tables(ctx)
-        if cos is None or cos.shape[1] * 2 != self.head_dim:
-            return False
-        table = ctx.block_tables[cache.group]
-        qkv = ops.small_norm_qkv_rope(residual, norm.weight, norm.eps, self.w_qkv, self.b_qkv, cos, sin,
-                                      ctx.positions, ctx.seq_of_token, table, cache.k_pages, cache.v_pages,
-                                      self.num_heads, self.num_kv_heads, self.head_dim, cache.page_size,
-                                      write_cache=cache.write)
-        attn = ops.attention(ctx, qkv, cache.k_pages, cache.v_pages, table, self.num_heads,
-                             self.num_kv_heads, self.head_dim, cache.page_size, self.window, self.scale)
-        ops.small_linear_residual(residual, attn, self.w_o)
-        return True
-
-    def _forward_deferred_norms(self, ctx, residual, norm, cache, pre, then):
-        if not ops.deferred_norm_fits(ctx.num_tokens, self.w_qkv, self.w_o):
+        if ctx.act_dtype != torch.bfloat16 or type(norm) is not RMSNorm or cache is None \
+                or not ops.deferred_norm_fits(ctx.num_tokens, self.w_qkv, self.w_o):
             return False
         if pre is not None:
             qkv = ops.linear_bf16(pre.scaled, self.w_qkv, self.b_qkv, sumsq=pre.sumsq, eps=norm.eps)

@@ -36,17 +36,11 @@ class SwiGLU(FeedForward):
         return ops.linear(ops.linear_swiglu(x, self.w_gate_up), self.w_down)
 
     def forward_from_residual(self, ctx, residual: torch.Tensor, norm, pre=None, then=None):
-        """Steps of few tokens.  Narrow models: norm + gate|up + SwiGLU in one launch, down +
-        residual add in another.  Otherwise the norm launches go: gate|up takes the 1 / rms of
-        ``pre`` as a factor on its accumulators, and the down projection adds into the
-        residual and leaves ``then`` all but done."""
-        if ctx.act_dtype != torch.bfloat16 or type(norm) is not RMSNorm:
-            return False
-        if ops.small_step_fits(ctx.num_tokens, self.width, self.width, self.inner):
-            h = ops.small_norm_swiglu(residual, norm.weight, norm.eps, self.w_gate_up)
-            ops.small_linear_residual(residual, h, self.w_down)
-            return True
-        if not ops.deferred_norm_fits(ctx.num_tokens, self.w_gate_up, self.w_down):
+        """Steps of few tokens run without norm launches: gate|up takes the 1 / rms of ``pre``
+        as a factor on its accumulators, and the down projection adds into the residual and
+        leaves ``then`` all but done."""
+        if ctx.act_dtype != torch.bfloat16 or type(norm) is not RMSNorm \
+                or not ops.deferred_norm_fits(ctx.num_tokens, self.w_gate_up, self.w_down):
             return False
         if pre is not None:
             h = ops.linear_bf16(pre.scaled, self.w_gate_up, glu=True, sumsq=pre.sumsq, eps=norm.eps)

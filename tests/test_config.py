@@ -143,8 +143,8 @@ def test_a_plan_names_the_kernel_libraries_its_sizes_need():
         return {n for _p, part in plan.named_parts() for n in part.kernel_libraries(dtype)}
 
     bf16, f32 = torch.bfloat16, torch.float32
-    assert libraries(TINY_LLAMA, bf16) == {"gemm_bf16", "small_step", "attention_generic"}
-    assert libraries(TINY_TILED, bf16) == {"gemm_bf16", "small_step", "attention_bf16"}
+    assert libraries(TINY_LLAMA, bf16) == {"gemm_bf16", "attention_generic"}
+    assert libraries(TINY_TILED, bf16) == {"gemm_bf16", "attention_bf16"}
     assert libraries(TINY_TILED, f32) == {"gemm_f32", "attention_generic"}
     wide = dict(TINY_LLAMA, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8)
     assert libraries(wide, bf16) == {"gemm_bf16", "attention_bf16", "attention_tc", "attention_pair"}

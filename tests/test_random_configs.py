@@ -67,13 +67,12 @@ def test_random_configurations_on_the_tensor_memory_attention_kernels(tmp_path, 
 
 @pytest.mark.parametrize("seed", range(4000, 4008))
 def test_random_configurations_with_the_norms_inside_the_products(tmp_path, seed, monkeypatch):
-    """Models this narrow run their steps of few tokens on the fused few-token kernels; with
-    those switched off the same steps take the path of wide models: no RMSNorm launches, the
-    products add into the residual, leave the next norm's input and apply 1 / rms to their
-    accumulators (here at sizes that are no multiples of a tile, with bias, windows and up
-    to 32 tokens), and decode attention rotates and stores the new token itself."""
+    """Steps of few tokens run without RMSNorm launches: the products add into the residual,
+    leave the next norm's input and apply 1 / rms to their accumulators (here at sizes that
+    are no multiples of a tile, with bias and windows, and with the limit raised from 16 to
+    the 32 tokens the epilogues take), and decode attention rotates and stores the new token
+    itself."""
     from helios_b200.csrc import ops
-    monkeypatch.setattr(ops, "SMALL_STEP_TOKENS_NARROW", 0)
     monkeypatch.setattr(ops, "DEFERRED_NORM_TOKENS", ops.DEFERRED_NORM_MOST if seed % 2 else 16)
     cfg, rng = draw_config(seed, 8, head_dims=(32, 64, 96, 128, 48))
     _compare(tmp_path, cfg, rng, seed, 8, "bfloat16")
