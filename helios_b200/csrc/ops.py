@@ -581,8 +581,8 @@ GEMM_LIBRARY_TOKEN_STEPS_FEW = ((128, 8), (256, 32))
 #: 30 / 10 at 1,024, 31 / 15 at 2,048, 32 / 27 at 4,096, 64 / 64 at 8,192); gate|up with SwiGLU
 #: 14.4 / 18.9 / 16.5 against 8.6 / 8.7 / 12.8 (library product + gate kernel; 26 / 26 at 768,
 #: 56 / 58 at 2,048, 96 / 117 at 4,096: GEMM_LIBRARY_SMALL_GLU_TOKENS).  Up to 32 tokens this
-#: package's kernels win as a whole (a step of 32 requests: 28,300 against 25,900 tokens/s),
-#: up to 16 the fused few-token kernels run.  0 bytes turns it off.
+#: package's kernels win as a whole (a step of 32 requests: 28,300 against 25,900 tokens/s).
+#: 0 bytes turns it off.
 GEMM_LIBRARY_SMALL_WEIGHT_BYTES = 20 * 1024 * 1024
 GEMM_LIBRARY_SMALL_TOKENS = (33, 4096)
 GEMM_LIBRARY_SMALL_GLU_TOKENS = (33, 512)

@@ -132,8 +132,7 @@ def test_plan_takes_every_size_from_the_configuration():
 
 def test_a_plan_names_the_kernel_libraries_its_sizes_need():
     """What a model compiles when it is made follows its parts' sizes and the dtype: heads of
-    16 have no tiled attention kernel, heads of 32 no tcgen05 one, float32 neither; a wide
-    model has no use for the fused few-token kernels."""
+    16 have no tiled attention kernel, heads of 32 no tcgen05 one, float32 neither."""
     import torch
     from helios_b200.csrc.build import LIBRARIES
     from helios_b200.models import build_dense_decoder_plan

@@ -164,8 +164,9 @@ SMALL = {
 
 
 def test_two_layers_of_the_small_models_sizes_across_the_kernel_choices():
-    """Qwen2.5-0.5B layer sizes: steps of up to 16 tokens run the fused few-token kernels, up
-    to 32 the tensor-memory products, beyond that the library's (small weight matrices); every
+    """Qwen2.5-0.5B layer sizes: steps of up to 16 tokens run the tensor-memory products with
+    the norms in their epilogues, up to 32 with norm launches, beyond that the library's
+    products (small weight matrices); every
     side of each line against the plain implementation, as portions and as batches of
     requests that decode."""
     from helios_b200.engine.batch import StepEntry
