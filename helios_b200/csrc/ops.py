@@ -612,9 +612,10 @@ def _library_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """y = x W^T + b.  float32: this package's FMA kernel.  bfloat16: the tcgen05 kernels
-    (see GEMM_LIBRARY_TOKEN_RANGE for the one case that goes to the library); a K that is
-    no multiple of 8 goes to the library too, as TMA needs 16-byte rows."""
+    """y = x W^T + b.  float32: this package's FMA kernel.  bfloat16: the tcgen05 kernels,
+    or the library for plain products in the token ranges of GEMM_LIBRARY_TOKEN_RANGE and
+    GEMM_LIBRARY_SMALL_TOKENS (small weight matrices); a K that is no multiple of 8 goes to
+    the library too, as TMA needs 16-byte rows."""
     if x.dtype == torch.float32:
         return linear_f32(x, weight, bias)
     _check(x, "x", torch.bfloat16, 2)
