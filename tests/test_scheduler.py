@@ -575,3 +575,17 @@ def test_token_slice_equals_slicing_the_whole_list():
     for start in range(0, 12):
         for n in range(0, 13 - start):
             assert seq.token_slice(start, n) == whole[start:start + n], (start, n)
+
+
+def test_captured_steps_pad_the_request_count_by_less_than_a_quarter():
+    """``EngineCore.padded_requests``: never fewer than asked, exact up to 8, the same for a
+    count and for what it was padded to, never more than a quarter on top, few distinct sizes."""
+    from helios_b200.engine.core import EngineCore
+
+    sizes = set()
+    for n in range(1, 1025):
+        p = EngineCore.padded_requests(n)
+        assert p >= n and EngineCore.padded_requests(p) == p
+        assert p == n if n <= 8 else 4 * (p - n) < n
+        sizes.add(p)
+    assert len(sizes) <= 8 + 4 * 7 and sorted(sizes)[:12] == [1, 2, 3, 4, 5, 6, 7, 8, 10, 12, 14, 16]
