@@ -642,10 +642,14 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
 
 # ------------------------------------------------------------------ sampling
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
-           top_p: torch.Tensor, seed: torch.Tensor, offset: torch.Tensor) -> torch.Tensor:
+           top_p: torch.Tensor, seed: torch.Tensor, offset: torch.Tensor,
+           narrows: Optional[bool] = None) -> torch.Tensor:
     """One token id per row of float32 ``logits`` [R, V]; per-row options as device tensors
     (temperature float32 with 0 = greedy, top_k int32 with 0 = off, top_p float32,
-    seed and offset int64)."""
+    seed and offset int64).  ``narrows``: whether any row has a top-k or top-p to search a
+    threshold for, if the caller knows (the options live on the device): rows that only take
+    the argmax or draw from all values are quickest on the one-block kernel, threshold
+    searches on the cluster kernel (``sampling.cu``); None lets the row length decide."""
     _check(logits, "logits", torch.float32, 2)
     R, V = logits.shape
     _check(temperature, "temperature", torch.float32, 1)
@@ -660,9 +664,9 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
     out = torch.empty((R,), dtype=torch.int32, device=logits.device)
     f = _fn("sampling", "hb_sample",
             [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-             c_void_p, c_void_p])
+             c_void_p, c_int, c_void_p])
     _run(f(_p(out), _p(logits), R, V, V, _p(temperature), _p(top_k), _p(top_p), _p(seed),
-           _p(offset), _stream()), "sample")
+           _p(offset), -1 if narrows is None else int(bool(narrows)), _stream()), "sample")
     return out
 
 

@@ -2,6 +2,8 @@
 // with optional top-k and top-p, drawn by inverse CDF from a Philox uniform that
 // depends on the request's (seed, offset) only.
 //
+// Two kernels: one block per row for any row length, and for rows of 4,096 to 163,840 values
+// a thread-block cluster per row that keeps the row in registers (see below).
 // Meaning of the options follows python/helios/exec/sampler.py:51-81: temperature 0 is
 // argmax of the raw logits; otherwise logits/T; top-k keeps logits >= the k-th
 // largest; top-p keeps, in descending order, every token before which the
@@ -163,11 +165,317 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int V, in
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same sampling with a row spread over a thread-block cluster: every block keeps its
+// eighth of the row in REGISTERS (as order-preserving keys), so the threshold searches read
+// memory once instead of once per bit, settle four bits a pass (fifteen thresholds counted
+// side by side), and eight SMs work on a row instead of one.  Sums keep a fixed order: a
+// thread's elements in index order, the block's threads by `block_sum`, the cluster's blocks
+// by rank; the draw walks the row in index order as the kernel above does.
+constexpr int SC_THREADS = 512;
+constexpr int SC_CLUSTER = 8;
+constexpr int SC_MOST = 40;          // elements a thread keeps: rows of up to 8 * 512 * 40 values
+constexpr int SC_WARPS = SC_THREADS / 32;
+
+__device__ __forceinline__ float key_float(uint32_t k) {   // inverse of float_key
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+__device__ __forceinline__ uint32_t sc_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void sc_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float sc_peer_f32(const float* mine, uint32_t rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote)
+               : "r"((uint32_t)__cvta_generic_to_shared(mine)), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
+// Fifteen sums over the whole cluster, the same in every thread of every block afterwards:
+// warp trees, then the block's warps in turn, then the cluster's blocks by rank.  `slot`
+// alternates between calls so that a block may run one call ahead of its peers.
+__device__ __forceinline__ void sc_sum15(float (&acc)[15], float (*warp_part)[15], float (*block_part)[16],
+                                         float* total, int slot) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int j = 0; j < 15; ++j) acc[j] = warp_sum(acc[j]);
+  if (lane == 0) {
+#pragma unroll
+    for (int j = 0; j < 15; ++j) warp_part[warp][j] = acc[j];
+  }
+  __syncthreads();
+  if (threadIdx.x < 15) {
+    float t = 0.f;
+    for (int w = 0; w < SC_WARPS; ++w) t += warp_part[w][threadIdx.x];
+    block_part[slot][threadIdx.x] = t;
+  }
+  sc_cluster_sync();
+  if (threadIdx.x < 15) {
+    float t = 0.f;
+    for (uint32_t r = 0; r < SC_CLUSTER; ++r) t += sc_peer_f32(&block_part[slot][threadIdx.x], r);
+    total[threadIdx.x] = t;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < 15; ++j) acc[j] = total[j];
+  __syncthreads();                                  // `total` and `warp_part` are free again
+}
+
+template <int EPT>
+__global__ void __launch_bounds__(SC_THREADS)
+sample_cluster_kernel(int* __restrict__ out, const float* __restrict__ logits, int V, int ld,
+                      const float* __restrict__ temperature, const int* __restrict__ top_k,
+                      const float* __restrict__ top_p, const unsigned long long* __restrict__ seed,
+                      const unsigned long long* __restrict__ offset) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float warp_part[SC_WARPS][15];
+  __shared__ float block_part[2][16];
+  __shared__ float total[16];
+  __shared__ uint32_t s_key[SC_WARPS];
+  __shared__ int s_idx[SC_WARPS];
+  __shared__ float x_f[4];                 // what a block shows its peers: key, index, total, pick
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t rank = sc_rank();
+  const int row = blockIdx.x / SC_CLUSTER;
+  const float* l = logits + (size_t)row * ld;
+  const int first = ((int)rank * SC_THREADS + tid) * EPT;       // this thread's elements, in index order
+
+  // The block's part of the row comes in with consecutive threads on consecutive values and
+  // goes through shared memory (rows of EPT + 1, so that the threads' own runs of EPT values
+  // do not meet in one bank).
+  extern __shared__ float staged[];
+  {
+    const int block_first = (int)rank * SC_THREADS * EPT;
+#pragma unroll 8
+    for (int c = tid; c < SC_THREADS * EPT; c += SC_THREADS) {
+      const int owner = c / EPT, i = c - owner * EPT;
+      staged[owner * (EPT + 1) + i] = (block_first + c < V) ? l[block_first + c] : 0.f;
+    }
+    __syncthreads();
+  }
+  uint32_t key[EPT];                       // 0 where the row has ended (no float has key 0 but one NaN)
+#pragma unroll
+  for (int i = 0; i < EPT; ++i) key[i] = (first + i < V) ? float_key(staged[tid * (EPT + 1) + i]) : 0u;
+
+  // ---- argmax, lowest index among equals
+  uint32_t bk = 0;
+  int bi = 0x7fffffff;
+#pragma unroll
+  for (int i = 0; i < EPT; ++i)
+    if (key[i] > bk) { bk = key[i]; bi = first + i; }
+  auto better = [](uint32_t k1, int i1, uint32_t k2, int i2) { return k1 > k2 || (k1 == k2 && i1 < i2); };
+  for (int o = 16; o > 0; o >>= 1) {
+    const uint32_t ok = __shfl_xor_sync(0xffffffffu, bk, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (better(ok, oi, bk, bi)) { bk = ok; bi = oi; }
+  }
+  if (lane == 0) { s_key[warp] = bk; s_idx[warp] = bi; }
+  __syncthreads();
+  if (tid == 0) {
+    for (int w = 1; w < SC_WARPS; ++w)
+      if (better(s_key[w], s_idx[w], bk, bi)) { bk = s_key[w]; bi = s_idx[w]; }
+    x_f[0] = __uint_as_float(bk);
+    x_f[1] = __int_as_float(bi);
+  }
+  sc_cluster_sync();
+  bk = 0; bi = 0x7fffffff;
+  for (uint32_t r = 0; r < SC_CLUSTER; ++r) {
+    const uint32_t ok = __float_as_uint(sc_peer_f32(&x_f[0], r));
+    const int oi = __float_as_int(sc_peer_f32(&x_f[1], r));
+    if (better(ok, oi, bk, bi)) { bk = ok; bi = oi; }
+  }
+  const int amax = bi == 0x7fffffff ? 0 : bi;
+  const float temp = temperature[row];
+  if (!(temp > 0.f)) {                     // the same for the whole cluster: nobody waits for anybody
+    if (rank == 0 && tid == 0) out[row] = amax;
+    sc_cluster_sync();                     // a peer may still be reading this block's shared memory
+    return;
+  }
+  const float inv_t = 1.f / temp;
+  const float mx_t = key_float(bk) * inv_t;
+  int slot = 0;
+  float acc[15];
+
+  // ---- top-k: the largest key c with #(key >= c) >= k, four bits a pass
+  uint32_t thr = 1;                        // keeps every value, and none of the padding
+  const int k = top_k[row];
+  if (k > 0 && k < V) {
+    uint32_t cand = 0;
+    for (int shift = 28; shift >= 0; shift -= 4) {
+#pragma unroll
+      for (int j = 0; j < 15; ++j) acc[j] = 0.f;
+#pragma unroll
+      for (int i = 0; i < EPT; ++i) {
+#pragma unroll
+        for (int j = 0; j < 15; ++j) acc[j] += (key[i] >= (cand | ((uint32_t)(j + 1) << shift))) ? 1.f : 0.f;
+      }
+      sc_sum15(acc, warp_part, block_part, total, slot);
+      slot ^= 1;
+      uint32_t digit = 0;
+#pragma unroll
+      for (int j = 0; j < 15; ++j)
+        if (acc[j] >= (float)k) digit = j + 1;
+      cand |= digit << shift;
+    }
+    if (cand > thr) thr = cand;
+  }
+  // ---- top-p over what top-k kept: the largest key c with mass(key >= c) > p * Z
+  const float pp = top_p[row];
+  if (pp < 1.f) {
+#pragma unroll
+    for (int j = 0; j < 15; ++j) acc[j] = 0.f;
+#pragma unroll
+    for (int i = 0; i < EPT; ++i)
+      if (key[i] >= thr) acc[0] += expf(key_float(key[i]) * inv_t - mx_t);
+    sc_sum15(acc, warp_part, block_part, total, slot);
+    slot ^= 1;
+    const float want = pp * acc[0];
+    uint32_t cand = 0;
+    for (int shift = 28; shift >= 0; shift -= 4) {
+#pragma unroll
+      for (int j = 0; j < 15; ++j) acc[j] = 0.f;
+#pragma unroll
+      for (int i = 0; i < EPT; ++i) {
+        if (key[i] >= thr) {
+          const float e = expf(key_float(key[i]) * inv_t - mx_t);
+#pragma unroll
+          for (int j = 0; j < 15; ++j) acc[j] += (key[i] >= (cand | ((uint32_t)(j + 1) << shift))) ? e : 0.f;
+        }
+      }
+      sc_sum15(acc, warp_part, block_part, total, slot);
+      slot ^= 1;
+      uint32_t digit = 0;
+#pragma unroll
+      for (int j = 0; j < 15; ++j)
+        if (acc[j] > want) digit = j + 1;
+      cand |= digit << shift;
+    }
+    if (cand > thr) thr = cand;
+  }
+
+  // ---- inverse CDF in index order: a thread's kept mass, its place among the block's
+  // threads (a scan in thread order), the block's place among the blocks (by rank)
+  float mine = 0.f;
+#pragma unroll
+  for (int i = 0; i < EPT; ++i)
+    if (key[i] >= thr) mine += expf(key_float(key[i]) * inv_t - mx_t);
+  float incl = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float v = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += v;
+  }
+  if (lane == 31) warp_part[warp][0] = incl;
+  __syncthreads();
+  float before = incl - mine;                        // exclusive, within the block
+  float block_total = 0.f;
+  for (int w = 0; w < SC_WARPS; ++w) {
+    if (w < warp) before += warp_part[w][0];
+    block_total += warp_part[w][0];
+  }
+  if (tid == 0) x_f[2] = block_total;
+  sc_cluster_sync();
+  float blocks_before = 0.f, grand = 0.f;
+  for (uint32_t r = 0; r < SC_CLUSTER; ++r) {
+    const float t = sc_peer_f32(&x_f[2], r);
+    if (r < rank) blocks_before += t;
+    grand += t;
+  }
+  const uint32_t word = philox_first_word(seed[row], offset[row]);
+  const float target = (float)(word >> 8) * (1.0f / 16777216.0f) * grand;
+  const float start = blocks_before + before;
+  // the last thread (in index order) that keeps something and starts at or before the target
+  const bool candidate = mine > 0.f && start <= target;
+  const uint32_t votes = __ballot_sync(0xffffffffu, candidate);
+  if (lane == 0) s_idx[warp] = votes ? warp * 32 + (31 - __clz(votes)) : -1;
+  __syncthreads();
+  if (tid == 0) {
+    int best = -1;
+    for (int w = 0; w < SC_WARPS; ++w) best = max(best, s_idx[w]);
+    x_f[3] = __int_as_float(best < 0 ? -1 : (int)rank * SC_THREADS + best);
+  }
+  sc_cluster_sync();
+  int pick = -1;
+  for (uint32_t r = 0; r < SC_CLUSTER; ++r) pick = max(pick, __float_as_int(sc_peer_f32(&x_f[3], r)));
+  if (pick < 0) {                                    // nothing kept any mass: cannot happen with finite logits
+    if (rank == 0 && tid == 0) out[row] = amax;
+  } else if (pick == (int)rank * SC_THREADS + tid) {
+    float cum = start;
+    int choice = -1, last_kept = amax;
+#pragma unroll
+    for (int i = 0; i < EPT; ++i) {
+      if (choice < 0 && key[i] >= thr) {
+        last_kept = first + i;
+        cum += expf(key_float(key[i]) * inv_t - mx_t);
+        if (cum > target) choice = first + i;
+      }
+    }
+    out[row] = choice >= 0 ? choice : last_kept;
+  }
+  sc_cluster_sync();                                 // nobody leaves while a peer may still read its shared memory
+}
+
+template <int EPT>
+static int launch_sample_cluster(int* out, const float* logits, int R, int V, int ld, const float* temperature,
+                                 const int* top_k, const float* top_p, const unsigned long long* seed,
+                                 const unsigned long long* offset, cudaStream_t stream) {
+  const size_t smem = (size_t)SC_THREADS * (EPT + 1) * sizeof(float);
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(sample_cluster_kernel<EPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+        cudaSuccess)
+      return HB_LAUNCH_FAILED;
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(R * SC_CLUSTER);
+  cfg.blockDim = dim3(SC_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = SC_CLUSTER;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = hb_pdl_enabled() ? 2 : 1;
+  cudaLaunchKernelEx(&cfg, sample_cluster_kernel<EPT>, out, logits, V, ld, temperature, top_k, top_p, seed, offset);
+  return hb_check_launch();
+}
+
+
+// Rows of 4,096 to 163,840 values go to the cluster kernel (a row of fewer gives eight blocks
+// nothing to share out), anything else to the one-block kernel; and so does everything when
+// the caller knows that no row has a top-k or top-p (narrows = 0; 1: some has; -1: unknown):
+// argmax and a draw from all values read the row once either way, and one block of 1,024
+// threads does that faster than eight that first sort it into registers (64 rows of 128,256:
+// 14 against 29 µs greedy; with top-k and top-p 1,015 against 428 µs, 8 rows 669 against 87).
 HB_EXPORT int hb_sample(int* out, const float* logits, int R, int V, int ld, const float* temperature,
                         const int* top_k, const float* top_p, const unsigned long long* seed,
-                        const unsigned long long* offset, cudaStream_t stream) {
+                        const unsigned long long* offset, int narrows, cudaStream_t stream) {
   if (R <= 0) return HB_OK;
   if (V <= 0) return HB_BAD_ARGUMENT;
+  const int per_thread = (V + SC_CLUSTER * SC_THREADS - 1) / (SC_CLUSTER * SC_THREADS);
+  if (narrows != 0 && V >= 4096 && per_thread <= SC_MOST) {
+#define HB_SAMPLE_CASE(EPT_)                                                                          \
+    if (per_thread <= EPT_)                                                                            \
+      return launch_sample_cluster<EPT_>(out, logits, R, V, ld, temperature, top_k, top_p, seed, offset, stream)
+    HB_SAMPLE_CASE(8);
+    HB_SAMPLE_CASE(16);
+    HB_SAMPLE_CASE(24);
+    HB_SAMPLE_CASE(32);
+    HB_SAMPLE_CASE(40);
+#undef HB_SAMPLE_CASE
+  }
   hb_launch(sample_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, stream, out, logits, V, ld, temperature, top_k, top_p,
                                                   seed, offset);
   return hb_check_launch();

@@ -56,7 +56,9 @@ class Sampler:
         i64 = words[:4 * R].view(np.int64)
         f32 = words[4 * R:6 * R].view(np.float32)
         top_k = words[6 * R:]
+        narrows = False
         for i, p in enumerate(params):
+            narrows = narrows or (p.temperature > 0 and (p.top_k > 0 or p.top_p < 1.0))
             i64[i] = np.uint64(seeds[i] & (2**64 - 1)).astype(np.int64)
             i64[R + i] = offsets[i]
             f32[i], f32[R + i] = p.temperature, p.top_p
@@ -66,4 +68,4 @@ class Sampler:
         st.event.record()
         d64 = dev[:4 * R].view(torch.int64)
         d32 = dev[4 * R:6 * R].view(torch.float32)
-        return ops.sample(logits, d32[:R], dev[6 * R:], d32[R:], d64[:R], d64[R:])
+        return ops.sample(logits, d32[:R], dev[6 * R:], d32[R:], d64[:R], d64[R:], narrows=narrows)

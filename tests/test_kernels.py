@@ -426,22 +426,29 @@ def test_linear_bf16(M):
 
 
 # ---------------------------------------------------------------------- sampling
-def _sample(logits, temps, ks, ps, seeds, offsets):
+def _sample(logits, temps, ks, ps, seeds, offsets, narrows=None):
     t = lambda x, d: torch.tensor(x, dtype=d, device=DEV)
     return ops().sample(logits.to(DEV), t(temps, torch.float32), t(ks, torch.int32), t(ps, torch.float32),
-                        t(seeds, torch.int64), t(offsets, torch.int64)).cpu().tolist()
+                        t(seeds, torch.int64), t(offsets, torch.int64), narrows=narrows).cpu().tolist()
 
 
-def test_greedy_is_argmax_with_lowest_index_on_ties():
+@pytest.mark.parametrize("V", [1231, 40000, 128256])
+def test_greedy_is_argmax_with_lowest_index_on_ties(V):
+    """(One block per row below 4,096 values, a cluster per row above.)"""
     g = torch.Generator().manual_seed(0)
-    logits = torch.randn(5, 1231, generator=g)
-    logits[2, 100] = logits[2, 900] = 50.0
+    logits = torch.randn(5, V, generator=g)
+    logits[2, 100] = logits[2, V - 300] = 50.0
+    logits[3, V - 1] = 60.0
     got = _sample(logits, [0.0] * 5, [0] * 5, [1.0] * 5, [1] * 5, [0] * 5)
-    assert got == torch.argmax(logits, -1).tolist() and got[2] == 100
+    assert got == torch.argmax(logits, -1).tolist() and got[2] == 100 and got[3] == V - 1
 
 
-@pytest.mark.parametrize("V", [384, 1231, 128256])
-def test_temperature_top_k_top_p_follow_the_reference_rules(V):
+@pytest.mark.parametrize("one_block", [False, True])
+@pytest.mark.parametrize("V", [384, 1231, 4095, 4096, 4097, 8192, 50001, 128256, 151936, 163840, 163841])
+def test_temperature_top_k_top_p_follow_the_reference_rules(V, one_block):
+    """Rows of 4,096 to 163,840 values run on the kernel that spreads a row over a cluster of
+    blocks, the others, and every row when the caller says that none narrows (which is always
+    allowed), on the kernel with one block a row."""
     g = torch.Generator().manual_seed(V)
     R = 24
     logits = torch.randn(R, V, generator=g) * 2
@@ -450,7 +457,7 @@ def test_temperature_top_k_top_p_follow_the_reference_rules(V):
     ps = [1.0, 1.0, 0.9, 0.5, 1.0, 0.2] * 4
     seeds = [11 + i for i in range(R)]
     offsets = [i * 3 for i in range(R)]
-    got = _sample(logits, temps, ks, ps, seeds, offsets)
+    got = _sample(logits, temps, ks, ps, seeds, offsets, narrows=False if one_block else None)
     for i in range(R):
         u = ops().philox_uniform(seeds[i], offsets[i])
         want = plain_model.sample_reference(logits[i], temps[i], ks[i], ps[i], u)
@@ -478,9 +485,10 @@ def _boundaries(logits, temp, k, p, a, b):
     return [float(cdf[j]) for j in range(lo, hi)]
 
 
-def test_a_requests_draws_depend_on_its_seed_and_offset_only():
+@pytest.mark.parametrize("V", [3000, 5000, 130000])
+def test_a_requests_draws_depend_on_its_seed_and_offset_only(V):
     g = torch.Generator().manual_seed(4)
-    logits = torch.randn(1, 5000, generator=g)
+    logits = torch.randn(1, V, generator=g)
     alone = _sample(logits, [1.0], [0], [1.0], [99], [7])
     batch = _sample(logits.repeat(6, 1), [1.0] * 6, [0] * 6, [1.0] * 6, [1, 2, 99, 3, 99, 5], [0, 1, 7, 2, 8, 3])
     assert batch[2] == alone[0]
