@@ -678,7 +678,8 @@ def main():
     e2e = None
     del core
     torch.cuda.empty_cache()
-    if not args.no_e2e:
+    def measure_e2e(**sampling):
+        """Decoded tokens a second through ``LLMEngine.step`` (host ids in, sampled ids out)."""
         engine = LLMEngine(EngineConfig(
             model_dir="", dtype="bfloat16", block_size=page, max_num_seqs=args.batch,
             max_num_batched_tokens=PREFILL_TOKENS, max_model_len=args.context + 8,
@@ -689,8 +690,8 @@ def main():
         # prompt was finished
         for b in range(args.batch):
             toks = torch.randint(0, cfg["vocab_size"], (ctx0 - 64,), generator=gen).tolist()
-            engine.add_request(f"e{b}", toks,
-                               SamplingParams(max_tokens=args.steps + args.warmup + SETTLE_STEPS + 64))
+            engine.add_request(f"e{b}", toks, SamplingParams(
+                max_tokens=args.steps + args.warmup + SETTLE_STEPS + 64, seed=b, **sampling))
         while any(s.num_pending_tokens > 1 for s in engine.scheduler.running) or engine.scheduler.waiting:
             engine.step()
         for _ in range(SETTLE_STEPS):        # as in measure_decode: out of the prompt fill's power state
@@ -703,11 +704,16 @@ def main():
             engine.step()
         torch.cuda.synchronize()
         wall = (time.perf_counter() - w0) / args.steps
+        return round(args.batch / wall, 1), engine.steps_ahead
+
+    if not args.no_e2e:
+        value, ahead = measure_e2e()
+        # the same with every request drawing from its top 50 tokens and 0.9 of the mass
+        sampled, _ = measure_e2e(temperature=0.8, top_k=50, top_p=0.9)
         h2d = 4 * (args.batch * 8 + args.batch * (args.context // page + 1)) + args.batch * 28
-        e2e = {"value": round(args.batch / wall, 1), "unit": "tokens/s",
+        e2e = {"value": value, "unit": "tokens/s",
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch,
-               "steps_launched_ahead": engine.steps_ahead}
-        del engine
+               "steps_launched_ahead": ahead, "value_top_k_50_top_p_09": sampled}
     sampler.stop()
     del model
     torch.cuda.empty_cache()
