@@ -177,6 +177,42 @@ class CacheLayout:
         want = self.pages_for_tokens(req.length + n_new)
         return [max(0, want - len(t)) for t in req.tables]
 
+    def pages_needed_each(self, request_ids: Sequence[Hashable], n_new: int = 1) -> List[int]:
+        """``pages_needed`` summed over many requests that each get ``n_new`` more tokens (a
+        decode step of hundreds of requests asks this every step: one loop, no lists)."""
+        need = [0] * len(self.groups)
+        requests, page = self.requests, self.page_size
+        for rid in request_ids:
+            req = requests[rid]
+            want = -(-(req.length + n_new) // page)
+            for g, t in enumerate(req.tables):
+                d = want - len(t)
+                if d > 0:
+                    need[g] += d
+        return need
+
+    def extend_each(self, request_ids: Sequence[Hashable], n_new: int = 1) -> None:
+        """``extend`` for every request in turn (the caller has made sure of the pages with
+        ``pages_needed_each``; a request that finds none raises as ``extend`` does)."""
+        requests, page, pools = self.requests, self.page_size, self.pools
+        for rid in request_ids:
+            req = requests[rid]
+            want = -(-(req.length + n_new) // page)
+            grow = False
+            for g, t in enumerate(req.tables):
+                d = want - len(t)
+                if d > 0:
+                    grow = True
+                    if d > pools[g].num_free:         # all of a request's groups, or none
+                        raise OutOfPages(f"request {rid!r} needs {d} pages of group {g}, "
+                                         f"{pools[g].num_free} free")
+            if grow:
+                for g, t in enumerate(req.tables):
+                    d = want - len(t)
+                    if d > 0:
+                        t.extend(pools[g].take(d, rid))
+                        req.version += 1
+
     def can_extend(self, request_id: Hashable, n_new: int, keep_free: int = 0) -> bool:
         need = self.pages_needed(request_id, n_new)
         return all(n + keep_free <= pool.num_free for n, pool in zip(need, self.pools))
@@ -209,6 +245,23 @@ class CacheLayout:
             if n:
                 req.tables[g].extend(self.pools[g].take(n, request_id))
                 req.version += 1
+
+    def commit_each(self, request_ids: Sequence[Hashable], counts: Sequence[int]) -> None:
+        """``commit`` for every request of a step; without a window group nothing is given
+        back and a commit is a check and an addition."""
+        if any(g.window is not None for g in self.groups):
+            for rid, n in zip(request_ids, counts):
+                self.commit(rid, n)
+            return
+        requests, page = self.requests, self.page_size
+        for rid, n in zip(request_ids, counts):
+            req = requests[rid]
+            length = req.length + n
+            want = -(-length // page)
+            for t in req.tables:
+                if want > len(t):
+                    raise CacheInvariantError(f"request {rid!r} commits tokens it has no pages for")
+            req.length = length
 
     def commit(self, request_id: Hashable, n_new: int) -> None:
         """``n_new`` tokens were written.  In a group with a window W the next token, at

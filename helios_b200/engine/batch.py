@@ -102,15 +102,74 @@ class MetaLayout:
         return [dev[o:o + n] for o, n in zip(self.offsets, self.sizes)]
 
 
+def _fill_decode(layout, entries, cache, pad_page, rows_kept, token_ids, positions, seq_of_token, cu,
+                 start, ctx_len, slots, want, tables) -> List[SeqSlice]:
+    """``fill_meta`` for a captured decode step (one token a request, one row a request): whole
+    arrays at once instead of slices per request, and a block-table row is written again only
+    when its request or that request's table has changed since this buffer was last filled
+    (``rows_kept``: row -> (request, table version)); with hundreds of requests the per-request
+    work of the general path costs more than the step."""
+    S, n_real = layout.S, len(entries)
+    requests = cache.requests
+    lengths, slot_of, seqs = [], [], []
+    for i, e in enumerate(entries):
+        req = requests[e.request_id]
+        lengths.append(req.length)
+        slot_of.append(req.slot)
+        seqs.append(SeqSlice(e.request_id, req.slot, req.length, 1, i))
+        key = (e.request_id, req.version)
+        if rows_kept.get(i) != key:
+            rows_kept[i] = key
+            for g, t in enumerate(tables):
+                row = cache.table_array(e.request_id, g)
+                t[i, :len(row)] = row
+                t[i, len(row):] = -1
+    for i in range(n_real, S):
+        if rows_kept.get(i) != "padding":
+            rows_kept[i] = "padding"
+            for g, t in enumerate(tables):
+                t[i, :1] = pad_page[g]
+                t[i, 1:] = -1
+    pad = S - n_real
+    token_ids[:S] = [e.tokens[0] for e in entries] + [0] * pad
+    positions[:S] = lengths + [0] * pad
+    start[:S] = positions[:S]
+    ctx_len[:S] = positions[:S] + 1
+    slots[:S] = slot_of + [0] * pad
+    seq_of_token[:S] = _iota(S)
+    want[:S] = seq_of_token[:S]
+    cu[:S + 1] = _iota(S + 1)
+    return seqs
+
+
+_iotas: dict = {}
+
+
+def _iota(n: int) -> np.ndarray:
+    a = _iotas.get(n)
+    if a is None:
+        a = _iotas[n] = np.arange(n, dtype=np.int32)
+    return a
+
+
 def fill_meta(layout: MetaLayout, host: np.ndarray, entries: Sequence[StepEntry], cache,
-              pad_page: Optional[List[int]] = None, page_size: int = 1) -> List[SeqSlice]:
+              pad_page: Optional[List[int]] = None, page_size: int = 1,
+              rows_kept: Optional[dict] = None) -> List[SeqSlice]:
     """Write the step's arrays into ``host`` (int32, ``layout.total`` long).  Requests
     beyond ``len(entries)`` up to ``layout.S`` are padding whose keys and values go to the
     spare page ``pad_page[group]`` that no request ever gets; an entry without a wanted place
-    gets its last token as one when the layout has a row for every request."""
+    gets its last token as one when the layout has a row for every request.  ``rows_kept``:
+    what the buffer's block-table rows hold from the fill before (a caller that fills the
+    same buffer step after step passes the same dict; see ``_fill_decode``)."""
     v = layout.host_views(host)
     token_ids, positions, seq_of_token, cu, start, ctx_len, slots, want = v[:8]
     tables = [t.reshape(layout.S, w) for t, w in zip(v[8:], layout.widths)]
+    if rows_kept is not None and pad_page is not None and layout.S == layout.T \
+            and all(len(e.tokens) == 1 and len(e.want) <= 1 for e in entries):
+        return _fill_decode(layout, entries, cache, pad_page, rows_kept,
+                            token_ids, positions, seq_of_token, cu, start, ctx_len, slots, want, tables)
+    if rows_kept is not None:
+        rows_kept.clear()
     for t in tables:
         t.fill(-1)
     seqs: List[SeqSlice] = []

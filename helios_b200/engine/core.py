@@ -44,6 +44,7 @@ class _StepGraph:
                 core.graph_max_context, max(s.head_dim for s in cache.specs) if cache.specs else 128)
         self.ctx.extras["tile_provider"] = self._tiles
         self._tile_buffers = {}          # (tile, longest first) -> (pinned rows, device rows)
+        self._rows_kept = {}             # block-table rows of the staging buffer that are still right
         self._page_size = cache.page_size
         self.graph = None
         self.warmed = False
@@ -83,7 +84,7 @@ class _StepGraph:
     def fill(self, entries, cache) -> None:
         self.copied.synchronize()        # the staging buffers are free again
         self.ctx.seqs = fill_meta(self.layout, self.host.numpy(), entries, cache, cache.pad_pages,
-                                  self._page_size)
+                                  self._page_size, rows_kept=self._rows_kept)
         # the padding requests count as requests of the step (the tile lists cover them)
         off = sum(s.num_tokens for s in self.ctx.seqs)
         for i in range(len(entries), self.num_seqs):

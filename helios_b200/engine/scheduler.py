@@ -225,14 +225,19 @@ class Scheduler:
         return plan
 
     def launched(self, plan: StepPlan) -> None:
-        for item in plan.items:
-            seq = self.seqs[item.seq_id]
-            self.cache.commit(seq.seq_id, item.num_tokens)
-            seq.num_computed_tokens += item.num_tokens
-            if item.num_tokens > 1 or item.start_pos < seq.prompt_len:
-                self.stats.prefill_tokens += item.num_tokens
+        items, by_id = plan.items, self.seqs
+        counts = [len(item.token_ids) for item in items]
+        self.cache.commit_each([item.seq_id for item in items], counts)
+        prefill = decode = 0
+        for item, n in zip(items, counts):
+            seq = by_id[item.seq_id]
+            seq.num_computed_tokens += n
+            if n > 1 or item.start_pos < len(seq.request.prompt_token_ids):
+                prefill += n
             else:
-                self.stats.decode_tokens += 1
+                decode += 1
+        self.stats.prefill_tokens += prefill
+        self.stats.decode_tokens += decode
 
     def complete(self, plan: StepPlan, tokens: Dict[int, int],
                  ahead: Optional[StepPlan] = None) -> None:
@@ -270,21 +275,22 @@ class Scheduler:
         if self.waiting and not self._admission_closed():
             return None           # a waiting request might join the next step
         seqs = []
-        for item in prev.items:
-            seq = self.seqs[item.seq_id]
-            if not item.sample or seq.state is not SeqState.RUNNING:
+        by_id, running, most_len = self.seqs, SeqState.RUNNING, self.config.max_model_len
+        for item in prev.items:                # (hundreds of requests a step: no property chains here)
+            seq = by_id[item.seq_id]
+            if not item.sample or seq.state is not running:
                 return None
-            if seq.num_pending_tokens != 0:
+            outputs = len(seq.output_token_ids)
+            total = len(seq.request.prompt_token_ids) + outputs
+            if total != seq.num_computed_tokens:
                 return None       # ``launched(prev)`` has not been called
-            if seq.num_output_tokens + 1 >= seq.request.params.max_tokens:
+            if outputs + 1 >= seq.request.params.max_tokens:
                 return None
-            if seq.total_tokens + 1 >= self.config.max_model_len:
+            if total + 1 >= most_len:
                 return None
             seqs.append(seq)
-        need = [0] * len(self.cache.groups)
-        for seq in seqs:
-            for g, n in enumerate(self.cache.pages_needed(seq.seq_id, 1)):
-                need[g] += n
+        ids = [seq.seq_id for seq in seqs]
+        need = self.cache.pages_needed_each(ids, 1)
         if any(n > pool.num_free for n, pool in zip(need, self.cache.pools)):
             return None
         self.step_t += 1
@@ -292,11 +298,11 @@ class Scheduler:
         if self.waiting:
             self._skipped_head_steps += 1      # as ``_admit`` counts a step without admission
         plan = StepPlan(self.step_t)
+        self.cache.extend_each(ids, 1)
+        items = plan.items
         for seq in seqs:
-            self.cache.extend(seq.seq_id, 1)
-            plan.items.append(PlanItem(seq.seq_id, [PLACEHOLDER], seq.num_computed_tokens, sample=True,
-                                       params=seq.request.params, rng_seed=seq.rng_seed,
-                                       rng_offset=seq.num_output_tokens + 1, fed_on_device=True))
+            items.append(PlanItem(seq.seq_id, [PLACEHOLDER], seq.num_computed_tokens, True,
+                                  seq.request.params, seq.rng_seed, len(seq.output_token_ids) + 1, True))
         self.last_plan = plan
         return plan
 

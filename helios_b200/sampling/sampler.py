@@ -56,13 +56,14 @@ class Sampler:
         i64 = words[:4 * R].view(np.int64)
         f32 = words[4 * R:6 * R].view(np.float32)
         top_k = words[6 * R:]
-        narrows = False
-        for i, p in enumerate(params):
-            narrows = narrows or (p.temperature > 0 and (p.top_k > 0 or p.top_p < 1.0))
-            i64[i] = np.uint64(seeds[i] & (2**64 - 1)).astype(np.int64)
-            i64[R + i] = offsets[i]
-            f32[i], f32[R + i] = p.temperature, p.top_p
-            top_k[i] = p.top_k
+        # whole arrays at once: with hundreds of rows a loop of scalar stores costs a millisecond
+        mask = 2**64 - 1
+        i64[:R] = np.fromiter((s & mask for s in seeds), dtype=np.uint64, count=R).view(np.int64)
+        i64[R:] = offsets
+        f32[:R] = [p.temperature for p in params]
+        f32[R:] = [p.top_p for p in params]
+        top_k[:] = [p.top_k for p in params]
+        narrows = any(p.temperature > 0 and (p.top_k > 0 or p.top_p < 1.0) for p in params)
         dev = torch.empty(7 * R, dtype=torch.int32, device=logits.device)
         dev.copy_(st.host[:7 * R], non_blocking=True)
         st.event.record()
