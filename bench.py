@@ -686,12 +686,16 @@ def main():
             num_blocks=args.batch * (args.context // page + 2) + 8, watermark=0.0,
             run_ahead=not args.no_run_ahead), model=model)
         ctx0 = args.context - args.steps - args.warmup - SETTLE_STEPS
-        # every request must still be decoding when the timed steps end, whenever its
-        # prompt was finished
+        # every request must still be decoding when the timed steps end, whenever its prompt
+        # was finished: the first ones decode while the others' prompts are still being filled
+        head_start = max(64, -(-args.batch * ctx0 // PREFILL_TOKENS) + 8)
+        if head_start >= ctx0:
+            raise SystemExit(f"--batch {args.batch} at --context {args.context}: the prompts take longer "
+                             "to fill than the context leaves room for")
         for b in range(args.batch):
-            toks = torch.randint(0, cfg["vocab_size"], (ctx0 - 64,), generator=gen).tolist()
+            toks = torch.randint(0, cfg["vocab_size"], (ctx0 - head_start,), generator=gen).tolist()
             engine.add_request(f"e{b}", toks, SamplingParams(
-                max_tokens=args.steps + args.warmup + SETTLE_STEPS + 64, seed=b, **sampling))
+                max_tokens=args.steps + args.warmup + SETTLE_STEPS + head_start, seed=b, **sampling))
         while any(s.num_pending_tokens > 1 for s in engine.scheduler.running) or engine.scheduler.waiting:
             engine.step()
         for _ in range(SETTLE_STEPS):        # as in measure_decode: out of the prompt fill's power state
