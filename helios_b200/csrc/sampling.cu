@@ -313,8 +313,12 @@ sample_cluster_kernel(int* __restrict__ out, const float* __restrict__ logits, i
       for (int j = 0; j < 15; ++j) acc[j] = 0.f;
 #pragma unroll
       for (int i = 0; i < EPT; ++i) {
+        // (what is below the digits settled so far is below every threshold of this pass:
+        // after a pass or two that is nearly everything, and whole warps skip it)
+        if (key[i] > cand) {
 #pragma unroll
-        for (int j = 0; j < 15; ++j) acc[j] += (key[i] >= (cand | ((uint32_t)(j + 1) << shift))) ? 1.f : 0.f;
+          for (int j = 0; j < 15; ++j) acc[j] += (key[i] >= (cand | ((uint32_t)(j + 1) << shift))) ? 1.f : 0.f;
+        }
       }
       sc_sum15(acc, warp_part, block_part, total, slot);
       slot ^= 1;
@@ -343,7 +347,7 @@ sample_cluster_kernel(int* __restrict__ out, const float* __restrict__ logits, i
       for (int j = 0; j < 15; ++j) acc[j] = 0.f;
 #pragma unroll
       for (int i = 0; i < EPT; ++i) {
-        if (key[i] >= thr) {
+        if (key[i] >= thr && key[i] > cand) {
           const float e = expf(key_float(key[i]) * inv_t - mx_t);
 #pragma unroll
           for (int j = 0; j < 15; ++j) acc[j] += (key[i] >= (cand | ((uint32_t)(j + 1) << shift))) ? e : 0.f;
