@@ -440,6 +440,21 @@ def run_micro(args):
                                                                 sumsq=ss, eps=1e-5))
                         report(name + "_with_rms_factor", us, rows * cols * 2, tokens=T)
             del w
+    elif args.micro == "sampling":
+        V = cfg["vocab_size"]
+        cases = (("greedy", (0.0, 0, 1.0)), ("temperature", (0.8, 0, 1.0)), ("top_k_50", (0.8, 50, 1.0)),
+                 ("top_p_09", (0.8, 0, 0.9)), ("top_k_50_top_p_09", (0.8, 50, 0.9)))
+        for R in (1, 8, 64, 256):
+            logits = torch.randn(R, V, device=dev) * 3
+            seeds = torch.arange(R, dtype=torch.int64, device=dev)
+            offsets = torch.zeros(R, dtype=torch.int64, device=dev)
+            for name, (temp, k, p) in cases:
+                t = torch.full((R,), temp, device=dev)
+                kk = torch.full((R,), k, dtype=torch.int32, device=dev)
+                pp = torch.full((R,), p, device=dev)
+                for kernel, kind in (("one block a row", "one_block"), ("cluster a row", "narrow")):
+                    us = chain_us(lambda i: ops.sample(logits, t, kk, pp, seeds, offsets, kind=kind))
+                    report(name, us, R * V * 4, rows=R, vocab=V, kernel=kernel)
     else:
         B, ctx, page = args.batch, args.context, 16
         pages = B * (ctx // page)
@@ -493,7 +508,7 @@ def main():
     ap.add_argument("--max-prompt", type=int, default=4096)
     ap.add_argument("--budget", type=int, default=2048, help="tokens a step (chunked prefill)")
     ap.add_argument("--new-tokens", type=int, default=256)
-    ap.add_argument("--micro", default=None, choices=["gemm", "attention_decode"],
+    ap.add_argument("--micro", default=None, choices=["gemm", "attention_decode", "sampling"],
                     help="time one kind of kernel as a chain in a captured graph instead of the step "
                          "(sizes of --model; --batch tokens or requests, --context keys)")
     ap.add_argument("--micro-case", default=None, help="--micro gemm: one of gate_up, down, qkv, o")

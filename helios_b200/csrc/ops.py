@@ -643,13 +643,14 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
 # ------------------------------------------------------------------ sampling
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
            top_p: torch.Tensor, seed: torch.Tensor, offset: torch.Tensor,
-           narrows: Optional[bool] = None) -> torch.Tensor:
+           kind: Optional[str] = None) -> torch.Tensor:
     """One token id per row of float32 ``logits`` [R, V]; per-row options as device tensors
     (temperature float32 with 0 = greedy, top_k int32 with 0 = off, top_p float32,
-    seed and offset int64).  ``narrows``: whether any row has a top-k or top-p to search a
-    threshold for, if the caller knows (the options live on the device): rows that only take
-    the argmax or draw from all values are quickest on the one-block kernel, threshold
-    searches on the cluster kernel (``sampling.cu``); None lets the row length decide."""
+    seed and offset int64).  ``kind``: what the caller knows of the options, which live on
+    the device: "greedy" (every row takes the argmax), "draw" (some rows draw, none has a
+    top-k or top-p), "narrow" (some have); it chooses between the kernel with one block a row
+    and the one with a cluster of blocks a row (``sampling.cu``), as does the number of
+    rows.  "one_block" takes the first whatever the rows; None counts as "narrow"."""
     _check(logits, "logits", torch.float32, 2)
     R, V = logits.shape
     _check(temperature, "temperature", torch.float32, 1)
@@ -666,8 +667,11 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
             [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
              c_void_p, c_int, c_void_p])
     _run(f(_p(out), _p(logits), R, V, V, _p(temperature), _p(top_k), _p(top_p), _p(seed),
-           _p(offset), -1 if narrows is None else int(bool(narrows)), _stream()), "sample")
+           _p(offset), _SAMPLE_KINDS[kind], _stream()), "sample")
     return out
+
+
+_SAMPLE_KINDS = {None: -1, "greedy": 0, "draw": 1, "narrow": 2, "one_block": 3}
 
 
 def philox_uniform(seed: int, offset: int) -> float:

@@ -457,19 +457,22 @@ static int launch_sample_cluster(int* out, const float* logits, int R, int V, in
 }
 
 
-// Rows of 4,096 to 163,840 values go to the cluster kernel (a row of fewer gives eight blocks
-// nothing to share out), anything else to the one-block kernel; and so does everything when
-// the caller knows that no row has a top-k or top-p (narrows = 0; 1: some has; -1: unknown):
-// argmax and a draw from all values read the row once either way, and one block of 1,024
-// threads does that faster than eight that first sort it into registers (64 rows of 128,256:
-// 14 against 29 µs greedy; with top-k and top-p 1,015 against 428 µs, 8 rows 669 against 87).
+// Rows of 4,096 to 163,840 values can go to the cluster kernel (a row of fewer gives eight
+// blocks nothing to share out).  It wins while its eight blocks a row find SMs of their own,
+// and longer the more passes over the row the options ask for; `kind` says what the caller
+// knows of them (the options live on the device): 0 every row takes the argmax, 1 some rows
+// draw but none has a top-k or top-p, 2 some have (-1: unknown, taken as 2), 3: the one-block
+// kernel whatever the rows.  Measured in chains at 128,256 values, one block / cluster, µs:
+// argmax 10 / 5 at 8 rows, 16 / 25 at 64, 24 / 116 at 256; temperature 57 / 11, 84 / 54,
+// 95 / 229; top-k 50 and top-p 0.9: 672 / 80, 1,030 / 391, 1,630 / 1,407.
 HB_EXPORT int hb_sample(int* out, const float* logits, int R, int V, int ld, const float* temperature,
                         const int* top_k, const float* top_p, const unsigned long long* seed,
-                        const unsigned long long* offset, int narrows, cudaStream_t stream) {
+                        const unsigned long long* offset, int kind, cudaStream_t stream) {
   if (R <= 0) return HB_OK;
   if (V <= 0) return HB_BAD_ARGUMENT;
   const int per_thread = (V + SC_CLUSTER * SC_THREADS - 1) / (SC_CLUSTER * SC_THREADS);
-  if (narrows != 0 && V >= 4096 && per_thread <= SC_MOST) {
+  const int most_rows = kind == 0 ? 32 : kind == 1 ? 128 : kind == 3 ? 0 : 1 << 30;
+  if (R <= most_rows && V >= 4096 && per_thread <= SC_MOST) {
 #define HB_SAMPLE_CASE(EPT_)                                                                          \
     if (per_thread <= EPT_)                                                                            \
       return launch_sample_cluster<EPT_>(out, logits, R, V, ld, temperature, top_k, top_p, seed, offset, stream)

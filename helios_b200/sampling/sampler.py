@@ -63,10 +63,13 @@ class Sampler:
         f32[:R] = [p.temperature for p in params]
         f32[R:] = [p.top_p for p in params]
         top_k[:] = [p.top_k for p in params]
-        narrows = any(p.temperature > 0 and (p.top_k > 0 or p.top_p < 1.0) for p in params)
+        if any(p.temperature > 0 and (p.top_k > 0 or p.top_p < 1.0) for p in params):
+            kind = "narrow"
+        else:
+            kind = "draw" if any(p.temperature > 0 for p in params) else "greedy"
         dev = torch.empty(7 * R, dtype=torch.int32, device=logits.device)
         dev.copy_(st.host[:7 * R], non_blocking=True)
         st.event.record()
         d64 = dev[:4 * R].view(torch.int64)
         d32 = dev[4 * R:6 * R].view(torch.float32)
-        return ops.sample(logits, d32[:R], dev[6 * R:], d32[R:], d64[:R], d64[R:], narrows=narrows)
+        return ops.sample(logits, d32[:R], dev[6 * R:], d32[R:], d64[:R], d64[R:], kind=kind)

@@ -426,10 +426,10 @@ def test_linear_bf16(M):
 
 
 # ---------------------------------------------------------------------- sampling
-def _sample(logits, temps, ks, ps, seeds, offsets, narrows=None):
+def _sample(logits, temps, ks, ps, seeds, offsets, kind=None):
     t = lambda x, d: torch.tensor(x, dtype=d, device=DEV)
     return ops().sample(logits.to(DEV), t(temps, torch.float32), t(ks, torch.int32), t(ps, torch.float32),
-                        t(seeds, torch.int64), t(offsets, torch.int64), narrows=narrows).cpu().tolist()
+                        t(seeds, torch.int64), t(offsets, torch.int64), kind=kind).cpu().tolist()
 
 
 @pytest.mark.parametrize("V", [1231, 40000, 128256])
@@ -447,8 +447,8 @@ def test_greedy_is_argmax_with_lowest_index_on_ties(V):
 @pytest.mark.parametrize("V", [384, 1231, 4095, 4096, 4097, 8192, 50001, 128256, 151936, 163840, 163841])
 def test_temperature_top_k_top_p_follow_the_reference_rules(V, one_block):
     """Rows of 4,096 to 163,840 values run on the kernel that spreads a row over a cluster of
-    blocks, the others, and every row when the caller says that none narrows (which is always
-    allowed), on the kernel with one block a row."""
+    blocks, the others, and every row when the caller asks for it, on the kernel with one
+    block a row."""
     g = torch.Generator().manual_seed(V)
     R = 24
     logits = torch.randn(R, V, generator=g) * 2
@@ -457,7 +457,7 @@ def test_temperature_top_k_top_p_follow_the_reference_rules(V, one_block):
     ps = [1.0, 1.0, 0.9, 0.5, 1.0, 0.2] * 4
     seeds = [11 + i for i in range(R)]
     offsets = [i * 3 for i in range(R)]
-    got = _sample(logits, temps, ks, ps, seeds, offsets, narrows=False if one_block else None)
+    got = _sample(logits, temps, ks, ps, seeds, offsets, kind="one_block" if one_block else None)
     for i in range(R):
         u = ops().philox_uniform(seeds[i], offsets[i])
         want = plain_model.sample_reference(logits[i], temps[i], ks[i], ps[i], u)
