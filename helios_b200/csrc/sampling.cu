@@ -167,9 +167,10 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int V, in
 
 // ---------------------------------------------------------------------------------------------
 // The same sampling with a row spread over a thread-block cluster: every block keeps its
-// eighth of the row in REGISTERS (as order-preserving keys), so the threshold searches read
-// memory once instead of once per bit, settle four bits a pass (fifteen thresholds counted
-// side by side), and eight SMs work on a row instead of one.  Sums keep a fixed order: a
+// eighth of the row in SHARED MEMORY (as order-preserving keys, a thread's run of values in a
+// row of its own), so the threshold searches read global memory once instead of once per
+// bit, settle four bits a pass (fifteen thresholds counted side by side), and eight SMs work
+// on a row instead of one; three such blocks fit an SM.  Sums keep a fixed order: a
 // thread's elements in index order, the block's threads by `block_sum`, the cluster's blocks
 // by rank; the draw walks the row in index order as the kernel above does.
 constexpr int SC_THREADS = 512;
@@ -228,7 +229,7 @@ __device__ __forceinline__ void sc_sum15(float (&acc)[15], float (*warp_part)[15
 }
 
 template <int EPT>
-__global__ void __launch_bounds__(SC_THREADS)
+__global__ void __launch_bounds__(SC_THREADS, EPT <= 32 ? 3 : 2)
 sample_cluster_kernel(int* __restrict__ out, const float* __restrict__ logits, int V, int ld,
                       const float* __restrict__ temperature, const int* __restrict__ top_k,
                       const float* __restrict__ top_p, const unsigned long long* __restrict__ seed,
@@ -248,21 +249,20 @@ sample_cluster_kernel(int* __restrict__ out, const float* __restrict__ logits, i
   const int first = ((int)rank * SC_THREADS + tid) * EPT;       // this thread's elements, in index order
 
   // The block's part of the row comes in with consecutive threads on consecutive values and
-  // goes through shared memory (rows of EPT + 1, so that the threads' own runs of EPT values
-  // do not meet in one bank).
-  extern __shared__ float staged[];
+  // stays in shared memory as keys, a thread's run of EPT values in a row of EPT + 1 (the runs
+  // of a warp's threads then lie in different banks); 0 where the row has ended (no float
+  // has key 0 but one NaN).
+  extern __shared__ uint32_t keys[];
   {
     const int block_first = (int)rank * SC_THREADS * EPT;
 #pragma unroll 8
     for (int c = tid; c < SC_THREADS * EPT; c += SC_THREADS) {
       const int owner = c / EPT, i = c - owner * EPT;
-      staged[owner * (EPT + 1) + i] = (block_first + c < V) ? l[block_first + c] : 0.f;
+      keys[owner * (EPT + 1) + i] = (block_first + c < V) ? float_key(l[block_first + c]) : 0u;
     }
     __syncthreads();
   }
-  uint32_t key[EPT];                       // 0 where the row has ended (no float has key 0 but one NaN)
-#pragma unroll
-  for (int i = 0; i < EPT; ++i) key[i] = (first + i < V) ? float_key(staged[tid * (EPT + 1) + i]) : 0u;
+  const uint32_t* key = keys + tid * (EPT + 1);
 
   // ---- argmax, lowest index among equals
   uint32_t bk = 0;
@@ -463,15 +463,15 @@ static int launch_sample_cluster(int* out, const float* logits, int R, int V, in
 // knows of them (the options live on the device): 0 every row takes the argmax, 1 some rows
 // draw but none has a top-k or top-p, 2 some have (-1: unknown, taken as 2), 3: the one-block
 // kernel whatever the rows.  Measured in chains at 128,256 values, one block / cluster, µs:
-// argmax 10 / 5 at 8 rows, 16 / 25 at 64, 24 / 116 at 256; temperature 57 / 11, 84 / 54,
-// 95 / 229; top-k 50 and top-p 0.9: 672 / 80, 1,030 / 391, 1,630 / 1,407.
+// argmax 10 / 6 at 8 rows, 16 / 15 at 64, 24 / 58 at 256; temperature 57 / 13, 84 / 31,
+// 95 / 106; top-k 50 and top-p 0.9: 672 / 91, 1,000 / 262, 1,620 / 855.
 HB_EXPORT int hb_sample(int* out, const float* logits, int R, int V, int ld, const float* temperature,
                         const int* top_k, const float* top_p, const unsigned long long* seed,
                         const unsigned long long* offset, int kind, cudaStream_t stream) {
   if (R <= 0) return HB_OK;
   if (V <= 0) return HB_BAD_ARGUMENT;
   const int per_thread = (V + SC_CLUSTER * SC_THREADS - 1) / (SC_CLUSTER * SC_THREADS);
-  const int most_rows = kind == 0 ? 32 : kind == 1 ? 128 : kind == 3 ? 0 : 1 << 30;
+  const int most_rows = kind == 0 ? 64 : kind == 1 ? 192 : kind == 3 ? 0 : 1 << 30;
   if (R <= most_rows && V >= 4096 && per_thread <= SC_MOST) {
 #define HB_SAMPLE_CASE(EPT_)                                                                          \
     if (per_thread <= EPT_)                                                                            \
