@@ -9,7 +9,7 @@ the group, and a (page, kv head) tile of ``page_size x head_dim`` is contiguous.
 """
 from __future__ import annotations
 
-from typing import Dict, Hashable, List, Optional, Sequence, Tuple
+from typing import Dict, Hashable, List, Optional, Tuple
 
 import torch
 

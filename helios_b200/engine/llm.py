@@ -4,7 +4,6 @@ run_until_complete / generate`` (python/helios/engine.py:120-470) and the shorte
 from __future__ import annotations
 
 import random
-from pathlib import Path
 from typing import Dict, List, Optional, Sequence, Union
 
 import torch

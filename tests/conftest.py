@@ -4,7 +4,6 @@ tolerances all comparisons use."""
 from __future__ import annotations
 
 import json
-import os
 import sys
 from pathlib import Path
 

@@ -2,7 +2,6 @@
 values with scattered page ids and poisoned free pages, and dense float64 references."""
 from __future__ import annotations
 
-import math
 from types import SimpleNamespace
 
 import torch

@@ -1,7 +1,6 @@
 """Each request alone and whole: one step over the whole sequence, logits at every
 place, against the plain implementation."""
 import pytest
-import torch
 
 from conftest import (TINY_CONFIGS, assert_logits_close, bf16_round, random_tokens, read_folder)
 import plain_model

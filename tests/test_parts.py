@@ -9,7 +9,6 @@ import torch
 
 import plain_model
 from conftest import TINY_LLAMA, assert_logits_close, random_tokens
-from kernel_util import dense_attention, make_paged_case, step_ctx
 
 pytestmark = pytest.mark.gpu
 DEV = torch.device("cuda:0")

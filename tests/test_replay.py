@@ -4,7 +4,6 @@ one by one; portions of changing size down to two tokens; and mixed, up to four
 live requests with so few pages that they are used again.  Once per
 configuration and dtype the whole set also goes through ``bin/trace_run``."""
 import pytest
-import torch
 
 from conftest import TINY_CONFIGS, bf16_round, random_tokens, read_folder
 import plain_model

@@ -3,12 +3,11 @@ import json
 
 import pytest
 import torch
-from safetensors.torch import load_file, save_file
+from safetensors.torch import save_file
 
 from conftest import TINY_CONFIGS, TINY_LLAMA, TINY_QWEN, read_folder
 from helios_b200.config import resolve_architecture
-from helios_b200.weights import (WeightsError, expected_tensors, load_weights, random_tensors,
-                                 write_model_folder)
+from helios_b200.weights import WeightsError, expected_tensors, load_weights, random_tensors
 
 
 def _plan(raw):

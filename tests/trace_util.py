@@ -4,7 +4,6 @@ user runs it), and how every returned row is compared with the plain model."""
 from __future__ import annotations
 
 import json
-import os
 import random
 import subprocess
 import sys
