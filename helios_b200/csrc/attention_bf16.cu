@@ -18,6 +18,7 @@
 // paged_attn.py:49.  Scores, the running maximum, the sum and the output
 // accumulators are float32; probabilities are rounded to bfloat16 for the PV
 // product, as the reference casts them to the value dtype (paged_attn.py:293).
+#include <type_traits>
 #include "common.cuh"
 #include "attention_mma.cuh"
 
@@ -27,6 +28,64 @@ namespace {
 constexpr int DEC_WARPS = 4;
 constexpr int DEC_TILE = 16;      // keys per warp tile
 constexpr int DEC_STAGES = 3;     // tiles a warp keeps in shared memory (all but one in flight)
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// The online-softmax step of the decode kernel over a tile's scaled, masked scores (log2
+// domain).  Without WIDE only the first eight rows of the MMA tile are query heads: the
+// second row group (rows 8-15, zero queries) is left out and its probabilities are zero.
+// The output and the sum are rescaled only in tiles where some row's maximum grew (a
+// warp-wide vote; otherwise every factor would be exactly 1).
+template <int HD, int NT, bool WIDE>
+__device__ __forceinline__ void decode_softmax_step(float (&s)[NT][4], float (&m)[2], float (&l)[2],
+                                                    float (&o)[HD / 8][4]) {
+  constexpr int R = WIDE ? 2 : 1;
+  float m_new[2] = {m[0], m[1]};
+  bool grew = false;
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    float mx = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) mx = fmaxf(mx, fmaxf(s[nt][2 * r], s[nt][2 * r + 1]));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    m_new[r] = fmaxf(m[r], mx);
+    grew = grew || m_new[r] > m[r];
+  }
+  if (__any_sync(0xffffffffu, grew)) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const float corr = fast_exp2(m[r] - ((m_new[r] == -INFINITY) ? 0.f : m_new[r]));
+      l[r] *= corr;
+#pragma unroll
+      for (int nt = 0; nt < HD / 8; ++nt) {
+        o[nt][2 * r] *= corr;
+        o[nt][2 * r + 1] *= corr;
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    m[r] = m_new[r];
+    const float m_use = (m_new[r] == -INFINITY) ? 0.f : m_new[r];
+    float sum = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      s[nt][2 * r] = fast_exp2(s[nt][2 * r] - m_use);
+      s[nt][2 * r + 1] = fast_exp2(s[nt][2 * r + 1] - m_use);
+      sum += s[nt][2 * r] + s[nt][2 * r + 1];
+    }
+    l[r] += sum;
+  }
+  if (!WIDE) {
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) s[nt][2] = s[nt][3] = 0.f;
+  }
+}
 
 template <int HD>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
@@ -63,11 +122,31 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
   const int* table = block_table + (size_t)seq * bt_stride;
 
   __nv_bfloat16* my = smem + (size_t)warp * DEC_STAGES * 2 * TILE_ELEMS;   // [stage][k|v][tile]
-  // A tile is DEC_TILE rows of HD/8 16-byte chunks.  Lane r first finds the cache row of
-  // key r (its page and slot); then consecutive lanes copy consecutive chunks, so a warp
-  // instruction reads 512 contiguous bytes.
+  // A tile is DEC_TILE rows of HD/8 16-byte chunks; consecutive lanes copy consecutive
+  // chunks, so a warp instruction reads 512 contiguous bytes.  Where the tile's keys are
+  // consecutive slots of ONE page (page_size a multiple of the tile, no window's ragged
+  // start) the whole tile is one contiguous stretch of the cache: one look-up in the block
+  // table and one address per warp.  Otherwise lane r first finds the cache row of key r.
+  const bool whole_pages = page_size % DEC_TILE == 0 && lo % DEC_TILE == 0;
   auto load_tile = [&](int tile, int stage) {
     constexpr int CH = HD / 8;
+    __nv_bfloat16* kd = my + (size_t)(stage * 2) * TILE_ELEMS;
+    __nv_bfloat16* vd = kd + TILE_ELEMS;
+    if (whole_pages) {
+      const int key_first = lo + tile * DEC_TILE;
+      const int page = table[key_first / page_size];
+      const size_t base = ((size_t)(page * nkv + kvh) * page_size + key_first % page_size) * HD + lane * 8;
+      const int rows_valid = k_end - key_first;            // >= 1; rows from there on are zero-filled
+#pragma unroll
+      for (int it = 0; it < DEC_TILE * CH / 32; ++it) {
+        const int idx = it * 32 + lane;
+        const int row = idx / CH, c = idx - row * CH;
+        const int bytes = row < rows_valid ? 16 : 0;
+        cp_async16(kd + row * RS + c * 8, k_pages + base + it * 256, bytes);
+        cp_async16(vd + row * RS + c * 8, v_pages + base + it * 256, bytes);
+      }
+      return;
+    }
     int row_id = -1;
     if (lane < DEC_TILE) {
       const int key = lo + tile * DEC_TILE + lane;
@@ -76,8 +155,6 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
         row_id = (page * nkv + kvh) * page_size + key % page_size;
       }
     }
-    __nv_bfloat16* kd = my + (size_t)(stage * 2) * TILE_ELEMS;
-    __nv_bfloat16* vd = kd + TILE_ELEMS;
 #pragma unroll
     for (int it = 0; it < DEC_TILE * CH / 32; ++it) {
       const int idx = it * 32 + lane;
@@ -179,35 +256,50 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     }
   }
 
-  int stage = 0;
-  for (; tile < tile_end; tile += DEC_WARPS) {
-    const int ahead = tile + (DEC_STAGES - 1) * DEC_WARPS;
-    int put = stage + DEC_STAGES - 1;
-    if (put >= DEC_STAGES) put -= DEC_STAGES;
-    if (ahead < tile_end) load_tile(ahead, put);
-    cp_async_commit();
-    cp_async_wait<DEC_STAGES - 1>();
-    __syncwarp();
-    const __nv_bfloat16* kt = my + (size_t)(stage * 2) * TILE_ELEMS;
-    const __nv_bfloat16* vt = kt + TILE_ELEMS;
-    float s[DEC_TILE / 8][4];
+  // the key tiles of this warp; `wide` (a compile-time tag): more than eight query heads
+  // share the KV head, so both row groups of the MMA tile are live
+  auto run = [&](auto wide) {
+    constexpr bool WIDE = decltype(wide)::value;
+    int stage = 0;
+    for (; tile < tile_end; tile += DEC_WARPS) {
+      const int ahead = tile + (DEC_STAGES - 1) * DEC_WARPS;
+      int put = stage + DEC_STAGES - 1;
+      if (put >= DEC_STAGES) put -= DEC_STAGES;
+      if (ahead < tile_end) load_tile(ahead, put);
+      cp_async_commit();
+      cp_async_wait<DEC_STAGES - 1>();
+      __syncwarp();
+      const __nv_bfloat16* kt = my + (size_t)(stage * 2) * TILE_ELEMS;
+      const __nv_bfloat16* vt = kt + TILE_ELEMS;
+      float s[DEC_TILE / 8][4];
 #pragma unroll
-    for (int i = 0; i < DEC_TILE / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
-    qk_tile<HD, DEC_TILE / 8>(s, qa, kt, lane);
-    const int key0 = lo + tile * DEC_TILE + 2 * (lane & 3);
+      for (int i = 0; i < DEC_TILE / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+      qk_tile<HD, DEC_TILE / 8>(s, qa, kt, lane);
+      const int tile_key0 = lo + tile * DEC_TILE;
+      if (tile_key0 + DEC_TILE > k_end) {          // the last tile: keys beyond the token's own
+        const int key0 = tile_key0 + 2 * (lane & 3);
 #pragma unroll
-    for (int nt = 0; nt < DEC_TILE / 8; ++nt) {
+        for (int nt = 0; nt < DEC_TILE / 8; ++nt) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int key = key0 + nt * 8 + (e & 1);
-        s[nt][e] = (key < k_end) ? s[nt][e] * scale_log2 : -INFINITY;
+          for (int e = 0; e < 4; ++e) {
+            const int key = key0 + nt * 8 + (e & 1);
+            s[nt][e] = (key < k_end) ? s[nt][e] * scale_log2 : -INFINITY;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int nt = 0; nt < DEC_TILE / 8; ++nt) {
+#pragma unroll
+          for (int e = 0; e < (WIDE ? 4 : 2); ++e) s[nt][e] *= scale_log2;
+        }
       }
+      decode_softmax_step<HD, DEC_TILE / 8, WIDE>(s, m, l, o);
+      pv_tile<HD, DEC_TILE / 8>(o, s, vt, lane);
+      __syncwarp();
+      if (++stage == DEC_STAGES) stage = 0;
     }
-    softmax_step<HD, DEC_TILE / 8>(s, m, l, o);
-    pv_tile<HD, DEC_TILE / 8>(o, s, vt, lane);
-    __syncwarp();
-    if (++stage == DEC_STAGES) stage = 0;
-  }
+  };
+  if (G > 8) run(std::true_type()); else run(std::false_type());
   cp_async_wait<0>();
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
