@@ -150,7 +150,7 @@ def test_generic_attention(dtype, nh, nkv, hd, page, window):
 
 
 @pytest.mark.parametrize("nh,nkv,hd,page", [(32, 8, 128, 16), (28, 4, 128, 16), (14, 2, 64, 8), (6, 6, 96, 64),
-                                            (16, 1, 32, 16), (7, 1, 64, 3)])
+                                            (16, 1, 32, 16), (7, 1, 64, 3), (24, 2, 128, 32)])
 @pytest.mark.parametrize("window", [None, 100])
 @pytest.mark.parametrize("splits,cluster", [(1, True), (3, True), (8, True), (3, False), (8, False), (13, True)])
 def test_decode_attention_bf16(nh, nkv, hd, page, window, splits, cluster, monkeypatch):
