@@ -25,7 +25,8 @@
 namespace {
 
 // ------------------------------------------------------------------------ decode
-constexpr int DEC_WARPS = 4;
+// warps per decode block: 4 (two blocks an SM), or 8 (one block an SM) where so few blocks run
+// that each warp's chain of key tiles, not the memory, bounds the kernel
 constexpr int DEC_TILE = 16;      // keys per warp tile
 constexpr int DEC_STAGES = 3;     // tiles a warp keeps in shared memory (all but one in flight)
 
@@ -87,8 +88,8 @@ __device__ __forceinline__ void decode_softmax_step(float (&s)[NT][4], float (&m
   }
 }
 
-template <int HD>
-__global__ void __launch_bounds__(DEC_WARPS * 32)
+template <int HD, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32)
 decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
                         float* __restrict__ part_ml, const __nv_bfloat16* __restrict__ q,
                         int q_stride, const __nv_bfloat16* __restrict__ k_pages,
@@ -180,7 +181,7 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
   bool early[DEC_STAGES - 1];
 #pragma unroll
   for (int p = 0; p < DEC_STAGES - 1; ++p) {
-    const int tp = tile + p * DEC_WARPS;
+    const int tp = tile + p * WARPS;
     early[p] = tp < tile_end && tp < tiles_total - 1;
     if (early[p]) load_tile(tp, p);
   }
@@ -190,7 +191,7 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     // value before it fetches that tile
     const int last_tile = tiles_total - 1;
     if (k_write != nullptr && last_tile >= tile_begin && last_tile < tile_end &&
-        (last_tile - tile_begin) % DEC_WARPS == warp) {
+        (last_tile - tile_begin) % WARPS == warp) {
       const int page = table[pos / page_size];
       const size_t dst = ((size_t)(page * nkv + kvh) * page_size + pos % page_size) * HD;
       const __nv_bfloat16* k_new = q + (size_t)seq * q_stride + (size_t)(nh + kvh) * HD;
@@ -215,7 +216,7 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
   }
 #pragma unroll
   for (int p = 0; p < DEC_STAGES - 1; ++p) {
-    const int tp = tile + p * DEC_WARPS;
+    const int tp = tile + p * WARPS;
     if (tp < tile_end && !early[p]) load_tile(tp, p);
     cp_async_commit();
   }
@@ -261,8 +262,8 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
   auto run = [&](auto wide) {
     constexpr bool WIDE = decltype(wide)::value;
     int stage = 0;
-    for (; tile < tile_end; tile += DEC_WARPS) {
-      const int ahead = tile + (DEC_STAGES - 1) * DEC_WARPS;
+    for (; tile < tile_end; tile += WARPS) {
+      const int ahead = tile + (DEC_STAGES - 1) * WARPS;
       int put = stage + DEC_STAGES - 1;
       if (put >= DEC_STAGES) put -= DEC_STAGES;
       if (ahead < tile_end) load_tile(ahead, put);
@@ -310,9 +311,9 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
   // merge the block's warps through shared memory (reusing the tile buffers)
   __syncthreads();
   float* red_o = reinterpret_cast<float*>(smem_raw);                 // [warps][16][HD]
-  float* red_m = red_o + DEC_WARPS * 16 * HD;                        // [warps][16]
-  float* red_l = red_m + DEC_WARPS * 16;
-  float* cta_o = red_l + DEC_WARPS * 16;                             // [16][HD] this block's merged partial
+  float* red_m = red_o + WARPS * 16 * HD;                        // [warps][16]
+  float* red_l = red_m + WARPS * 16;
+  float* cta_o = red_l + WARPS * 16;                             // [16][HD] this block's merged partial
   float* cta_ml = cta_o + 16 * HD;                                   // [16][2]
   {
     const int g0 = lane >> 2, c0 = 2 * (lane & 3);
@@ -332,15 +333,15 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     }
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < G * HD; idx += DEC_WARPS * 32) {
+  for (int idx = threadIdx.x; idx < G * HD; idx += WARPS * 32) {
     const int row = idx / HD, d = idx - row * HD;
     float M = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, red_m[w * 16 + row]);
+    for (int w = 0; w < WARPS; ++w) M = fmaxf(M, red_m[w * 16 + row]);
     const float m_use = (M == -INFINITY) ? 0.f : M;
     float L = 0.f, acc = 0.f;
 #pragma unroll
-    for (int w = 0; w < DEC_WARPS; ++w) {
+    for (int w = 0; w < WARPS; ++w) {
       const float f = exp2f(red_m[w * 16 + row] - m_use);
       L += red_l[w * 16 + row] * f;
       acc += red_o[((size_t)w * 16 + row) * HD + d] * f;
@@ -381,7 +382,7 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     const int total = G * HD;
     const int per = (total + n_splits - 1) / n_splits;
     const int e_end = min(total, (split + 1) * per);
-    for (int idx = split * per + threadIdx.x; idx < e_end; idx += DEC_WARPS * 32) {
+    for (int idx = split * per + threadIdx.x; idx < e_end; idx += WARPS * 32) {
       const int row = idx / HD, d = idx - row * HD;
       float ms[8], ls[8], os[8];
 #pragma unroll
@@ -563,7 +564,7 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
   }
 }
 
-template <int HD>
+template <int HD, int WARPS>
 int launch_decode(void* out, float* part_o, float* part_ml, const void* q, int q_stride,
                   const void* k_pages, const void* v_pages, const int* block_table, int bt_stride,
                   const int* positions, int S, int nh, int nkv, int page_size, int window,
@@ -573,10 +574,10 @@ int launch_decode(void* out, float* part_o, float* part_ml, const void* q, int q
   // the new keys and values go into the very pages the kernel reads
   __nv_bfloat16* k_write = write_cache ? (__nv_bfloat16*)const_cast<void*>(k_pages) : nullptr;
   __nv_bfloat16* v_write = write_cache ? (__nv_bfloat16*)const_cast<void*>(v_pages) : nullptr;
-  size_t smem = (size_t)DEC_WARPS * DEC_STAGES * 2 * DEC_TILE * RS * sizeof(__nv_bfloat16);
-  const size_t red = (size_t)(DEC_WARPS * 16 * (HD + 2) + 16 * (HD + 2)) * sizeof(float);
+  size_t smem = (size_t)WARPS * DEC_STAGES * 2 * DEC_TILE * RS * sizeof(__nv_bfloat16);
+  const size_t red = (size_t)(WARPS * 16 * (HD + 2) + 16 * (HD + 2)) * sizeof(float);
   if (red > smem) smem = red;
-  auto kernel = decode_attention_kernel<HD>;
+  auto kernel = decode_attention_kernel<HD, WARPS>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
@@ -589,7 +590,7 @@ int launch_decode(void* out, float* part_o, float* part_ml, const void* q, int q
     // the slices of one (request, KV head) as a cluster: merged through distributed shared memory
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
-    cfg.blockDim = dim3(DEC_WARPS * 32);
+    cfg.blockDim = dim3(WARPS * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
@@ -607,7 +608,7 @@ int launch_decode(void* out, float* part_o, float* part_ml, const void* q, int q
                        rot_cos, rot_sin, k_write, v_write);
     return hb_check_launch();
   }
-  hb_launch(kernel, dim3(grid), dim3(DEC_WARPS * 32), smem, stream, 
+  hb_launch(kernel, dim3(grid), dim3(WARPS * 32), smem, stream, 
       (__nv_bfloat16*)out, part_o, part_ml, (const __nv_bfloat16*)q, q_stride,
       (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, bt_stride,
       positions, nh, nkv, page_size, window, scale * LOG2E, n_splits, 0,
@@ -621,18 +622,18 @@ int launch_decode(void* out, float* part_o, float* part_ml, const void* q, int q
 // Clusters of `cluster_size` decode blocks the device keeps resident at once (-1 if the
 // query fails): whole clusters are placed inside a GPC, so this can be fewer than the blocks
 // that would fit one by one.
-template <int HD>
+template <int HD, int WARPS>
 int decode_max_clusters(int cluster_size) {
   constexpr int RS = HD + 8;
-  size_t smem = (size_t)DEC_WARPS * DEC_STAGES * 2 * DEC_TILE * RS * sizeof(__nv_bfloat16);
-  const size_t red = (size_t)(DEC_WARPS * 16 * (HD + 2) + 16 * (HD + 2)) * sizeof(float);
+  size_t smem = (size_t)WARPS * DEC_STAGES * 2 * DEC_TILE * RS * sizeof(__nv_bfloat16);
+  const size_t red = (size_t)(WARPS * 16 * (HD + 2) + 16 * (HD + 2)) * sizeof(float);
   if (red > smem) smem = red;
-  auto kernel = decode_attention_kernel<HD>;
+  auto kernel = decode_attention_kernel<HD, WARPS>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     return -1;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(cluster_size, 1, 1);
-  cfg.blockDim = dim3(DEC_WARPS * 32);
+  cfg.blockDim = dim3(WARPS * 32);
   cfg.dynamicSmemBytes = smem;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -696,22 +697,29 @@ HB_EXPORT int hb_attention_decode_bf16(void* out, float* part_o, float* part_ml,
                                        const int* block_table, int bt_stride, const int* positions,
                                        int S, int nh, int nkv, int hd, int page_size, int window,
                                        float scale, int n_splits, const float* rot_cos,
-                                       const float* rot_sin, int write_cache, cudaStream_t stream) {
+                                       const float* rot_sin, int write_cache, int warps,
+                                       cudaStream_t stream) {
   if (S <= 0) return HB_OK;
-  if (nkv <= 0 || nh % nkv != 0 || nh / nkv > 16 || page_size <= 0 || n_splits < 1)
+  if (nkv <= 0 || nh % nkv != 0 || nh / nkv > 16 || page_size <= 0 || n_splits < 1 ||
+      (warps != 4 && warps != 8))
     return HB_BAD_ARGUMENT;
   if ((rot_cos == nullptr) != (rot_sin == nullptr)) return HB_BAD_ARGUMENT;
   if (write_cache && (q_stride < (nh + 2 * nkv) * hd || (q_stride & 7) || ((uintptr_t)q & 15)))
     return HB_BAD_ARGUMENT;
-  HB_DISPATCH_HD(hd, return launch_decode<HD>(out, part_o, part_ml, q, q_stride, k_pages, v_pages,
-                                              block_table, bt_stride, positions, S, nh, nkv,
-                                              page_size, window, scale, n_splits, rot_cos, rot_sin,
-                                              write_cache, stream));
+#define HB_DECODE(W)                                                                              \
+  HB_DISPATCH_HD(hd, return (launch_decode<HD, W>(out, part_o, part_ml, q, q_stride, k_pages, v_pages, \
+                                                  block_table, bt_stride, positions, S, nh, nkv,      \
+                                                  page_size, window, scale, n_splits, rot_cos,        \
+                                                  rot_sin, write_cache, stream)))
+  if (warps == 8) HB_DECODE(8);
+  HB_DECODE(4);
+#undef HB_DECODE
 }
 
-HB_EXPORT int hb_attention_decode_max_clusters(int hd, int cluster_size) {
-  if (cluster_size < 1 || cluster_size > 8) return -1;
-  HB_DISPATCH_HD(hd, return decode_max_clusters<HD>(cluster_size));
+HB_EXPORT int hb_attention_decode_max_clusters(int hd, int cluster_size, int warps) {
+  if (cluster_size < 1 || cluster_size > 8 || (warps != 4 && warps != 8)) return -1;
+  if (warps == 8) HB_DISPATCH_HD(hd, return (decode_max_clusters<HD, 8>(cluster_size)));
+  HB_DISPATCH_HD(hd, return (decode_max_clusters<HD, 4>(cluster_size)));
 }
 
 // Prefill / mixed: q_tiles holds (request, first local token) for every tile of

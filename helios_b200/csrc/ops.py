@@ -744,35 +744,69 @@ def _wave_splits(blocks: int, slots: int, most: int) -> int:
 
 _decode_clusters = {}
 
+#: Decode attention blocks have 4 warps, two blocks an SM, or 8 warps, one block an SM, for
+#: steps of so few requests that clusters of eight such blocks per (request, KV head) are all
+#: resident at once: a warp walks its key tiles one after the other, about 0.8 microseconds
+#: each, and with few blocks that chain, not the memory, is what the kernel takes.  Measured,
+#: milliseconds a decode step at Llama-3.1-8B sizes, context 4,096 (slices, warps): one request
+#: 3.140 (29, 4), 3.129 (8, 4), 3.007 (8, 8), 3.073 (18, 8); two 3.192 (17, 4), 3.164 (8, 8);
+#: four 3.365 (9, 4), 3.308 (8, 4), 3.289 (4, 8); eight 3.718 (4, 4), 3.891 (2, 8): once the
+#: four-warp blocks fill the SMs they are ahead.  False: always 4.
+ATTENTION_DECODE_WIDE_BLOCKS = True
 
-def decode_cluster_capacity(head_dim: int, size: int) -> int:
-    """Clusters of ``size`` decode-attention blocks the device keeps resident at once (the
-    occupancy calculator knows how the SMs are spread over the GPCs, which bounds whole
-    clusters: 71 clusters of 4 on a B200 where 74 would fit block by block)."""
-    key = (head_dim, size)
+
+def decode_cluster_capacity(head_dim: int, size: int, warps: int = 4) -> int:
+    """Clusters of ``size`` decode-attention blocks of ``warps`` warps the device keeps
+    resident at once (the occupancy calculator knows how the SMs are spread over the GPCs,
+    which bounds whole clusters: 71 clusters of 4 on a B200 where 74 would fit block by block)."""
+    key = (head_dim, size, warps)
     if key not in _decode_clusters:
         n = -1
         if torch.cuda.is_available() and head_dim in TILED_HEAD_DIMS and 1 <= size <= 8:
-            n = int(load_library("attention_bf16").hb_attention_decode_max_clusters(head_dim, size))
-        _decode_clusters[key] = n if n > 0 else (2 * sm_count()) // size
+            n = int(load_library("attention_bf16").hb_attention_decode_max_clusters(head_dim, size, warps))
+        _decode_clusters[key] = n if n > 0 else ((2 if warps == 4 else 1) * sm_count()) // size
     return _decode_clusters[key]
+
+
+#: ... and each of the eight warps still has this many keys (four tiles) of the longest context
+#: (Qwen2.5-0.5B sizes at 1,024 tokens, 21 keys a warp: 0.783 against 0.773 ms a step)
+ATTENTION_DECODE_WIDE_MIN_KEYS = 64
+
+
+def decode_warps(blocks: int, n_splits: int, head_dim: int, max_context: int) -> int:
+    """Warps per block for ``blocks`` (request, KV head) pairs in ``n_splits`` slices of at most
+    ``max_context`` keys together: 8 for slices that run as a cluster in a step small enough
+    for clusters of eight, where a warp still has keys enough, else 4."""
+    if not (ATTENTION_DECODE_WIDE_BLOCKS and ATTENTION_CLUSTER_MERGE and 1 < n_splits <= 8):
+        return 4
+    if max_context < ATTENTION_DECODE_WIDE_MIN_KEYS * 8 * n_splits:
+        return 4
+    fits = min(decode_cluster_capacity(head_dim, n_splits, 8), decode_cluster_capacity(head_dim, 8, 8))
+    return 8 if blocks <= fits else 4
 
 
 def decode_splits(num_seqs: int, num_kv_heads: int, max_context: int, head_dim: int = 128) -> int:
     """Slices of the context per (request, KV head) of the decode attention kernel, by a cost
     model fitted to measurements (64 requests x 8 KV heads of 128 at contexts 1,024 and 4,096;
-    it then predicts 40 to 96 requests within 5 %): two blocks are resident per SM, the blocks
-    run in rounds of that many, and a block costs its keys plus a fixed part (set-up, merge)
-    worth about 176 keys of 128 values.  A slice has at least 128 keys."""
+    it then predicts 40 to 96 requests within 5 %): two blocks of four warps are resident per
+    SM, the blocks run in rounds of that many, and a block costs its keys plus a fixed part
+    (set-up, merge) worth about 176 keys of 128 values; slices that do not run as a cluster
+    need the merge kernel, worth about 300 keys more; a block of eight warps
+    (``decode_warps``) walks its keys twice as fast.  A slice has at least 128 keys."""
     blocks = max(1, num_seqs * num_kv_heads)
     slots = 2 * sm_count()
     fixed = 176.0 * 128.0 / max(1, head_dim)
+    merge_kernel = 300.0 * 128.0 / max(1, head_dim)
     best, best_cost = 1, None
     for s in range(1, max(1, min(32, max_context // 128)) + 1):
         # 2 to 8 slices run as one cluster per (request, KV head) while all clusters are
         # resident at once; otherwise block by block, with a merge kernel
-        rounds = 1 if (1 < s <= 8 and blocks <= decode_cluster_capacity(head_dim, s)) else -(-blocks * s // slots)
-        cost = rounds * (max_context / s + fixed)
+        if decode_warps(blocks, s, head_dim, max_context) == 8:
+            cost = max_context / s / 2 + fixed
+        else:
+            clustered = 1 < s <= 8 and ATTENTION_CLUSTER_MERGE and blocks <= decode_cluster_capacity(head_dim, s)
+            rounds = 1 if clustered else -(-blocks * s // slots)
+            cost = rounds * (max_context / s + fixed) + (0.0 if clustered or s == 1 else merge_kernel)
         if best_cost is None or cost < best_cost * 0.94:      # fewer slices unless clearly better
             best, best_cost = s, cost
     return best
@@ -782,7 +816,7 @@ def attention_decode_bf16(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: tor
                           block_table: torch.Tensor, positions: torch.Tensor, num_heads: int,
                           num_kv_heads: int, head_dim: int, page_size: int,
                           window: Optional[int], scale: float, n_splits: int,
-                          rotary=None, write_cache: bool = False) -> torch.Tensor:
+                          rotary=None, write_cache: bool = False, warps: Optional[int] = None) -> torch.Tensor:
     """Decode attention (token i is the one new token of request i) on the tensor cores;
     bfloat16, head_dim in TILED_HEAD_DIMS, at most 16 query heads per KV head.
 
@@ -790,7 +824,8 @@ def attention_decode_bf16(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: tor
     rotated yet; the kernel rotates the query heads on the way in.  ``write_cache``: the
     requests' new keys (rotated likewise) and values are still in ``qkv`` and the kernel
     stores them in the pages before it attends.  (Without either, ``rope_kv_write`` must have
-    run.)  ``qkv`` itself is left as it was."""
+    run.)  ``qkv`` itself is left as it was.  ``warps``: 4 (the default) or 8 warps a block
+    (``decode_warps``)."""
     _check(qkv, "qkv", torch.bfloat16, 2)
     _check(k_pages, "k_pages", torch.bfloat16, 4)
     _check(v_pages, "v_pages", torch.bfloat16, 4)
@@ -823,18 +858,21 @@ def attention_decode_bf16(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: tor
     part_o = part_ml = None
     # slices as one cluster only while all blocks are resident at once: with several rounds
     # of blocks, clusters (whose blocks must start together) cost more than the merge kernel
-    one_round = n_splits <= 8 and S * num_kv_heads <= decode_cluster_capacity(head_dim, n_splits)
+    warps = 4 if warps is None else int(warps)
+    if warps not in (4, 8):
+        raise KernelError(f"decode attention blocks have 4 or 8 warps, not {warps}")
+    one_round = n_splits <= 8 and S * num_kv_heads <= decode_cluster_capacity(head_dim, n_splits, warps)
     if n_splits > 8 or (n_splits > 1 and not (ATTENTION_CLUSTER_MERGE and one_round)):
         part_o = torch.empty((S, num_heads, n_splits, head_dim), dtype=torch.float32, device=qkv.device)
         part_ml = torch.empty((S, num_heads, n_splits, 2), dtype=torch.float32, device=qkv.device)
     f = _fn("attention_bf16", "hb_attention_decode_bf16",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p,
-             c_int, c_void_p])
+             c_int, c_int, c_void_p])
     _run(f(_p(out), _p(part_o), _p(part_ml), _p(qkv), qkv.shape[1], _p(k_pages), _p(v_pages),
            _p(block_table), block_table.shape[1], _p(positions), S, num_heads, num_kv_heads,
            head_dim, page_size, int(window or 0), float(scale), int(n_splits), _p(cos), _p(sin),
-           1 if write_cache else 0, _stream()),
+           1 if write_cache else 0, int(warps), _stream()),
          "attention_decode_bf16")
     return out
 
@@ -990,7 +1028,9 @@ def attention(ctx, qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
                 splits = decode_splits(ctx.num_seqs, num_kv_heads, ctx.max_context_len, head_dim)
             return attention_decode_bf16(qkv, k_pages, v_pages, block_table, ctx.positions,
                                          num_heads, num_kv_heads, head_dim, page_size, window,
-                                         scale, splits, rotary, write_cache)
+                                         scale, splits, rotary, write_cache,
+                                         decode_warps(ctx.num_seqs * num_kv_heads, splits, head_dim,
+                                                      ctx.max_context_len))
         if (ATTENTION_TCGEN05 and ctx.max_tokens_per_seq >= 16
                 and tc_attention_supported(num_heads, num_kv_heads, head_dim, page_size)):
             tile = 128 // (num_heads // num_kv_heads)

@@ -164,6 +164,22 @@ def test_decode_attention_bf16(nh, nkv, hd, page, window, splits, cluster, monke
     torch.testing.assert_close(out.cpu().double(), dense_attention(case, scale, window), atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("nh,nkv,hd,page", [(32, 8, 128, 16), (14, 2, 64, 8), (24, 2, 128, 32), (6, 6, 96, 3)])
+@pytest.mark.parametrize("window", [None, 100])
+@pytest.mark.parametrize("splits,cluster", [(1, True), (3, True), (8, True), (5, False), (13, True)])
+@pytest.mark.parametrize("warps", [4, 8])
+def test_decode_attention_blocks_of_four_and_of_eight_warps(nh, nkv, hd, page, window, splits, cluster, warps,
+                                                            monkeypatch):
+    """The kernel runs with 4 or 8 warps a block (``ops.decode_warps`` chooses; here it is given)."""
+    monkeypatch.setattr(ops(), "ATTENTION_CLUSTER_MERGE", cluster)
+    seqs = [(n, 1) for n in (0, 1, 31, 33, 129, 255, 1000, 2049)]
+    case = make_paged_case(seqs, nh, nkv, hd, page, torch.bfloat16, DEV, seed=nh + hd + warps)
+    scale = 1.0 / math.sqrt(hd)
+    out = ops().attention_decode_bf16(case.qkv, case.k_pages, case.v_pages, case.table, case.positions,
+                                      nh, nkv, hd, page, window, scale, splits, warps=warps)
+    torch.testing.assert_close(out.cpu().double(), dense_attention(case, scale, window), atol=2e-2, rtol=2e-2)
+
+
 @pytest.mark.parametrize("nh,nkv,hd,page", [(32, 8, 128, 16), (28, 4, 128, 16), (14, 2, 64, 8), (6, 6, 96, 64),
                                             (16, 1, 32, 16), (7, 1, 64, 3)])
 @pytest.mark.parametrize("window", [None, 100])
