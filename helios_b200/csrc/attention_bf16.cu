@@ -4,7 +4,9 @@
 //   * decode: one query token per request.  A block takes one (request, KV head,
 //     slice of the context); the query heads that share the KV head are the rows
 //     of one MMA tile, so every key and value is read once for the whole group.
-//     Slices are merged by a second kernel (flash-decoding).  The kernel can take the
+//     Up to 8 slices run as one thread-block cluster and are merged through distributed
+//     shared memory; more are merged by a second kernel (flash-decoding).  A block has 4
+//     or 8 warps, each with key tiles of its own.  The kernel can take the
 //     step's rotary position encoding and cache write with it: every block rotates its
 //     query heads in registers, and the one warp whose tile holds the request's new
 //     token rotates that key and puts it and the value into the cache first
@@ -25,8 +27,8 @@
 namespace {
 
 // ------------------------------------------------------------------------ decode
-// warps per decode block: 4 (two blocks an SM), or 8 (one block an SM) where so few blocks run
-// that each warp's chain of key tiles, not the memory, bounds the kernel
+// (warps per decode block, a template parameter: 4, two blocks an SM, or 8, one block an SM,
+// where so few blocks run that each warp's chain of key tiles, not the memory, bounds the kernel)
 constexpr int DEC_TILE = 16;      // keys per warp tile
 constexpr int DEC_STAGES = 3;     // tiles a warp keeps in shared memory (all but one in flight)
 
