@@ -589,3 +589,35 @@ def test_captured_steps_pad_the_request_count_by_less_than_a_quarter():
         assert p == n if n <= 8 else 4 * (p - n) < n
         sizes.add(p)
     assert len(sizes) <= 8 + 4 * 7 and sorted(sizes)[:12] == [1, 2, 3, 4, 5, 6, 7, 8, 10, 12, 14, 16]
+
+
+def test_decode_attention_slices_and_warps_by_the_size_of_the_step(monkeypatch):
+    """``ops.decode_splits`` / ``ops.decode_warps`` with the cluster capacities of a device of
+    148 SMs: few requests run clusters of eight-warp blocks, eight requests clusters of four
+    slices, many requests whole contexts; a slice never has fewer than 128 keys, and eight warps
+    only where each has 64 keys."""
+    from helios_b200.csrc import ops
+
+    four = {1: 296, 2: 148, 3: 98, 4: 71, 5: 56, 6: 48, 7: 40, 8: 34}
+    eight = {1: 148, 2: 74, 3: 48, 4: 35, 5: 28, 6: 24, 7: 20, 8: 16}
+    monkeypatch.setattr(ops, "sm_count", lambda device=None: 148)
+    monkeypatch.setattr(ops, "decode_cluster_capacity",
+                        lambda head_dim, size, warps=4: (eight if warps == 8 else four)[size])
+
+    def plan(requests, kv_heads, context, head_dim=128):
+        s = ops.decode_splits(requests, kv_heads, context, head_dim)
+        return s, ops.decode_warps(requests * kv_heads, s, head_dim, context)
+
+    assert plan(1, 8, 4096) == (8, 8) and plan(2, 8, 4096) == (8, 8)
+    assert plan(4, 8, 4096) == (8, 4)          # 32 clusters of 8 four-warp blocks, no merge kernel
+    assert plan(8, 8, 4096) == (4, 4)
+    assert plan(64, 8, 4096) == (1, 4) and plan(256, 2, 1024, 64) == (1, 4)
+    assert plan(9, 8, 4096)[0] > 1 and plan(9, 8, 4096)[1] == 4     # 72 pairs: no room for clusters of 4
+    assert plan(1, 2, 1024, 64)[1] == 4        # 1,024 keys over 6 to 8 slices: too few for eight warps
+    for requests in (1, 3, 8, 20, 100):
+        for context in (128, 200, 1000, 5000):
+            s, w = plan(requests, 8, context)
+            assert 1 <= s <= max(1, context // 128)
+            assert w == 4 or context >= 64 * 8 * s
+    monkeypatch.setattr(ops, "ATTENTION_DECODE_WIDE_BLOCKS", False)
+    assert plan(1, 8, 4096)[1] == 4
