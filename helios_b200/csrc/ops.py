@@ -792,7 +792,11 @@ def decode_splits(num_seqs: int, num_kv_heads: int, max_context: int, head_dim: 
     SM, the blocks run in rounds of that many, and a block costs its keys plus a fixed part
     (set-up, merge) worth about 176 keys of 128 values; slices that do not run as a cluster
     need the merge kernel, worth about 300 keys more; a block of eight warps
-    (``decode_warps``) walks its keys twice as fast.  A slice has at least 128 keys."""
+    (``decode_warps``) walks its keys twice as fast.  A slice has at least 128 keys.  More
+    slices are taken when the model gives them 4 % (measured, milliseconds a step at
+    Llama-3.1-8B sizes, with the count that a margin of 6 % chose against this one's: 16
+    requests x 32,768 keys 15.70 / 14.74, 32 x 16,384 15.91 / 15.06, 64 x 8,192 15.63 / 15.21,
+    8 x 32,768 9.23 / 8.98)."""
     blocks = max(1, num_seqs * num_kv_heads)
     slots = 2 * sm_count()
     fixed = 176.0 * 128.0 / max(1, head_dim)
@@ -807,7 +811,7 @@ def decode_splits(num_seqs: int, num_kv_heads: int, max_context: int, head_dim: 
             clustered = 1 < s <= 8 and ATTENTION_CLUSTER_MERGE and blocks <= decode_cluster_capacity(head_dim, s)
             rounds = 1 if clustered else -(-blocks * s // slots)
             cost = rounds * (max_context / s + fixed) + (0.0 if clustered or s == 1 else merge_kernel)
-        if best_cost is None or cost < best_cost * 0.94:      # fewer slices unless clearly better
+        if best_cost is None or cost < best_cost * 0.96:      # fewer slices unless clearly better
             best, best_cost = s, cost
     return best
 
