@@ -115,7 +115,12 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
   const int G = nh / nkv;
   const int pos = positions[seq];
   const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-  const int n_keys = pos - lo + 1;
+  // Tiles start at a multiple of the tile size where pages hold whole tiles: then every tile's
+  // keys are consecutive slots of ONE page.  Keys of the first tile from before the window
+  // are zero-filled and masked.
+  const bool whole_pages = page_size % DEC_TILE == 0;
+  const int first = whole_pages ? lo - lo % DEC_TILE : lo;
+  const int n_keys = pos - first + 1;
   // slices of whole tiles
   const int tiles_total = (n_keys + DEC_TILE - 1) / DEC_TILE;
   const int tiles_per_split = (tiles_total + n_splits - 1) / n_splits;
@@ -127,24 +132,24 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
   __nv_bfloat16* my = smem + (size_t)warp * DEC_STAGES * 2 * TILE_ELEMS;   // [stage][k|v][tile]
   // A tile is DEC_TILE rows of HD/8 16-byte chunks; consecutive lanes copy consecutive
   // chunks, so a warp instruction reads 512 contiguous bytes.  Where the tile's keys are
-  // consecutive slots of ONE page (page_size a multiple of the tile, no window's ragged
-  // start) the whole tile is one contiguous stretch of the cache: one look-up in the block
-  // table and one address per warp.  Otherwise lane r first finds the cache row of key r.
-  const bool whole_pages = page_size % DEC_TILE == 0 && lo % DEC_TILE == 0;
+  // consecutive slots of ONE page (page_size a multiple of the tile) the whole tile is one
+  // contiguous stretch of the cache: one look-up in the block table and one address per
+  // warp.  Otherwise lane r first finds the cache row of key r.
   auto load_tile = [&](int tile, int stage) {
     constexpr int CH = HD / 8;
     __nv_bfloat16* kd = my + (size_t)(stage * 2) * TILE_ELEMS;
     __nv_bfloat16* vd = kd + TILE_ELEMS;
     if (whole_pages) {
-      const int key_first = lo + tile * DEC_TILE;
+      const int key_first = first + tile * DEC_TILE;
       const int page = table[key_first / page_size];
       const size_t base = ((size_t)(page * nkv + kvh) * page_size + key_first % page_size) * HD + lane * 8;
-      const int rows_valid = k_end - key_first;            // >= 1; rows from there on are zero-filled
+      const int rows_valid = k_end - key_first;            // >= 1; rows from there on are zero-filled,
+      const int rows_skipped = lo - key_first;             // and so are rows before the window
 #pragma unroll
       for (int it = 0; it < DEC_TILE * CH / 32; ++it) {
         const int idx = it * 32 + lane;
         const int row = idx / CH, c = idx - row * CH;
-        const int bytes = row < rows_valid ? 16 : 0;
+        const int bytes = (row < rows_valid && row >= rows_skipped) ? 16 : 0;
         cp_async16(kd + row * RS + c * 8, k_pages + base + it * 256, bytes);
         cp_async16(vd + row * RS + c * 8, v_pages + base + it * 256, bytes);
       }
@@ -152,7 +157,7 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
     }
     int row_id = -1;
     if (lane < DEC_TILE) {
-      const int key = lo + tile * DEC_TILE + lane;
+      const int key = first + tile * DEC_TILE + lane;
       if (key < k_end) {
         const int page = table[key / page_size];
         row_id = (page * nkv + kvh) * page_size + key % page_size;
@@ -278,15 +283,16 @@ decode_attention_kernel(__nv_bfloat16* __restrict__ out, float* __restrict__ par
 #pragma unroll
       for (int i = 0; i < DEC_TILE / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
       qk_tile<HD, DEC_TILE / 8>(s, qa, kt, lane);
-      const int tile_key0 = lo + tile * DEC_TILE;
-      if (tile_key0 + DEC_TILE > k_end) {          // the last tile: keys beyond the token's own
+      const int tile_key0 = first + tile * DEC_TILE;
+      if (tile_key0 + DEC_TILE > k_end || tile_key0 < lo) {
+        // the last tile (keys beyond the token's own) or the first (keys before the window)
         const int key0 = tile_key0 + 2 * (lane & 3);
 #pragma unroll
         for (int nt = 0; nt < DEC_TILE / 8; ++nt) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int key = key0 + nt * 8 + (e & 1);
-            s[nt][e] = (key < k_end) ? s[nt][e] * scale_log2 : -INFINITY;
+            s[nt][e] = (key < k_end && key >= lo) ? s[nt][e] * scale_log2 : -INFINITY;
           }
         }
       } else {
