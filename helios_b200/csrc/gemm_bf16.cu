@@ -142,6 +142,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
   }
 
+  // Residual epilogue with the K slices as a cluster: what a thread's first two elements need
+  // from global memory (the residual, the norm weight, the bias) does not depend on this
+  // kernel's sums; it is fetched as soon as the kernel before is done, under the main loop.
+  float early_old[2] = {0.f, 0.f}, early_weight[2] = {0.f, 0.f}, early_bias[2] = {0.f, 0.f};
+
   if (warp == 0) {
    if (lane == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -216,6 +221,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     pdl_wait();                                    // nothing is written before the kernel before is done
     const int quarter = warp & 3;                  // the 32 lanes of tensor memory this warp may read
     const int r = quarter * 32 + lane;             // row of the A-side tile
+    if (SWAP && args.residual != nullptr && args.cluster_reduce) {
+      const int S = args.k_splits;
+      const int r0 = split * BM / S, nrows = (split + 1) * BM / S - r0;
+      const int ncols = min(BN, args.T - tile_b * BN);
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const int e = (int)threadIdx.x - 64 + k * 128;
+        if (e < ncols * nrows) {
+          const int c = e / nrows;
+          const int t = tile_b * BN + c, n = tile_a * BM + r0 + (e - c * nrows);
+          if (n < args.N) {
+            early_old[k] = __ldcg(args.residual + (size_t)t * args.N + n);
+            if (args.norm_weight) early_weight[k] = args.norm_weight[n];
+            if (args.bias) early_bias[k] = args.bias[n];
+          }
+        }
+      }
+    }
     const bool scaled = SWAP && args.sumsq_in != nullptr;
     if (scaled) {
       // 1 / rms of this tile's tokens, while the products run: a warp per column adds the
@@ -438,9 +461,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           const int c = e / nrows, rr = r0 + (e - c * nrows);
           const int t = tile_b * BN + c, n = tile_a * BM + rr;
           const bool mine = n < args.N;
-          const float old = mine ? args.residual[(size_t)t * args.N + n] : 0.f;
-          const float weight_n = (mine && args.norm_weight) ? args.norm_weight[n] : 0.f;
-          const float bias_n = (mine && args.bias) ? args.bias[n] : 0.f;
+          const int k = (e - et) >> 7;               // the first two were fetched under the main loop
+          const bool early = k < 2;
+          const float old = k == 0 ? early_old[0] : early ? early_old[1]
+                            : mine ? args.residual[(size_t)t * args.N + n] : 0.f;
+          const float weight_n = k == 0 ? early_weight[0] : early ? early_weight[1]
+                                 : (mine && args.norm_weight) ? args.norm_weight[n] : 0.f;
+          const float bias_n = k == 0 ? early_bias[0] : early ? early_bias[1]
+                               : (mine && args.bias) ? args.bias[n] : 0.f;
           float pv[8];
 #pragma unroll
           for (int sp = 0; sp < 8; ++sp)
