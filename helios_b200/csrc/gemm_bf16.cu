@@ -514,13 +514,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       // two elements a thread and pass: the loads of both (from up to 8 peers each) go out
       // before either sum is used
       for (int e0 = e_begin + (int)threadIdx.x - 64; e0 < e_end; e0 += 256) {
-        float gv[2][8], uv[2][8];
+        float gv[2][8], uv[2][8], bias_n[2];
         bool live[2];
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
           const int e = e0 + k * 128;
           const int c = e / BM, rr = e - c * BM;
           live[k] = e < e_end && (SWAP || tile_a * BM + rr < args.T);     // not a row beyond the last token
+          // the bias goes out with the partial sums, not after them
+          const int feature = SWAP ? tile_a * BM + rr : tile_b * OUT_COLS + c;
+          bias_n[k] = (args.bias != nullptr && live[k] && feature < args.N) ? args.bias[feature] : 0.f;
 #pragma unroll
           for (int sp = 0; sp < 8; ++sp) {
             const bool on = live[k] && sp < S;
@@ -544,7 +547,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           if (SWAP) { t = tile_b * BN + c; n = tile_a * BM + rr; }
           else { t = tile_a * BM + rr; n = tile_b * OUT_COLS + c; }
           if (t < args.T && n < args.N) {
-            if (args.bias) val += args.bias[n];
+            val += bias_n[k];
             if (args.out_f32) reinterpret_cast<float*>(args.out)[(size_t)t * args.ldo + n] = val;
             else reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)t * args.ldo + n] = __float2bfloat16_rn(val);
           }
